@@ -1,0 +1,163 @@
+// Combine: per-route FC2 rows -> one output row per token.
+//
+//   * combine_routes_kernel restates the accumulation of the Python oracle
+//     (python/reference/glmrt_reference/moe_ref.py:30-36): for slot in order,
+//     out = bf16(out + bf16(bf16(w) * y)), so the result is independent of how routes were
+//     scheduled and bit-reproducible (the reference keeps a fixed-order sum for the same
+//     reason: native/cuda/kernels/b12x_direct.cu:203-219, residual.cu:438-453);
+//   * sum_topk8, weighted scatter-add and row gather keep the reference entry points
+//     (b12x_direct.cu:203-219, residual.cu:666-678, residual.cu:133-158).
+#include "common.cuh"
+#include "internal.h"
+
+namespace glmrt {
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void __launch_bounds__(kThreads)
+combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __restrict__ topk_weights,
+                      const int32_t* __restrict__ route_slot, uint16_t* __restrict__ out, int rows, int top_k,
+                      int hidden) {
+  const int vec_per_row = hidden / 8;
+  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
+  if (gid >= static_cast<size_t>(rows) * vec_per_row) return;
+  const int row = static_cast<int>(gid / vec_per_row);
+  const int v = static_cast<int>(gid % vec_per_row);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int k = 0; k < top_k; ++k) {
+    const int r = row * top_k + k;
+    if (route_slot != nullptr && route_slot[r] < 0) continue;
+    const float w = bf16_bits_to_f32(f32_to_bf16_rne(topk_weights[r]));
+    const uint4 y4 = reinterpret_cast<const uint4*>(route_rows + static_cast<size_t>(r) * hidden)[v];
+    const uint32_t yw[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float y0 = __uint_as_float(yw[i] << 16);
+      const float y1 = __uint_as_float(yw[i] & 0xffff0000u);
+      const float p0 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w, y0)));
+      const float p1 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w, y1)));
+      acc[2 * i] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i], p0)));
+      acc[2 * i + 1] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i + 1], p1)));
+    }
+  }
+  uint4 o;
+  o.x = (__float_as_uint(acc[0]) >> 16) | (__float_as_uint(acc[1]) & 0xffff0000u);
+  o.y = (__float_as_uint(acc[2]) >> 16) | (__float_as_uint(acc[3]) & 0xffff0000u);
+  o.z = (__float_as_uint(acc[4]) >> 16) | (__float_as_uint(acc[5]) & 0xffff0000u);
+  o.w = (__float_as_uint(acc[6]) >> 16) | (__float_as_uint(acc[7]) & 0xffff0000u);
+  reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * hidden)[v] = o;
+}
+
+// Fixed-order float32 sum of 8 rows of width 6144, truncating bf16 store.
+__global__ void __launch_bounds__(kThreads)
+sum_topk8_kernel(const uint16_t* __restrict__ routed, uint16_t* __restrict__ out, size_t rows) {
+  constexpr int kWidth = 6144, kTop = 8;
+  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
+  if (gid >= rows * (kWidth / 2)) return;
+  const size_t row = gid / (kWidth / 2);
+  const size_t pair = gid % (kWidth / 2);
+  float a = 0.0f, b = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kTop; ++k) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(routed + (row * kTop + k) * kWidth)[pair];
+    a = __fadd_rn(a, __uint_as_float(w << 16));
+    b = __fadd_rn(b, __uint_as_float(w & 0xffff0000u));
+  }
+  reinterpret_cast<uint32_t*>(out + row * kWidth)[pair] =
+      (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xffff0000u);
+}
+
+__global__ void __launch_bounds__(kThreads)
+scatter_add_weighted_kernel(const uint16_t* __restrict__ src, const uint32_t* __restrict__ row_indices,
+                            const float* __restrict__ row_weights, float* __restrict__ dst, size_t rows,
+                            size_t width) {
+  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
+  if (gid >= rows * width) return;
+  const size_t r = gid / width, c = gid % width;
+  atomicAdd(&dst[static_cast<size_t>(row_indices[r]) * width + c], row_weights[r] * bf16_bits_to_f32(src[gid]));
+}
+
+__global__ void __launch_bounds__(kThreads)
+gather_rows_bf16_kernel(const uint16_t* __restrict__ src, const uint32_t* __restrict__ row_indices,
+                        uint16_t* __restrict__ dst, size_t rows, size_t width) {
+  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
+  if (gid >= rows * width) return;
+  const size_t r = gid / width, c = gid % width;
+  dst[gid] = src[static_cast<size_t>(row_indices[r]) * width + c];
+}
+
+unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / kThreads); }
+
+}  // namespace
+
+glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
+                                     const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
+                                     cudaStream_t stream) {
+  combine_routes_kernel<<<grid_for(static_cast<size_t>(rows) * (hidden / 8)), kThreads, 0, stream>>>(
+      route_rows, topk_weights, route_slot, out, rows, top_k, hidden);
+  GLMRT_LAUNCH_CHECK("combine_routes_kernel");
+  return GLMRT_STATUS_OK;
+}
+
+}  // namespace glmrt
+
+using namespace glmrt;
+
+extern "C" glmrt_status_t glmrt_cuda_b12x_spark_sum_topk8_bf16_async(glmrt_device_buffer_t routed_bf16,
+                                                                     glmrt_device_buffer_t output_bf16,
+                                                                     size_t rows, void* cuda_stream) {
+  if (routed_bf16.ptr == nullptr || output_bf16.ptr == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "sum_topk8: null buffer");
+  if (rows == 0) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "sum_topk8: rows must be > 0");
+  size_t out_bytes = 0, in_bytes = 0;
+  if (!checked_mul(rows, 6144 * 2, &out_bytes) || !checked_mul(out_bytes, 8, &in_bytes))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "sum_topk8: size overflow");
+  if (routed_bf16.bytes < in_bytes || output_bf16.bytes < out_bytes)
+    return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "sum_topk8: buffer too small");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  sum_topk8_kernel<<<grid_for(rows * 3072), kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint16_t*>(routed_bf16.ptr), static_cast<uint16_t*>(output_bf16.ptr), rows);
+  GLMRT_LAUNCH_CHECK("sum_topk8_kernel");
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32_async(
+    const uint16_t* src, const uint32_t* row_indices, const float* row_weights, float* dst, size_t rows,
+    size_t row_width, void* cuda_stream) {
+  if (src == nullptr || row_indices == nullptr || row_weights == nullptr || dst == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "scatter_add: null pointer argument");
+  size_t total = 0;
+  if (rows == 0 || row_width == 0 || !checked_mul(rows, row_width, &total))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "scatter_add: bad dimensions");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  scatter_add_weighted_kernel<<<grid_for(total), kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, row_indices, row_weights, dst, rows, row_width);
+  GLMRT_LAUNCH_CHECK("scatter_add_weighted_kernel");
+  return ok();
+}
+extern "C" glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32(const uint16_t* src,
+                                                                           const uint32_t* row_indices,
+                                                                           const float* row_weights, float* dst,
+                                                                           size_t rows, size_t row_width) {
+  GLMRT_RETURN_IF_ERROR(glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32_async(src, row_indices, row_weights, dst,
+                                                                               rows, row_width, nullptr));
+  return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+}
+
+extern "C" glmrt_status_t glmrt_cuda_gather_rows_bf16_async(const uint16_t* src, const uint32_t* row_indices,
+                                                            uint16_t* dst, size_t rows, size_t row_width,
+                                                            void* cuda_stream) {
+  if (src == nullptr || row_indices == nullptr || dst == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows: null pointer argument");
+  size_t total = 0;
+  if (rows == 0 || row_width == 0 || !checked_mul(rows, row_width, &total))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows: bad dimensions");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  gather_rows_bf16_kernel<<<grid_for(total), kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, row_indices, dst, rows, row_width);
+  GLMRT_LAUNCH_CHECK("gather_rows_bf16_kernel");
+  return ok();
+}

@@ -1,0 +1,107 @@
+// Internal launch interfaces shared by the translation units of libglmrt_b200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace glmrt {
+
+// Error bits a kernel may set in the layer's device error word.
+enum DeviceError : uint32_t {
+  kErrWaitTimeout = 1u,       // a bounded mbarrier / flag wait gave up
+  kErrSlotOverflow = 2u,      // route plan needs more slots than the layer holds
+  kErrChunkOverflow = 4u,     // more (expert, token-chunk) work items than the layer holds
+  kErrBadExpert = 8u,         // a route names an expert id >= experts
+};
+
+// Counters written by the route-plan kernel (device memory, uint32 each).
+enum Counter : int {
+  kCntChunks = 0,
+  kCntSlots = 1,
+  kCntError = 2,
+  kCntDistinct = 3,
+  kCntLocalRoutes = 4,
+  kCntWords = 8,
+};
+
+struct Chunk {      // one (expert, block of <= BN tokens) work item
+  int32_t expert;      // local expert index
+  int32_t slot_base;   // first slot (multiple of 32)
+  int32_t tokens;      // valid slots in this chunk
+  int32_t reserved;
+};
+
+// ---- router.cu ----
+glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* weight, bool weight_bf16,
+                             const float* bias, float* logits, uint32_t* idx, float* scores, float* weights,
+                             size_t rows, size_t hidden_dim, size_t experts, size_t top_k, float scaling,
+                             cudaStream_t stream);
+
+// ---- quant.cu ----
+glmrt_status_t launch_quantize_rows_payload(const uint16_t* in, uint8_t* payload, size_t rows, size_t cols,
+                                            uint32_t rule, cudaStream_t stream);
+glmrt_status_t launch_tile_scales(const uint8_t* in, uint8_t* out, size_t rows, size_t kblocks,
+                                  size_t out_row_offset, cudaStream_t stream);
+glmrt_status_t launch_quantize_weight_f32(const float* in, uint8_t* packed, uint8_t* scales, float* scale_2_out,
+                                          uint32_t* amax_scratch, size_t rows, size_t cols, cudaStream_t stream);
+
+// ---- plan.cu ----
+struct PlanArgs {
+  const uint32_t* topk_indices;  // [rows * top_k] global expert ids
+  int rows, top_k, experts;      // experts = global count
+  int ep_world, ep_rank;
+  int chunk_tokens;              // BN: tokens per chunk (32 or 128)
+  int max_slots, max_chunks;
+  int32_t* route_slot;           // [rows * top_k] -> slot or -1
+  int32_t* slot_route;           // [max_slots] -> route or -1
+  int32_t* expert_counts;        // [local experts]
+  Chunk* chunks;                 // [max_chunks]
+  uint32_t* counters;            // [kCntWords]
+};
+glmrt_status_t launch_route_plan(const PlanArgs& a, cudaStream_t stream);
+
+struct DispatchArgs {
+  const uint8_t* payload;        // [rows, H/2 + H/16]
+  const int32_t* route_slot;     // [rows * top_k]
+  int rows, top_k, hidden;
+  uint8_t* act_codes;            // [max_slots, H/2]
+  uint8_t* act_sf;               // tiled scales, H/16 blocks per slot
+  uint16_t* route_rows;          // bf16 [rows * top_k, H]: destination rows of FC2
+  uint16_t** slot_out;           // [max_slots] destination row pointer per slot
+};
+glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
+
+// ---- combine.cu ----
+glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
+                                     const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
+                                     cudaStream_t stream);
+
+// ---- ffn_simt.cu (verification engine) ----
+struct FfnArgs {
+  // weights of local experts, stacked
+  const uint8_t* gate_codes; const uint8_t* up_codes; const uint8_t* down_codes;   // [E_l*I, H/2] x2, [E_l*H, I/2]
+  const uint8_t* gate_sf; const uint8_t* up_sf; const uint8_t* down_sf;            // tiled scales
+  const float* scale2;                                                                // [E_l][3]
+  const uint8_t* act1_codes; const uint8_t* act1_sf;                                   // dispatch output
+  uint8_t* act2_codes; uint8_t* act2_sf;                                               // FC1 output
+  uint16_t* const* slot_out;                                                           // FC2 destination rows
+  const Chunk* chunks; const uint32_t* counters;
+  int hidden, inter, max_chunks, chunk_tokens;
+  uint32_t* error_word;
+};
+glmrt_status_t launch_ffn_simt(const FfnArgs& a, cudaStream_t stream);
+
+// ---- gemm_tc.cu (tcgen05 engine) ----
+struct TensorMaps {
+  CUtensorMap gate, up, down;   // weight codes
+  CUtensorMap act1, act2;       // activation codes (box rows = chunk_tokens)
+};
+// Encodes a 2D uint8 tensor map [rows, row_bytes] with a {128 B, box_rows} box and 128-byte swizzle.
+glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
+                                     uint32_t box_rows);
+glmrt_status_t launch_ffn_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
+
+}  // namespace glmrt

@@ -1,0 +1,472 @@
+// Layer object: owns the NVFP4 expert weights of one sparse layer in tensor-core layout and all
+// work buffers, and sequences the kernels of one forward pass.
+//
+// It stands where the reference has RealNvfp4ProtocolV2Executor (resident expert preload:
+// rust/crates/glmrt-daemon/src/commands/expertd.rs:246-259, route.rs:2793-3054; per-request
+// execution: expert_probe/protocol_v2_executor.rs:1882-2493) plus the coordinator's router and
+// activation quantiser.  One layer object is driven by one host thread at a time.
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace glmrt {
+namespace {
+
+struct Layer {
+  glmrt_b200_moe_config_t cfg{};
+  int device = 0;
+  int sm_count = 0;
+  int local_experts = 0;
+  int max_slots = 0;
+  int max_chunks = 0;
+  std::vector<void*> allocations;
+  // weights (local experts stacked)
+  uint8_t *gate_codes = nullptr, *up_codes = nullptr, *down_codes = nullptr;
+  uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr;
+  float* scale2 = nullptr;
+  float *router_w = nullptr, *router_b = nullptr;
+  // work buffers
+  float *logits = nullptr, *topk_w = nullptr, *topk_scores = nullptr;
+  uint32_t* topk_idx = nullptr;
+  uint8_t* payload = nullptr;
+  int32_t *route_slot = nullptr, *slot_route = nullptr, *expert_counts = nullptr;
+  Chunk* chunks = nullptr;
+  uint32_t* counters = nullptr;
+  uint8_t *act1_codes = nullptr, *act1_sf = nullptr, *act2_codes = nullptr, *act2_sf = nullptr;
+  uint16_t* route_rows = nullptr;
+  uint16_t** slot_out = nullptr;
+  uint16_t *hidden_stage = nullptr, *out_stage = nullptr;
+  // scratch for weight loading
+  float* wtmp = nullptr;
+  uint8_t* sftmp = nullptr;
+  uint32_t* amax_tmp = nullptr;
+  TensorMaps maps32{}, maps128{};
+  bool have_maps = false;
+  uint32_t launches_last = 0;
+  uint32_t last_rows = 0;
+};
+
+size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+template <typename T>
+glmrt_status_t dev_alloc(Layer* l, T** out, size_t count, bool zero = false) {
+  void* p = nullptr;
+  const size_t bytes = round_up(count * sizeof(T), 256);
+  cudaError_t err = cudaMalloc(&p, bytes);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return fail_cuda(GLMRT_STATUS_ALLOCATION_FAILED, "cudaMalloc (layer buffer)", err);
+  }
+  l->allocations.push_back(p);
+  if (zero) cudaMemset(p, 0, bytes);
+  *out = static_cast<T*>(p);
+  return GLMRT_STATUS_OK;
+}
+
+void destroy(Layer* l) {
+  for (void* p : l->allocations) cudaFree(p);
+  delete l;
+}
+
+bool local_expert(const Layer* l, uint32_t e) { return e % l->cfg.ep_world == l->cfg.ep_rank; }
+
+glmrt_status_t check_buf(const glmrt_device_buffer_t& b, size_t need, const char* what) {
+  if (b.ptr == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, std::string(what) + ": null buffer");
+  if (b.bytes < need) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, std::string(what) + ": buffer too small");
+  return GLMRT_STATUS_OK;
+}
+
+// Seeded synthetic weights: N(0, std) from a counter-based generator (one Box-Muller pair per
+// two elements), so any expert can be regenerated independently of the others.
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+__global__ void synth_normal_kernel(float* out, size_t n, uint64_t stream_key, float std) {
+  const size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 2;
+  if (i >= n) return;
+  const uint64_t r = mix64(stream_key ^ mix64(i));
+  const float u1 = (static_cast<float>(static_cast<uint32_t>(r >> 40)) + 1.0f) * (1.0f / 16777216.0f);
+  const float u2 = static_cast<float>(static_cast<uint32_t>(r) >> 8) * (1.0f / 16777216.0f);
+  const float rad = sqrtf(-2.0f * logf(u1)) * std;
+  float s, c;
+  sincospif(2.0f * u2, &s, &c);
+  out[i] = rad * c;
+  if (i + 1 < n) out[i + 1] = rad * s;
+}
+
+glmrt_status_t build_maps(Layer* l) {
+  const auto& c = l->cfg;
+  const uint64_t wrows_fc1 = static_cast<uint64_t>(l->local_experts) * c.intermediate_dim;
+  const uint64_t wrows_fc2 = static_cast<uint64_t>(l->local_experts) * c.hidden_dim;
+  for (TensorMaps* m : {&l->maps32, &l->maps128}) {
+    const uint32_t box = (m == &l->maps32) ? 32 : 128;
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->gate, l->gate_codes, wrows_fc1, c.hidden_dim / 2, 128));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->up, l->up_codes, wrows_fc1, c.hidden_dim / 2, 128));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->down, l->down_codes, wrows_fc2, c.intermediate_dim / 2, 128));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act1, l->act1_codes, l->max_slots, c.hidden_dim / 2, box));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act2, l->act2_codes, l->max_slots, c.intermediate_dim / 2, box));
+  }
+  l->have_maps = true;
+  return GLMRT_STATUS_OK;
+}
+
+FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
+  FfnArgs a{};
+  a.gate_codes = l->gate_codes; a.up_codes = l->up_codes; a.down_codes = l->down_codes;
+  a.gate_sf = l->gate_sf; a.up_sf = l->up_sf; a.down_sf = l->down_sf;
+  a.scale2 = l->scale2;
+  a.act1_codes = l->act1_codes; a.act1_sf = l->act1_sf;
+  a.act2_codes = l->act2_codes; a.act2_sf = l->act2_sf;
+  a.slot_out = l->slot_out;
+  a.chunks = l->chunks; a.counters = l->counters;
+  a.hidden = static_cast<int>(l->cfg.hidden_dim); a.inter = static_cast<int>(l->cfg.intermediate_dim);
+  a.max_chunks = l->max_chunks; a.chunk_tokens = chunk_tokens;
+  a.error_word = l->counters + kCntError;
+  return a;
+}
+
+// Everything after the router: quantise, plan, dispatch, expert FFN, combine.
+glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream) {
+  const auto& c = l->cfg;
+  const int chunk_tokens = rows <= 256 ? 32 : 128;
+  cudaError_t err = cudaMemsetAsync(l->counters, 0, kCntWords * sizeof(uint32_t), stream);
+  if (err != cudaSuccess) return status_from_cuda(err, "cudaMemsetAsync(counters)");
+  GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
+                                                     GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
+  PlanArgs p{};
+  p.topk_indices = l->topk_idx;
+  p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
+  p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
+  p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
+  p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
+  p.chunks = l->chunks; p.counters = l->counters;
+  GLMRT_RETURN_IF_ERROR(launch_route_plan(p, stream));
+  DispatchArgs d{};
+  d.payload = l->payload; d.route_slot = l->route_slot;
+  d.rows = static_cast<int>(rows); d.top_k = static_cast<int>(c.top_k); d.hidden = static_cast<int>(c.hidden_dim);
+  d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
+  GLMRT_RETURN_IF_ERROR(launch_dispatch(d, stream));
+  FfnArgs f = ffn_args(l, chunk_tokens);
+  if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
+    GLMRT_RETURN_IF_ERROR(launch_ffn_simt(f, stream));
+  } else {
+    if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
+    GLMRT_RETURN_IF_ERROR(launch_ffn_tc(f, chunk_tokens == 32 ? l->maps32 : l->maps128, l->sm_count, stream));
+  }
+  // with one shard every route is local; a shard of an expert-parallel layer only sums its own
+  const int32_t* mask = c.ep_world > 1 ? l->route_slot : nullptr;
+  GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
+                                              static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream));
+  l->last_rows = static_cast<uint32_t>(rows);
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t validate_forward(Layer* l, size_t rows) {
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  if (rows == 0 || rows > l->cfg.max_tokens)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward: rows must be in 1..max_tokens");
+  return GLMRT_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace glmrt
+
+using namespace glmrt;
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer) {
+  if (config == nullptr || out_layer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: null argument");
+  *out_layer = nullptr;
+  const glmrt_b200_moe_config_t c = *config;
+  if (c.hidden_dim == 0 || c.hidden_dim % 256 != 0 || c.intermediate_dim == 0 || c.intermediate_dim % 256 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: hidden_dim and intermediate_dim must be positive multiples of 256");
+  if (c.experts == 0 || c.experts > 1024 || c.top_k == 0 || c.top_k > 16 || c.top_k > c.experts)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: experts must be 1..1024 and top_k 1..min(16, experts)");
+  if (c.max_tokens == 0 || c.max_tokens > (1u << 20))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: max_tokens must be 1..1048576");
+  if (c.ep_world == 0 || c.ep_rank >= c.ep_world || c.ep_world > c.experts)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: need 0 <= ep_rank < ep_world <= experts");
+  if (!(c.routed_scaling > 0.0f)) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: routed_scaling must be positive");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  Layer* l = new (std::nothrow) Layer();
+  if (l == nullptr) return fail(GLMRT_STATUS_ALLOCATION_FAILED, "layer create: out of host memory");
+  l->cfg = c;
+  cudaGetDevice(&l->device);
+  cudaDeviceGetAttribute(&l->sm_count, cudaDevAttrMultiProcessorCount, l->device);
+  l->local_experts = static_cast<int>((c.experts - c.ep_rank + c.ep_world - 1) / c.ep_world);
+  const size_t H = c.hidden_dim, I = c.intermediate_dim, E = l->local_experts, T = c.max_tokens, K = c.top_k;
+  const size_t routes = T * K;
+  l->max_slots = static_cast<int>(round_up(routes + E * 127, 128));
+  l->max_chunks = static_cast<int>(E + (routes + 31) / 32);
+  glmrt_status_t st = GLMRT_STATUS_OK;
+  auto A = [&](glmrt_status_t s) { if (st == GLMRT_STATUS_OK) st = s; };
+  A(dev_alloc(l, &l->gate_codes, E * I * H / 2));
+  A(dev_alloc(l, &l->up_codes, E * I * H / 2));
+  A(dev_alloc(l, &l->down_codes, E * H * I / 2));
+  A(dev_alloc(l, &l->gate_sf, E * I * H / 16));
+  A(dev_alloc(l, &l->up_sf, E * I * H / 16));
+  A(dev_alloc(l, &l->down_sf, E * H * I / 16));
+  A(dev_alloc(l, &l->scale2, E * 3, true));
+  A(dev_alloc(l, &l->router_w, static_cast<size_t>(c.experts) * H, true));
+  A(dev_alloc(l, &l->router_b, c.experts, true));
+  A(dev_alloc(l, &l->logits, T * c.experts));
+  A(dev_alloc(l, &l->topk_w, routes));
+  A(dev_alloc(l, &l->topk_scores, routes));
+  A(dev_alloc(l, &l->topk_idx, routes));
+  A(dev_alloc(l, &l->payload, T * (H / 2 + H / 16)));
+  A(dev_alloc(l, &l->route_slot, routes));
+  A(dev_alloc(l, &l->slot_route, static_cast<size_t>(l->max_slots)));
+  A(dev_alloc(l, &l->expert_counts, E));
+  A(dev_alloc(l, &l->chunks, static_cast<size_t>(l->max_chunks)));
+  A(dev_alloc(l, &l->counters, kCntWords, true));
+  // slot-ordered operands; zero-filled once so that padding slots hold finite values
+  A(dev_alloc(l, &l->act1_codes, static_cast<size_t>(l->max_slots) * H / 2, true));
+  A(dev_alloc(l, &l->act1_sf, static_cast<size_t>(l->max_slots) * H / 16, true));
+  A(dev_alloc(l, &l->act2_codes, static_cast<size_t>(l->max_slots) * I / 2, true));
+  A(dev_alloc(l, &l->act2_sf, static_cast<size_t>(l->max_slots) * I / 16, true));
+  A(dev_alloc(l, &l->route_rows, routes * H));
+  A(dev_alloc(l, &l->slot_out, static_cast<size_t>(l->max_slots)));
+  A(dev_alloc(l, &l->hidden_stage, T * H));
+  A(dev_alloc(l, &l->out_stage, T * H));
+  A(dev_alloc(l, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
+  A(dev_alloc(l, &l->sftmp, I * H / 16));
+  A(dev_alloc(l, &l->amax_tmp, 1, true));
+  if (st != GLMRT_STATUS_OK) {
+    destroy(l);
+    return st;
+  }
+  *out_layer = l;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_destroy(void* layer) {
+  if (layer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  cudaDeviceSynchronize();
+  destroy(static_cast<Layer*>(layer));
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_device_buffer_t weight_f32,
+                                                          glmrt_device_buffer_t bias_f32, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  const size_t wbytes = static_cast<size_t>(l->cfg.experts) * l->cfg.hidden_dim * 4, bbytes = l->cfg.experts * 4;
+  GLMRT_RETURN_IF_ERROR(check_buf(weight_f32, wbytes, "set_router weight"));
+  GLMRT_RETURN_IF_ERROR(check_buf(bias_f32, bbytes, "set_router bias"));
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t err = cudaMemcpyAsync(l->router_w, weight_f32.ptr, wbytes, cudaMemcpyDeviceToDevice, s);
+  if (err == cudaSuccess) err = cudaMemcpyAsync(l->router_b, bias_f32.ptr, bbytes, cudaMemcpyDeviceToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_router copy", err);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_set_expert(
+    void* layer, uint32_t expert_id, glmrt_device_buffer_t gate_codes, glmrt_device_buffer_t gate_scales,
+    glmrt_device_buffer_t up_codes, glmrt_device_buffer_t up_scales, glmrt_device_buffer_t down_codes,
+    glmrt_device_buffer_t down_scales, float gate_scale_2, float up_scale_2, float down_scale_2, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  if (expert_id >= l->cfg.experts || !local_expert(l, expert_id))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "set_expert: expert is not local to this shard");
+  if (!isfinite(gate_scale_2) || !isfinite(up_scale_2) || !isfinite(down_scale_2))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "set_expert: second-level scales must be finite");
+  const size_t H = l->cfg.hidden_dim, I = l->cfg.intermediate_dim;
+  GLMRT_RETURN_IF_ERROR(check_buf(gate_codes, I * H / 2, "set_expert gate codes"));
+  GLMRT_RETURN_IF_ERROR(check_buf(up_codes, I * H / 2, "set_expert up codes"));
+  GLMRT_RETURN_IF_ERROR(check_buf(down_codes, H * I / 2, "set_expert down codes"));
+  GLMRT_RETURN_IF_ERROR(check_buf(gate_scales, I * H / 16, "set_expert gate scales"));
+  GLMRT_RETURN_IF_ERROR(check_buf(up_scales, I * H / 16, "set_expert up scales"));
+  GLMRT_RETURN_IF_ERROR(check_buf(down_scales, H * I / 16, "set_expert down scales"));
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const size_t le = expert_id / l->cfg.ep_world;
+  cudaError_t err = cudaMemcpyAsync(l->gate_codes + le * I * H / 2, gate_codes.ptr, I * H / 2, cudaMemcpyDeviceToDevice, s);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(l->up_codes + le * I * H / 2, up_codes.ptr, I * H / 2, cudaMemcpyDeviceToDevice, s);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(l->down_codes + le * H * I / 2, down_codes.ptr, H * I / 2, cudaMemcpyDeviceToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_expert copy", err);
+  GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(gate_scales.ptr), l->gate_sf, I, H / 16, le * I, s));
+  GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(up_scales.ptr), l->up_sf, I, H / 16, le * I, s));
+  GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(down_scales.ptr), l->down_sf, H, I / 16, le * H, s));
+  const float s2[3] = {gate_scale_2, up_scale_2, down_scale_2};
+  err = cudaMemcpyAsync(l->scale2 + le * 3, s2, sizeof(s2), cudaMemcpyHostToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_expert scale copy", err);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_fill_synthetic(void* layer, uint64_t seed, float weight_std,
+                                                              void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  if (!(weight_std > 0.0f)) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "fill_synthetic: weight_std must be positive");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const size_t H = l->cfg.hidden_dim, I = l->cfg.intermediate_dim, n = I * H;
+  const unsigned blocks = static_cast<unsigned>((n / 2 + 255) / 256);
+  for (int le = 0; le < l->local_experts; ++le) {
+    const uint64_t e = static_cast<uint64_t>(le) * l->cfg.ep_world + l->cfg.ep_rank;  // global expert id
+    for (int t = 0; t < 3; ++t) {
+      const uint64_t key = seed * 0x100000001b3ull + e * 3 + t + 1;
+      synth_normal_kernel<<<blocks, 256, 0, s>>>(l->wtmp, n, key, weight_std);
+      GLMRT_LAUNCH_CHECK("synth_normal_kernel");
+      uint8_t* codes = t == 0 ? l->gate_codes : t == 1 ? l->up_codes : l->down_codes;
+      uint8_t* sf = t == 0 ? l->gate_sf : t == 1 ? l->up_sf : l->down_sf;
+      const size_t rows = t == 2 ? H : I, cols = t == 2 ? I : H;
+      GLMRT_RETURN_IF_ERROR(launch_quantize_weight_f32(l->wtmp, codes + static_cast<size_t>(le) * n / 2, l->sftmp,
+                                                       l->scale2 + le * 3 + t, l->amax_tmp, rows, cols, s));
+      GLMRT_RETURN_IF_ERROR(launch_tile_scales(l->sftmp, sf, rows, cols / 16, static_cast<size_t>(le) * rows, s));
+    }
+  }
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_async(void* layer, glmrt_device_buffer_t hidden_bf16,
+                                                             size_t rows, glmrt_device_buffer_t output_bf16,
+                                                             glmrt_device_buffer_t topk_indices,
+                                                             glmrt_device_buffer_t topk_weights, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
+  if (l->cfg.ep_world != 1)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward: this entry point needs ep_world == 1");
+  const size_t row_bytes = static_cast<size_t>(l->cfg.hidden_dim) * 2, routes = rows * l->cfg.top_k;
+  GLMRT_RETURN_IF_ERROR(check_buf(hidden_bf16, rows * row_bytes, "forward hidden"));
+  GLMRT_RETURN_IF_ERROR(check_buf(output_bf16, rows * row_bytes, "forward output"));
+  if (topk_indices.ptr != nullptr && topk_indices.bytes < routes * 4)
+    return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "forward topk_indices: buffer too small");
+  if (topk_weights.ptr != nullptr && topk_weights.bytes < routes * 4)
+    return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "forward topk_weights: buffer too small");
+  if (reinterpret_cast<uintptr_t>(hidden_bf16.ptr) % 16 != 0 || reinterpret_cast<uintptr_t>(output_bf16.ptr) % 16 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward: hidden and output must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const uint64_t before = launches_total();
+  GLMRT_RETURN_IF_ERROR(launch_router(hidden_bf16.ptr, true, l->router_w, false, l->router_b, l->logits, l->topk_idx,
+                                      l->topk_scores, l->topk_w, rows, l->cfg.hidden_dim, l->cfg.experts,
+                                      l->cfg.top_k, l->cfg.routed_scaling, s));
+  GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                   static_cast<uint16_t*>(output_bf16.ptr), s));
+  l->launches_last = static_cast<uint32_t>(launches_total() - before);
+  cudaError_t err = cudaSuccess;
+  if (topk_indices.ptr != nullptr)
+    err = cudaMemcpyAsync(topk_indices.ptr, l->topk_idx, routes * 4, cudaMemcpyDeviceToDevice, s);
+  if (err == cudaSuccess && topk_weights.ptr != nullptr)
+    err = cudaMemcpyAsync(topk_weights.ptr, l->topk_w, routes * 4, cudaMemcpyDeviceToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward route copy", err);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_routed_async(
+    void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t topk_indices,
+    glmrt_device_buffer_t topk_weights, glmrt_device_buffer_t output_bf16, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
+  const size_t row_bytes = static_cast<size_t>(l->cfg.hidden_dim) * 2, routes = rows * l->cfg.top_k;
+  GLMRT_RETURN_IF_ERROR(check_buf(hidden_bf16, rows * row_bytes, "forward_routed hidden"));
+  GLMRT_RETURN_IF_ERROR(check_buf(output_bf16, rows * row_bytes, "forward_routed output"));
+  GLMRT_RETURN_IF_ERROR(check_buf(topk_indices, routes * 4, "forward_routed topk_indices"));
+  GLMRT_RETURN_IF_ERROR(check_buf(topk_weights, routes * 4, "forward_routed topk_weights"));
+  if (reinterpret_cast<uintptr_t>(hidden_bf16.ptr) % 16 != 0 || reinterpret_cast<uintptr_t>(output_bf16.ptr) % 16 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_routed: hidden and output must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const uint64_t before = launches_total();
+  cudaError_t err = cudaMemcpyAsync(l->topk_idx, topk_indices.ptr, routes * 4, cudaMemcpyDeviceToDevice, s);
+  if (err == cudaSuccess) err = cudaMemcpyAsync(l->topk_w, topk_weights.ptr, routes * 4, cudaMemcpyDeviceToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_routed route copy", err);
+  GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                   static_cast<uint16_t*>(output_bf16.ptr), s));
+  l->launches_last = static_cast<uint32_t>(launches_total() - before);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_host(void* layer, const void* hidden_host, size_t rows,
+                                                            void* output_host, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
+  if (hidden_host == nullptr || output_host == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_host: null host pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const size_t bytes = rows * static_cast<size_t>(l->cfg.hidden_dim) * 2;
+  cudaError_t err = cudaMemcpyAsync(l->hidden_stage, hidden_host, bytes, cudaMemcpyHostToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_host input copy", err);
+  glmrt_device_buffer_t in{l->hidden_stage, bytes, l->device, 0}, out{l->out_stage, bytes, l->device, 0};
+  glmrt_device_buffer_t none{nullptr, 0, l->device, 0};
+  GLMRT_RETURN_IF_ERROR(glmrt_b200_moe_layer_forward_async(layer, in, rows, out, none, none, cuda_stream));
+  err = cudaMemcpyAsync(output_host, l->out_stage, bytes, cudaMemcpyDeviceToHost, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_host output copy", err);
+  err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_host synchronize", err);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_check(void* layer, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  uint32_t host[kCntWords] = {0};
+  cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
+  if (err == cudaSuccess) err = cudaMemcpy(host, l->counters, sizeof(host), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "layer check", err);
+  const uint32_t e = host[kCntError];
+  if (e == 0) return ok();
+  std::string msg = "device reported:";
+  if (e & kErrWaitTimeout) msg += " a bounded wait expired;";
+  if (e & kErrSlotOverflow) msg += " route plan exceeds slot capacity;";
+  if (e & kErrChunkOverflow) msg += " route plan exceeds chunk capacity;";
+  if (e & kErrBadExpert) msg += " a route names an expert id outside the layer;";
+  return fail(GLMRT_STATUS_INTERNAL_ERROR, msg);
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_debug_buffer(void* layer, uint32_t which, glmrt_device_buffer_t* out) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr || out == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "debug_buffer: null argument");
+  const auto& c = l->cfg;
+  const size_t H = c.hidden_dim, I = c.intermediate_dim, T = c.max_tokens, K = c.top_k, S = l->max_slots,
+               E = l->local_experts;
+  void* p = nullptr;
+  size_t bytes = 0;
+  switch (which) {
+    case GLMRT_B200_DEBUG_PAYLOAD: p = l->payload; bytes = T * (H / 2 + H / 16); break;
+    case GLMRT_B200_DEBUG_ROUTE_SLOT: p = l->route_slot; bytes = T * K * 4; break;
+    case GLMRT_B200_DEBUG_ACT1_CODES: p = l->act1_codes; bytes = S * H / 2; break;
+    case GLMRT_B200_DEBUG_ACT1_SF: p = l->act1_sf; bytes = S * H / 16; break;
+    case GLMRT_B200_DEBUG_ACT2_CODES: p = l->act2_codes; bytes = S * I / 2; break;
+    case GLMRT_B200_DEBUG_ACT2_SF: p = l->act2_sf; bytes = S * I / 16; break;
+    case GLMRT_B200_DEBUG_ROUTE_ROWS: p = l->route_rows; bytes = T * K * H * 2; break;
+    case GLMRT_B200_DEBUG_COUNTERS: p = l->counters; bytes = kCntWords * 4; break;
+    case GLMRT_B200_DEBUG_CHUNKS: p = l->chunks; bytes = static_cast<size_t>(l->max_chunks) * sizeof(Chunk); break;
+    case GLMRT_B200_DEBUG_EXPERT_COUNTS: p = l->expert_counts; bytes = E * 4; break;
+    case GLMRT_B200_DEBUG_GATE_CODES: p = l->gate_codes; bytes = E * I * H / 2; break;
+    case GLMRT_B200_DEBUG_UP_CODES: p = l->up_codes; bytes = E * I * H / 2; break;
+    case GLMRT_B200_DEBUG_DOWN_CODES: p = l->down_codes; bytes = E * H * I / 2; break;
+    case GLMRT_B200_DEBUG_GATE_SF: p = l->gate_sf; bytes = E * I * H / 16; break;
+    case GLMRT_B200_DEBUG_UP_SF: p = l->up_sf; bytes = E * I * H / 16; break;
+    case GLMRT_B200_DEBUG_DOWN_SF: p = l->down_sf; bytes = E * H * I / 16; break;
+    case GLMRT_B200_DEBUG_SCALE2: p = l->scale2; bytes = E * 3 * 4; break;
+    case GLMRT_B200_DEBUG_TOPK_IDX: p = l->topk_idx; bytes = T * K * 4; break;
+    case GLMRT_B200_DEBUG_TOPK_W: p = l->topk_w; bytes = T * K * 4; break;
+    default: return fail(GLMRT_STATUS_INVALID_ARGUMENT, "debug_buffer: unknown buffer id");
+  }
+  out->ptr = p;
+  out->bytes = bytes;
+  out->device_id = l->device;
+  out->flags = 0;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_layer_stats_t* out) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr || out == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer stats: null argument");
+  uint32_t host[kCntWords] = {0};
+  cudaError_t err = cudaMemcpy(host, l->counters, sizeof(host), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "layer stats", err);
+  std::memset(out, 0, sizeof(*out));
+  out->launches_total = launches_total();
+  out->launches_last_forward = l->launches_last;
+  out->chunks = host[kCntChunks];
+  out->slots = host[kCntSlots];
+  out->distinct_experts = host[kCntDistinct];
+  out->device_error = host[kCntError];
+  return ok();
+}

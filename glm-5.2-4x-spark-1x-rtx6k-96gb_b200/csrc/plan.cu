@@ -1,0 +1,127 @@
+// Route plan and dispatch.
+//
+// route plan: counting sort of the rows * top_k routes by expert on the device, replacing the
+// host-side plan_packed_w4a16_topk8_prefill_flat of the reference
+// (rust/crates/glmrt-daemon/src/commands/real_full/sparse_mlp/route.rs:3727-3828).  Each local
+// expert receives a contiguous slot range that starts on a multiple of 128 slots (the row
+// granularity of the tiled scale layout) and is cut into chunks of `chunk_tokens` slots, the
+// work items of the expert GEMM kernels.  The order of routes inside an expert is arbitrary;
+// every route's result is independent of its slot, so outputs stay bit-reproducible.
+//
+// dispatch: copies each route's NVFP4 activation payload row into its slot (codes row-major,
+// scales into the tiled layout) -- the single-GPU form of the all-to-all send.
+#include "common.cuh"
+#include "internal.h"
+
+namespace glmrt {
+namespace {
+
+constexpr int kPlanThreads = 1024;
+constexpr int kMaxLocalExperts = 1024;
+
+__global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
+  __shared__ int cnt[kMaxLocalExperts];
+  __shared__ int base[kMaxLocalExperts];
+  __shared__ int s_error;
+  const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
+  for (int i = threadIdx.x; i < local_experts; i += kPlanThreads) cnt[i] = 0;
+  if (threadIdx.x == 0) s_error = 0;
+  __syncthreads();
+  const int n = a.rows * a.top_k;
+  for (int r = threadIdx.x; r < n; r += kPlanThreads) {
+    const uint32_t e = a.topk_indices[r];
+    int pos = -1;
+    if (e >= static_cast<uint32_t>(a.experts)) {
+      atomicOr(&s_error, static_cast<int>(kErrBadExpert));
+    } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
+      pos = atomicAdd(&cnt[e / a.ep_world], 1);
+    }
+    a.route_slot[r] = pos;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int running = 0, chunks = 0, distinct = 0, routes = 0;
+    int err = s_error;
+    for (int le = 0; le < local_experts; ++le) {
+      const int c = cnt[le];
+      base[le] = running;
+      a.expert_counts[le] = c;
+      if (c == 0) continue;
+      ++distinct;
+      routes += c;
+      for (int off = 0; off < c; off += a.chunk_tokens) {
+        if (chunks < a.max_chunks) {
+          Chunk ch;
+          ch.expert = le;
+          ch.slot_base = running + off;
+          ch.tokens = min(a.chunk_tokens, c - off);
+          ch.reserved = 0;
+          a.chunks[chunks] = ch;
+        } else {
+          err |= static_cast<int>(kErrChunkOverflow);
+        }
+        ++chunks;
+      }
+      running += (c + 127) & ~127;
+    }
+    if (running > a.max_slots) err |= static_cast<int>(kErrSlotOverflow);
+    if (err != 0) chunks = 0;  // never launch expert work on an inconsistent plan
+    s_error = err;
+    a.counters[kCntChunks] = static_cast<uint32_t>(min(chunks, a.max_chunks));
+    a.counters[kCntSlots] = static_cast<uint32_t>(running);
+    a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+    a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+    if (err != 0) atomicOr(&a.counters[kCntError], static_cast<uint32_t>(err));
+  }
+  __syncthreads();
+  const bool bad = s_error != 0;
+  for (int r = threadIdx.x; r < n; r += kPlanThreads) {
+    const int pos = a.route_slot[r];
+    if (pos < 0) continue;
+    const uint32_t e = a.topk_indices[r];
+    const int slot = base[e / a.ep_world] + pos;
+    if (bad || slot >= a.max_slots) {
+      a.route_slot[r] = -1;
+    } else {
+      a.route_slot[r] = slot;
+      a.slot_route[slot] = r;
+    }
+  }
+}
+
+// One warp per route.
+__global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  const int lane = threadIdx.x % 32;
+  const int n = a.rows * a.top_k;
+  if (warp >= n) return;
+  const int slot = a.route_slot[warp];
+  if (slot < 0) return;
+  const int row = warp / a.top_k;
+  const int code_bytes = a.hidden / 2;
+  const int kblocks = a.hidden / 16;
+  const uint8_t* src = a.payload + static_cast<size_t>(row) * (code_bytes + kblocks);
+  const uint4* src4 = reinterpret_cast<const uint4*>(src);
+  uint4* dst4 = reinterpret_cast<uint4*>(a.act_codes + static_cast<size_t>(slot) * code_bytes);
+  for (int i = lane; i < code_bytes / 16; i += 32) dst4[i] = src4[i];
+  const uint8_t* ssrc = src + code_bytes;
+  for (int j = lane; j < kblocks; j += 32) a.act_sf[sf_tile_offset(slot, j, kblocks)] = ssrc[j];
+  if (lane == 0) a.slot_out[slot] = a.route_rows + static_cast<size_t>(warp) * a.hidden;
+}
+
+}  // namespace
+
+glmrt_status_t launch_route_plan(const PlanArgs& a, cudaStream_t stream) {
+  route_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);
+  GLMRT_LAUNCH_CHECK("route_plan_kernel");
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream) {
+  const int n = a.rows * a.top_k;
+  dispatch_kernel<<<(n + 7) / 8, 256, 0, stream>>>(a);
+  GLMRT_LAUNCH_CHECK("dispatch_kernel");
+  return GLMRT_STATUS_OK;
+}
+
+}  // namespace glmrt

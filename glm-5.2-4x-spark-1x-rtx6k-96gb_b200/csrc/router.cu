@@ -1,0 +1,238 @@
+// Router: logits = X W^T (float32 accumulate), sigmoid, + per-expert bias for selection,
+// top-k with ties to the lower expert id, weights = raw score / max(sum, 1e-12) * scaling.
+//
+// Replaces native/cuda/kernels/router.cu:7-180 (one serial thread per row, or one CTA per
+// (expert,row) dot product plus a global spin lock per row) with a tiled logits kernel and
+// a one-warp-per-row selection kernel; there are no locks and no atomics, so the result is
+// bit-reproducible.  Semantics follow python/reference/glmrt_reference/
+// glm_moe_dsa_layer_ref.py:62-83 and, for non-finite scores, router.cu:112-116.
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace glmrt {
+namespace {
+
+constexpr int kTM = 64;    // rows per CTA
+constexpr int kTN = 4;     // experts per CTA
+constexpr int kKC = 128;   // K chunk staged in shared memory
+constexpr size_t kMaxRouterTopK = 64;  // native/cuda/kernels/common.h:18
+
+template <typename T>
+__device__ __forceinline__ float load_as_f32(const T* p, size_t i);
+template <>
+__device__ __forceinline__ float load_as_f32<float>(const float* p, size_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float load_as_f32<uint16_t>(const uint16_t* p, size_t i) {
+  return bf16_bits_to_f32(p[i]);
+}
+
+// logits[row, expert] = sum_k x[row, k] * w[expert, k], float32 FMA in ascending k.
+template <typename XT, typename WT>
+__global__ void __launch_bounds__(kTM * kTN)
+router_logits_kernel(const XT* __restrict__ x, const WT* __restrict__ w, float* __restrict__ logits,
+                     int rows, int hidden, int experts) {
+  __shared__ float xs[kKC][kTM + 1];
+  __shared__ float ws[kTN][kKC];
+  const int tm = threadIdx.x % kTM;
+  const int tn = threadIdx.x / kTM;
+  const int row0 = blockIdx.x * kTM;
+  const int exp0 = blockIdx.y * kTN;
+  float acc = 0.0f;
+  for (int k0 = 0; k0 < hidden; k0 += kKC) {
+    const int kc = min(kKC, hidden - k0);
+    // stage X: coalesced along k
+    for (int i = threadIdx.x; i < kTM * kKC; i += kTM * kTN) {
+      const int r = i / kKC, k = i % kKC;
+      float v = 0.0f;
+      if (row0 + r < rows && k < kc) v = load_as_f32<XT>(x, static_cast<size_t>(row0 + r) * hidden + k0 + k);
+      xs[k][r] = v;
+    }
+    for (int i = threadIdx.x; i < kTN * kKC; i += kTM * kTN) {
+      const int e = i / kKC, k = i % kKC;
+      float v = 0.0f;
+      if (exp0 + e < experts && k < kc) v = load_as_f32<WT>(w, static_cast<size_t>(exp0 + e) * hidden + k0 + k);
+      ws[e][k] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < kKC; ++k) acc = fmaf(xs[k][tm], ws[tn][k], acc);
+    __syncthreads();
+  }
+  if (row0 + tm < rows && exp0 + tn < experts)
+    logits[static_cast<size_t>(row0 + tm) * experts + exp0 + tn] = acc;
+}
+
+// One warp per row.  Shared memory: per warp `experts` selection scores.
+__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                     uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
+                                     float* __restrict__ topk_weights, int rows, int experts, int top_k,
+                                     float scaling) {
+  extern __shared__ float smem[];
+  const int warps = blockDim.x / 32;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int row = blockIdx.x * warps + warp;
+  if (row >= rows) return;
+  float* sel = smem + static_cast<size_t>(warp) * 2 * experts;
+  float* raw = sel + experts;
+  for (int e = lane; e < experts; e += 32) {
+    const float s = sigmoid_f32(logits[static_cast<size_t>(row) * experts + e]);
+    const bool fin = isfinite(s);
+    const float score = fin ? s : 0.0f;
+    const float corrected = score + bias[e];
+    raw[e] = score;
+    sel[e] = (fin && isfinite(corrected)) ? corrected : -CUDART_INF_F;
+  }
+  __syncwarp();
+  float sum = 0.0f;
+  float my_score = 0.0f;   // lane j keeps the score of rank j (top_k <= 64: two per lane)
+  float my_score2 = 0.0f;
+  uint32_t my_idx = 0, my_idx2 = 0;
+  for (int rank = 0; rank < top_k; ++rank) {
+    float best = -CUDART_INF_F;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = sel[e];
+      if (v > best) { best = v; best_e = e; }   // ascending e: first maximum wins inside a lane
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    float score = 0.0f;
+    uint32_t idx = 0;
+    if (best_e != 0x7fffffff) {  // a finite candidate exists
+      score = raw[best_e];
+      idx = static_cast<uint32_t>(best_e);
+      if (lane == 0) sel[best_e] = -CUDART_INF_F;  // -inf entries are never picked (best starts at -inf)
+    }
+    __syncwarp();
+    sum += score;  // sequential float32 sum in rank order (router.cu:52-56)
+    if (rank == lane) { my_score = score; my_idx = idx; }
+    if (rank == lane + 32) { my_score2 = score; my_idx2 = idx; }
+  }
+  sum = fmaxf(sum, 1.0e-12f);
+  const size_t out = static_cast<size_t>(row) * top_k;
+  if (lane < top_k) {
+    topk_indices[out + lane] = my_idx;
+    if (topk_scores != nullptr) topk_scores[out + lane] = my_score;
+    topk_weights[out + lane] = my_score / sum * scaling;
+  }
+  if (lane + 32 < top_k) {
+    topk_indices[out + lane + 32] = my_idx2;
+    if (topk_scores != nullptr) topk_scores[out + lane + 32] = my_score2;
+    topk_weights[out + lane + 32] = my_score2 / sum * scaling;
+  }
+}
+
+glmrt_status_t validate(const void* hidden, const void* weight, const float* bias, const uint32_t* idx,
+                        const float* weights, size_t rows, size_t hidden_dim, size_t experts, size_t top_k) {
+  if (hidden == nullptr || weight == nullptr || bias == nullptr || idx == nullptr || weights == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: null pointer argument");
+  if (rows == 0 || hidden_dim == 0 || experts == 0 || top_k == 0 || top_k > experts || top_k > kMaxRouterTopK)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: rows, hidden_dim, experts must be > 0 and 0 < top_k <= min(experts, 64)");
+  size_t ignored = 0;
+  if (!checked_mul(rows, hidden_dim, &ignored) || !checked_mul(experts, hidden_dim, &ignored) ||
+      !checked_mul(rows, experts, &ignored) || rows > static_cast<size_t>(std::numeric_limits<int>::max()) ||
+      experts > 1024 || hidden_dim > static_cast<size_t>(std::numeric_limits<int>::max()))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: dimensions out of range");
+  return GLMRT_STATUS_OK;
+}
+
+}  // namespace
+
+glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* weight, bool weight_bf16,
+                             const float* bias, float* logits, uint32_t* idx, float* scores, float* weights,
+                             size_t rows, size_t hidden_dim, size_t experts, size_t top_k, float scaling,
+                             cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>((rows + kTM - 1) / kTM), static_cast<unsigned>((experts + kTN - 1) / kTN));
+  const int r = static_cast<int>(rows), h = static_cast<int>(hidden_dim), e = static_cast<int>(experts);
+  if (hidden_bf16 && weight_bf16)
+    router_logits_kernel<uint16_t, uint16_t><<<grid, kTM * kTN, 0, stream>>>(
+        static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e);
+  else if (hidden_bf16)
+    router_logits_kernel<uint16_t, float><<<grid, kTM * kTN, 0, stream>>>(
+        static_cast<const uint16_t*>(hidden), static_cast<const float*>(weight), logits, r, h, e);
+  else if (!weight_bf16)
+    router_logits_kernel<float, float><<<grid, kTM * kTN, 0, stream>>>(
+        static_cast<const float*>(hidden), static_cast<const float*>(weight), logits, r, h, e);
+  else
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: float32 hidden with bf16 weights is not supported");
+  GLMRT_LAUNCH_CHECK("router_logits_kernel");
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * 2 * experts * sizeof(float);
+  router_select_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, smem, stream>>>(
+      logits, bias, idx, scores, weights, r, e, static_cast<int>(top_k), scaling);
+  GLMRT_LAUNCH_CHECK("router_select_kernel");
+  return GLMRT_STATUS_OK;
+}
+
+namespace {
+// Entry points without a scratch argument take the logits buffer from the stream-ordered pool.
+glmrt_status_t router_with_pool(const void* hidden, bool hidden_bf16, const void* weight, bool weight_bf16,
+                                const float* bias, uint32_t* idx, float* scores, float* weights, size_t rows,
+                                size_t hidden_dim, size_t experts, size_t top_k, cudaStream_t stream) {
+  GLMRT_RETURN_IF_ERROR(validate(hidden, weight, bias, idx, weights, rows, hidden_dim, experts, top_k));
+  if (scores == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: null pointer argument");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  float* logits = nullptr;
+  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&logits), rows * experts * sizeof(float), stream);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_ALLOCATION_FAILED, "cudaMallocAsync", err);
+  glmrt_status_t st = launch_router(hidden, hidden_bf16, weight, weight_bf16, bias, logits, idx, scores, weights,
+                                    rows, hidden_dim, experts, top_k, 2.5f, stream);
+  cudaFreeAsync(logits, stream);
+  return st == GLMRT_STATUS_OK ? ok() : st;
+}
+}  // namespace
+}  // namespace glmrt
+
+using namespace glmrt;
+
+extern "C" glmrt_status_t glmrt_cuda_router_topk_f32_async(
+    const float* hidden, const float* router_weight, const float* correction_bias, uint32_t* topk_indices,
+    float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim, size_t experts, size_t top_k,
+    void* cuda_stream) {
+  return router_with_pool(hidden, false, router_weight, false, correction_bias, topk_indices, topk_scores,
+                          topk_weights, rows, hidden_dim, experts, top_k, static_cast<cudaStream_t>(cuda_stream));
+}
+extern "C" glmrt_status_t glmrt_cuda_router_topk_f32(const float* hidden, const float* router_weight,
+                                                     const float* correction_bias, uint32_t* topk_indices,
+                                                     float* topk_scores, float* topk_weights, size_t rows,
+                                                     size_t hidden_dim, size_t experts, size_t top_k) {
+  GLMRT_RETURN_IF_ERROR(glmrt_cuda_router_topk_f32_async(hidden, router_weight, correction_bias, topk_indices,
+                                                         topk_scores, topk_weights, rows, hidden_dim, experts,
+                                                         top_k, nullptr));
+  return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+}
+extern "C" glmrt_status_t glmrt_cuda_router_topk_bf16_async(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias, uint32_t* topk_indices,
+    float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim, size_t experts, size_t top_k,
+    void* cuda_stream) {
+  return router_with_pool(hidden, true, router_weight, true, correction_bias, topk_indices, topk_scores,
+                          topk_weights, rows, hidden_dim, experts, top_k, static_cast<cudaStream_t>(cuda_stream));
+}
+extern "C" glmrt_status_t glmrt_cuda_router_topk_bf16(const uint16_t* hidden, const uint16_t* router_weight,
+                                                      const float* correction_bias, uint32_t* topk_indices,
+                                                      float* topk_scores, float* topk_weights, size_t rows,
+                                                      size_t hidden_dim, size_t experts, size_t top_k) {
+  GLMRT_RETURN_IF_ERROR(glmrt_cuda_router_topk_bf16_async(hidden, router_weight, correction_bias, topk_indices,
+                                                          topk_scores, topk_weights, rows, hidden_dim, experts,
+                                                          top_k, nullptr));
+  return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+}
+extern "C" glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
+    const uint16_t* hidden, const float* router_weight, const float* correction_bias, float* logits_scratch,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim,
+    size_t experts, size_t top_k, void* cuda_stream) {
+  GLMRT_RETURN_IF_ERROR(validate(hidden, router_weight, correction_bias, topk_indices, topk_weights, rows,
+                                 hidden_dim, experts, top_k));
+  if (logits_scratch == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: logits scratch is null");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, router_weight, false, correction_bias, logits_scratch,
+                                      topk_indices, topk_scores, topk_weights, rows, hidden_dim, experts, top_k,
+                                      2.5f, static_cast<cudaStream_t>(cuda_stream)));
+  return ok();
+}

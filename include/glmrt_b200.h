@@ -1,0 +1,291 @@
+/*
+ * C ABI of libglmrt_b200.so: the routed-MoE expert FFN path of GLMRT, written for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The library is a drop-in for the hot-path subset of the reference's
+ * libglmrt_native.so (reference header: native/include/glmrt_native.h).  Symbols
+ * that keep a reference name keep the reference signature and error behaviour;
+ * each declaration cites the reference declaration it replaces.  Entry points
+ * named glmrt_b200_* are additions for what the reference's fixed-shape structs
+ * cannot express (full-intermediate experts, fp32 router weights, expert-parallel
+ * shards) and say so.
+ *
+ * Conventions (reference: native/include/glmrt_native.h:10-20,77-82,427;
+ * native/src/glmrt_native.cc:30-49):
+ *   - every function returns glmrt_status_t; on failure a thread-local message
+ *     is readable with glmrt_last_error();
+ *   - glmrt_device_buffer_t is passed by value, owned by the caller, never freed
+ *     by the callee, and its `bytes` is validated before anything is launched;
+ *   - *_async functions only enqueue work on `cuda_stream` (a cudaStream_t, NULL
+ *     for the default stream); the twin without _async runs on the default
+ *     stream and synchronises it;
+ *   - no exception crosses the ABI; all validation happens before any launch;
+ *   - there is no CPU fallback: without a CUDA device compute entry points
+ *     return GLMRT_STATUS_CUDA_UNAVAILABLE.
+ */
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* native/include/glmrt_native.h:10-20 */
+typedef enum glmrt_status_t {
+  GLMRT_STATUS_OK = 0,
+  GLMRT_STATUS_INVALID_ARGUMENT = 1,
+  GLMRT_STATUS_BUFFER_TOO_SMALL = 2,
+  GLMRT_STATUS_CUDA_UNAVAILABLE = 3,
+  GLMRT_STATUS_ALLOCATION_FAILED = 4,
+  GLMRT_STATUS_COPY_FAILED = 5,
+  GLMRT_STATUS_INTERNAL_ERROR = 6,
+  GLMRT_STATUS_RDMA_UNAVAILABLE = 7,
+  GLMRT_STATUS_NCCL_UNAVAILABLE = 8,
+} glmrt_status_t;
+
+/* native/include/glmrt_native.h:62-74 */
+typedef struct glmrt_cuda_device_info_t {
+  int device_id;
+  int cuda_available;
+  int compute_capability_major;
+  int compute_capability_minor;
+  int integrated;
+  int can_map_host_memory;
+  int unified_addressing;
+  uint64_t total_memory_bytes;
+  char name[128];
+  char driver_version[64];
+  char runtime_version[64];
+} glmrt_cuda_device_info_t;
+
+/* native/include/glmrt_native.h:77-82 */
+typedef struct glmrt_device_buffer_t {
+  void* ptr;
+  size_t bytes;
+  int device_id;
+  uint64_t flags;
+} glmrt_device_buffer_t;
+
+/* ------------------------------------------------------------------------ */
+/* Infrastructure (native/include/glmrt_native.h:296-313,415-427)             */
+/* ------------------------------------------------------------------------ */
+glmrt_status_t glmrt_native_version(char* out, size_t out_len);
+glmrt_status_t glmrt_last_error(char* out, size_t out_len);
+glmrt_status_t glmrt_cuda_device_info(int device_id, glmrt_cuda_device_info_t* out);
+glmrt_status_t glmrt_alloc_device_buffer(size_t bytes, glmrt_device_buffer_t* out);
+glmrt_status_t glmrt_free_device_buffer(glmrt_device_buffer_t* buf);
+glmrt_status_t glmrt_cuda_stream_create(void** out_cuda_stream);
+glmrt_status_t glmrt_cuda_stream_destroy(void* cuda_stream);
+glmrt_status_t glmrt_cuda_stream_synchronize(void* cuda_stream);
+glmrt_status_t glmrt_cuda_event_create(void** out_cuda_event);
+glmrt_status_t glmrt_cuda_event_destroy(void* cuda_event);
+glmrt_status_t glmrt_cuda_event_record(void* cuda_event, void* cuda_stream);
+glmrt_status_t glmrt_cuda_event_synchronize(void* cuda_event);
+glmrt_status_t glmrt_cuda_event_elapsed_ms(void* start_event, void* end_event, float* out_ms);
+glmrt_status_t glmrt_copy_h2d(glmrt_device_buffer_t dst, const void* src, size_t bytes);
+glmrt_status_t glmrt_copy_d2h(void* dst, glmrt_device_buffer_t src, size_t bytes);
+glmrt_status_t glmrt_copy_d2d(glmrt_device_buffer_t dst, glmrt_device_buffer_t src, size_t bytes);
+glmrt_status_t glmrt_copy_h2d_async(glmrt_device_buffer_t dst, const void* src, size_t bytes,
+                                    void* cuda_stream);
+glmrt_status_t glmrt_copy_d2h_async(void* dst, glmrt_device_buffer_t src, size_t bytes,
+                                    void* cuda_stream);
+glmrt_status_t glmrt_copy_d2d_async(glmrt_device_buffer_t dst, glmrt_device_buffer_t src,
+                                    size_t bytes, void* cuda_stream);
+
+/* ------------------------------------------------------------------------ */
+/* Router (native/include/glmrt_native.h:1002-1018; kernels router.cu:7-180)  */
+/* sigmoid(X W^T), selection = score + bias, top-k by selection (ties to the  */
+/* lower expert id), weights = score / max(sum, 1e-12) * 2.5.                 */
+/* rows, hidden_dim, experts > 0; 0 < top_k <= min(experts, 64).              */
+/* ------------------------------------------------------------------------ */
+glmrt_status_t glmrt_cuda_router_topk_f32(const float* hidden, const float* router_weight,
+                                          const float* correction_bias, uint32_t* topk_indices,
+                                          float* topk_scores, float* topk_weights, size_t rows,
+                                          size_t hidden_dim, size_t experts, size_t top_k);
+glmrt_status_t glmrt_cuda_router_topk_f32_async(
+    const float* hidden, const float* router_weight, const float* correction_bias,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows,
+    size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
+glmrt_status_t glmrt_cuda_router_topk_bf16(const uint16_t* hidden,
+                                           const uint16_t* router_weight,
+                                           const float* correction_bias, uint32_t* topk_indices,
+                                           float* topk_scores, float* topk_weights, size_t rows,
+                                           size_t hidden_dim, size_t experts, size_t top_k);
+glmrt_status_t glmrt_cuda_router_topk_bf16_async(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows,
+    size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
+/* Addition: bf16 activations against float32 router weights, the operand types of
+ * the Python oracle (python/reference/glmrt_reference/glm_moe_dsa_layer_ref.py:62-83).
+ * `logits_scratch` holds rows * experts floats. */
+glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
+    const uint16_t* hidden, const float* router_weight, const float* correction_bias,
+    float* logits_scratch, uint32_t* topk_indices, float* topk_scores, float* topk_weights,
+    size_t rows, size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
+
+/* ------------------------------------------------------------------------ */
+/* NVFP4 codecs                                                               */
+/* ------------------------------------------------------------------------ */
+/* native/include/glmrt_native.h:610-612 (kernel nvfp4_payload.cu:35-73): bf16 rows ->
+ * row payload [hidden_dim/2 packed codes | hidden_dim/16 E4M3 scales], round-to-
+ * nearest-even code thresholds on x * (1/scale).  hidden_dim % 16 == 0. */
+glmrt_status_t glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async(
+    glmrt_device_buffer_t input, glmrt_device_buffer_t payload, size_t rows, size_t hidden_dim,
+    void* cuda_stream);
+/* Addition: same payload layout with a selectable code rule. */
+typedef enum glmrt_b200_fp4_rule_t {
+  GLMRT_B200_FP4_RULE_RNE_PAYLOAD = 0, /* nvfp4_payload.cu:11-33,56-66 */
+  GLMRT_B200_FP4_RULE_NEAREST_LOW = 1, /* quant_ref.py:41-46: x / scale, ties to lower magnitude */
+} glmrt_b200_fp4_rule_t;
+glmrt_status_t glmrt_b200_quantize_bf16_nvfp4_row_payload_async(
+    glmrt_device_buffer_t input, glmrt_device_buffer_t payload, size_t rows, size_t hidden_dim,
+    uint32_t rule, void* cuda_stream);
+/* native/include/glmrt_native.h:627-630 (kernel mlp.cu:98-132): bf16 weights ->
+ * packed codes + E4M3 block scales with a multiplicative global scale. */
+glmrt_status_t glmrt_cuda_quantize_bf16_weight_nvfp4_async(
+    glmrt_device_buffer_t input, glmrt_device_buffer_t packed, glmrt_device_buffer_t scales,
+    size_t rows, size_t cols, float global_scale, void* cuda_stream);
+/* Addition: float32 weights -> NVFP4 with scale_2 = amax / (6 * 448) (the benchmark's
+ * weight recipe).  `scale_2_out` receives one float; `scratch` holds one uint32. */
+glmrt_status_t glmrt_b200_quantize_f32_weight_nvfp4_async(
+    glmrt_device_buffer_t input, glmrt_device_buffer_t packed, glmrt_device_buffer_t scales,
+    glmrt_device_buffer_t scale_2_out, glmrt_device_buffer_t scratch, size_t rows, size_t cols,
+    void* cuda_stream);
+/* native/include/glmrt_native.h:631-634 (kernel b12x_direct.cu:269-290): gather payload
+ * rows and expand them to bf16 (code * E4M3 scale, truncating bf16 store). */
+glmrt_status_t glmrt_cuda_b12x_gather_nvfp4_rows_bf16_async(
+    glmrt_device_buffer_t payload, size_t source_rows, size_t source_row_stride_bytes,
+    glmrt_device_buffer_t row_indices, glmrt_device_buffer_t output, size_t rows,
+    size_t hidden_dim, void* cuda_stream);
+
+/* ------------------------------------------------------------------------ */
+/* Combine (native/include/glmrt_native.h:679-681,843-846)                    */
+/* ------------------------------------------------------------------------ */
+/* b12x_direct.cu:203-219: fixed-order float32 sum of the 8 per-route bf16 rows of width
+ * 6144 per token, truncated to bf16.  routed_bf16 is [rows * 8, 6144]. */
+glmrt_status_t glmrt_cuda_b12x_spark_sum_topk8_bf16_async(
+    glmrt_device_buffer_t routed_bf16, glmrt_device_buffer_t output_bf16, size_t rows,
+    void* cuda_stream);
+/* residual.cu:666-678: dst[row_indices[r]] += row_weights[r] * src[r] (atomic). */
+glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32(
+    const uint16_t* src, const uint32_t* row_indices, const float* row_weights, float* dst,
+    size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32_async(
+    const uint16_t* src, const uint32_t* row_indices, const float* row_weights, float* dst,
+    size_t rows, size_t row_width, void* cuda_stream);
+/* residual.cu:133-158 */
+glmrt_status_t glmrt_cuda_gather_rows_bf16_async(const uint16_t* src, const uint32_t* row_indices,
+                                                 uint16_t* dst, size_t rows, size_t row_width,
+                                                 void* cuda_stream);
+
+/* ------------------------------------------------------------------------ */
+/* Layer-level entry points (additions).                                      */
+/*                                                                            */
+/* A layer object owns the NVFP4 weights of its local experts in tensor-core   */
+/* layout plus all work buffers for up to max_tokens rows.  It replaces, for   */
+/* one sparse layer, what the reference does in                                */
+/* RealNvfp4ProtocolV2Executor::execute_protocol_v2_unordered                  */
+/* (rust/crates/glmrt-daemon/src/commands/real_full/expert_probe/              */
+/* protocol_v2_executor.rs:1882-2493) plus the coordinator-side router and     */
+/* activation quantiser (sparse_mlp/router.rs:184-219,                         */
+/* coordinator_kernels/activation.rs:34-92).                                   */
+/* ------------------------------------------------------------------------ */
+typedef struct glmrt_b200_moe_config_t {
+  uint32_t hidden_dim;        /* H, multiple of 256 */
+  uint32_t intermediate_dim;  /* I, multiple of 256 */
+  uint32_t experts;           /* routed experts in the whole layer, <= 1024 */
+  uint32_t top_k;             /* 1..16 */
+  uint32_t max_tokens;        /* capacity in rows per forward call */
+  uint32_t ep_world;          /* expert-parallel world size (1 = all experts local) */
+  uint32_t ep_rank;           /* expert e is local iff e % ep_world == ep_rank
+                                 (rust/crates/glmrt-core/src/placement.rs:25-42) */
+  uint32_t flags;             /* GLMRT_B200_LAYER_* */
+  float routed_scaling;       /* 2.5 for GLM-5.2 */
+} glmrt_b200_moe_config_t;
+
+enum {
+  GLMRT_B200_LAYER_ENGINE_SIMT = 1u, /* run the expert FFN on the SIMT verification kernels */
+};
+
+glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer);
+glmrt_status_t glmrt_b200_moe_layer_destroy(void* layer);
+/* float32 router weight [experts, hidden_dim] and bias [experts] (device memory). */
+glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_device_buffer_t weight_f32,
+                                               glmrt_device_buffer_t bias_f32, void* cuda_stream);
+/* One expert's projections in the reference's tensor layout (route.rs:6732-6757):
+ * gate/up codes [I, H/2], scales [I, H/16]; down codes [H, I/2], scales [H, I/16];
+ * value = code * e4m3(scale) * scale_2.  Non-local experts are rejected. */
+glmrt_status_t glmrt_b200_moe_layer_set_expert(
+    void* layer, uint32_t expert_id, glmrt_device_buffer_t gate_codes,
+    glmrt_device_buffer_t gate_scales, glmrt_device_buffer_t up_codes,
+    glmrt_device_buffer_t up_scales, glmrt_device_buffer_t down_codes,
+    glmrt_device_buffer_t down_scales, float gate_scale_2, float up_scale_2, float down_scale_2,
+    void* cuda_stream);
+/* Seeded synthetic expert weights generated and quantised on the device (benchmarks). */
+glmrt_status_t glmrt_b200_moe_layer_fill_synthetic(void* layer, uint64_t seed, float weight_std,
+                                                   void* cuda_stream);
+
+/* One forward pass: router -> quantise -> plan/dispatch -> FC1+SwiGLU+requant -> FC2 ->
+ * combine.  hidden_bf16 and output_bf16 are [rows, hidden_dim] bf16 in device memory.
+ * topk_indices / topk_weights ([rows, top_k] uint32 / float) are optional (ptr may be
+ * NULL).  ep_world must be 1 for this entry point. */
+glmrt_status_t glmrt_b200_moe_layer_forward_async(
+    void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t output_bf16,
+    glmrt_device_buffer_t topk_indices, glmrt_device_buffer_t topk_weights, void* cuda_stream);
+/* Same with host buffers: copies the rows in from `hidden_host`, runs the layer, copies the
+ * result out to `output_host` and synchronises the stream.  Host memory may be pageable;
+ * pinned memory makes the copies asynchronous. */
+glmrt_status_t glmrt_b200_moe_layer_forward_host(void* layer, const void* hidden_host, size_t rows,
+                                                 void* output_host, void* cuda_stream);
+/* Routed forward with caller-supplied routes (the expert worker's view of a request:
+ * rows + (expert, weight) routes; protocol_v2.rs:236-310).  Skips the router. */
+glmrt_status_t glmrt_b200_moe_layer_forward_routed_async(
+    void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t topk_indices,
+    glmrt_device_buffer_t topk_weights, glmrt_device_buffer_t output_bf16, void* cuda_stream);
+
+/* Device-side error word of the last forward (0 = none): bounded waits that gave up and
+ * capacity overflows are reported here instead of hanging or faulting.  Synchronises. */
+glmrt_status_t glmrt_b200_moe_layer_check(void* layer, void* cuda_stream);
+
+/* Introspection for tests and profiling. */
+typedef enum glmrt_b200_debug_buffer_t {
+  GLMRT_B200_DEBUG_PAYLOAD = 0,      /* [rows, H/2 + H/16] activation payload */
+  GLMRT_B200_DEBUG_ROUTE_SLOT = 1,   /* int32 [rows * top_k] slot of each route (-1 = not local) */
+  GLMRT_B200_DEBUG_ACT1_CODES = 2,   /* [slots, H/2] expert-sorted activation codes */
+  GLMRT_B200_DEBUG_ACT1_SF = 3,      /* tiled scales of ACT1 */
+  GLMRT_B200_DEBUG_ACT2_CODES = 4,   /* [slots, I/2] requantised SwiGLU output */
+  GLMRT_B200_DEBUG_ACT2_SF = 5,
+  GLMRT_B200_DEBUG_ROUTE_ROWS = 6,   /* bf16 [rows * top_k, H] per-route FC2 output */
+  GLMRT_B200_DEBUG_COUNTERS = 7,     /* uint32 [8]: chunks, slots, error, ... */
+  GLMRT_B200_DEBUG_CHUNKS = 8,       /* int32 [chunks][4]: expert, slot_base, tokens, 0 */
+  GLMRT_B200_DEBUG_EXPERT_COUNTS = 9, /* int32 [local experts] routes per expert */
+  GLMRT_B200_DEBUG_GATE_CODES = 10,   /* [local experts * I, H/2] */
+  GLMRT_B200_DEBUG_UP_CODES = 11,
+  GLMRT_B200_DEBUG_DOWN_CODES = 12,   /* [local experts * H, I/2] */
+  GLMRT_B200_DEBUG_GATE_SF = 13,      /* tiled scales */
+  GLMRT_B200_DEBUG_UP_SF = 14,
+  GLMRT_B200_DEBUG_DOWN_SF = 15,
+  GLMRT_B200_DEBUG_SCALE2 = 16,       /* float [local experts][3] = gate, up, down */
+  GLMRT_B200_DEBUG_TOPK_IDX = 17,     /* uint32 [rows * top_k] */
+  GLMRT_B200_DEBUG_TOPK_W = 18        /* float [rows * top_k] */
+} glmrt_b200_debug_buffer_t;
+glmrt_status_t glmrt_b200_moe_layer_debug_buffer(void* layer, uint32_t which,
+                                                 glmrt_device_buffer_t* out);
+/* Statistics of the last forward (after a stream synchronise): kernels launched by this
+ * library, distinct experts touched, slots used. */
+typedef struct glmrt_b200_layer_stats_t {
+  uint64_t launches_total;
+  uint32_t launches_last_forward;
+  uint32_t chunks;
+  uint32_t slots;
+  uint32_t distinct_experts;
+  uint32_t device_error;
+  uint32_t reserved;
+} glmrt_b200_layer_stats_t;
+glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_layer_stats_t* out);
+
+#ifdef __cplusplus
+}
+#endif

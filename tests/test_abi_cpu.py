@@ -1,0 +1,93 @@
+"""C-ABI checks that need no GPU: the library loads, exports every declared symbol, and
+validates arguments / reports CUDA_UNAVAILABLE without launching anything.
+
+Modelled on the reference's native CPU self-test (native/tests/native_selftest.cc:10-112:
+version string, error propagation through glmrt_last_error, clean *_UNAVAILABLE statuses).
+"""
+import ctypes as C
+import os
+
+import pytest
+import torch
+
+HAS_GPU = torch.cuda.is_available()
+
+
+@pytest.fixture(scope="module")
+def lib(pkg):
+    from glmrt_b200 import native as N
+    path = N.DEFAULT_LIB
+    if not os.path.exists(path):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_b", os.path.join(N.HERE, "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    return N.NativeLibrary(path)
+
+
+def test_every_declared_symbol_is_exported(lib, pkg):
+    from glmrt_b200 import native as N
+    names = N.declared_symbols()
+    assert len(names) >= 40
+    missing = [n for n in names if not hasattr(lib.lib, n)]
+    assert missing == []
+
+
+def test_version_and_last_error(lib):
+    assert "glmrt-b200" in lib.version()
+    small = C.create_string_buffer(4)
+    assert lib.call_status("glmrt_native_version", small, C.c_size_t(4)) == 2  # BUFFER_TOO_SMALL
+    assert lib.call_status("glmrt_native_version", None, C.c_size_t(4)) == 1
+    assert "null" in lib.last_error()
+
+
+def test_invalid_arguments_are_rejected_before_any_launch(lib, pkg):
+    from glmrt_b200 import native as N
+    null = N.DeviceBuffer.null()
+    # router: null pointers, zero rows, top_k > experts (router.cu:259-281 rules)
+    assert lib.call_status("glmrt_cuda_router_topk_bf16_async", None, None, None, None, None, None,
+                           C.c_size_t(1), C.c_size_t(16), C.c_size_t(4), C.c_size_t(2), None) == 1
+    one = C.c_void_p(16)
+    assert lib.call_status("glmrt_cuda_router_topk_f32_async", one, one, one, one, one, one,
+                           C.c_size_t(0), C.c_size_t(16), C.c_size_t(4), C.c_size_t(2), None) == 1
+    assert lib.call_status("glmrt_cuda_router_topk_f32_async", one, one, one, one, one, one,
+                           C.c_size_t(1), C.c_size_t(16), C.c_size_t(4), C.c_size_t(5), None) == 1
+    # payload quantiser: hidden_dim not a multiple of 16, too-small buffers
+    buf = N.DeviceBuffer.of(4096, 64)
+    assert lib.call_status("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", buf, buf,
+                           C.c_size_t(1), C.c_size_t(24), None) == 1
+    assert lib.call_status("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", buf, buf,
+                           C.c_size_t(8), C.c_size_t(64), None) == 2
+    assert "too small" in lib.last_error()
+    assert lib.call_status("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", null, buf,
+                           C.c_size_t(1), C.c_size_t(16), None) == 1
+    # layer create: bad shapes
+    out = C.c_void_p()
+    for cfg in (N.MoeConfig(100, 256, 16, 4, 8, 1, 0, 0, 2.5), N.MoeConfig(256, 256, 16, 32, 8, 1, 0, 0, 2.5),
+                N.MoeConfig(256, 256, 16, 4, 0, 1, 0, 0, 2.5), N.MoeConfig(256, 256, 16, 4, 8, 2, 2, 0, 2.5)):
+        assert lib.call_status("glmrt_b200_moe_layer_create", C.byref(cfg), C.byref(out)) == 1
+    assert lib.call_status("glmrt_b200_moe_layer_destroy", None) == 1
+    assert lib.call_status("glmrt_cuda_event_elapsed_ms", None, None, None) == 1
+
+
+@pytest.mark.skipif(HAS_GPU, reason="checks the no-device behaviour")
+def test_without_a_device_compute_calls_report_cuda_unavailable(lib, pkg):
+    from glmrt_b200 import native as N
+    b = N.DeviceBuffer()
+    assert lib.call_status("glmrt_alloc_device_buffer", C.c_size_t(1024), C.byref(b)) == 3
+    assert "CUDA" in lib.last_error()
+    out = C.c_void_p()
+    cfg = N.MoeConfig(256, 256, 16, 4, 8, 1, 0, 0, 2.5)
+    assert lib.call_status("glmrt_b200_moe_layer_create", C.byref(cfg), C.byref(out)) == 3
+    info = N.DeviceInfo()
+    assert lib.call_status("glmrt_cuda_device_info", C.c_int(0), C.byref(info)) == 3
+    buf = N.DeviceBuffer.of(4096, 1 << 20)
+    assert lib.call_status("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", buf, buf,
+                           C.c_size_t(1), C.c_size_t(64), None) == 3
+
+
+def test_missing_library_fails_loudly(pkg):
+    from glmrt_b200 import native as N
+    with pytest.raises(FileNotFoundError):
+        N.NativeLibrary("/nonexistent/libglmrt_b200.so")

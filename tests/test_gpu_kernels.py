@@ -1,0 +1,277 @@
+"""GPU parity tests of the stand-alone kernels behind the reference-named C-ABI symbols:
+router, NVFP4 codecs, combine.  Each compares the CUDA result with the CPU oracle on the
+same seeded inputs (bit-exact for codes, indices and bf16 words), the pattern of the
+reference's native/tests/cuda_selftest.cc.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import glmrt_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib(pkg):
+    from glmrt_b200 import native as N
+    return N.library()
+
+
+def dbuf(t):
+    from glmrt_b200 import native as N
+    return N.DeviceBuffer.of(t.data_ptr(), t.numel() * t.element_size(), 0)
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def bf16_tensor(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).cuda()
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+# ---------------------------------------------------------------------------------- router
+@pytest.mark.parametrize("T,H,E,K", [(1, 256, 16, 4), (33, 256, 16, 4), (16, 6144, 256, 8), (200, 512, 64, 8)])
+def test_router_bf16_f32w_matches_oracle(lib, T, H, E, K):
+    rng = np.random.default_rng(T * 7 + E)
+    rw = (rng.standard_normal((E, H), np.float32) * np.float32(0.02)).astype(np.float32)
+    bias = (rng.standard_normal(E, np.float32) * np.float32(0.01)).astype(np.float32)
+    hid = O.make_hidden(T + 5, T, H)
+    x = bf16_tensor(hid)
+    w = torch.from_numpy(rw).cuda()
+    b = torch.from_numpy(bias).cuda()
+    logits = torch.empty(T * E, dtype=torch.float32, device="cuda")
+    idx = torch.empty((T, K), dtype=torch.int32, device="cuda")
+    sc = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    wt = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    lib.call("glmrt_b200_router_topk_bf16_f32w_async", ptr(x), ptr(w), ptr(b), ptr(logits), ptr(idx), ptr(sc),
+             ptr(wt), C.c_size_t(T), C.c_size_t(H), C.c_size_t(E), C.c_size_t(K), stream())
+    torch.cuda.synchronize()
+    oi, ow, oscores, osel = O.router_topk(O.bf16_to_f32(hid), rw, bias, K)
+    sel64 = (1.0 / (1.0 + np.exp(-(O.bf16_to_f32(hid).astype(np.float64) @ rw.astype(np.float64).T)))) + bias
+    gi = idx.cpu().numpy()
+    assert O.router_indices_equivalent(gi, oi, sel64, tol=1e-6)
+    same = np.all(gi == oi.astype(np.int32), axis=1)
+    assert same.mean() > 0.9
+    np.testing.assert_allclose(wt.cpu().numpy()[same], ow[same], atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(wt.cpu().numpy().sum(axis=1), 2.5, atol=1e-5)
+    raw = np.take_along_axis(oscores, oi.astype(np.int64), axis=1)
+    np.testing.assert_allclose(sc.cpu().numpy()[same], raw[same], atol=2e-6)
+
+
+def test_router_reference_named_entry_points_and_golden(lib, golden_dir):
+    # generated-layer golden of python/reference/tests/test_glm_moe_dsa_layer_ref.py:67-96
+    g = np.load(os.path.join(golden_dir, "router.npz"))
+    E, H, K = 256, 6144, 8
+    rw = np.zeros((E, H), np.float32)
+    for e in range(E):
+        rw[e, e % H] = np.float32(0.03125 + e / 8192.0)
+        rw[e, (e * 17 + 13) % H] = np.float32(-0.015625)
+    bias = np.linspace(-0.125, 0.125, E, dtype=np.float64).astype(np.float32)
+    x = torch.from_numpy(g["gen_normalized"]).cuda()
+    w = torch.from_numpy(rw).cuda()
+    b = torch.from_numpy(bias).cuda()
+    idx = torch.empty((2, K), dtype=torch.int32, device="cuda")
+    sc = torch.empty((2, K), dtype=torch.float32, device="cuda")
+    wt = torch.empty((2, K), dtype=torch.float32, device="cuda")
+    lib.call("glmrt_cuda_router_topk_f32", ptr(x), ptr(w), ptr(b), ptr(idx), ptr(sc), ptr(wt), C.c_size_t(2),
+             C.c_size_t(H), C.c_size_t(E), C.c_size_t(K))
+    assert idx.cpu().numpy().tolist() == [[255, 254, 253, 252, 251, 250, 249, 248]] * 2
+    np.testing.assert_allclose(wt.cpu().numpy(), g["gen_w"], atol=1e-6)
+    # bf16 x bf16 variant against the oracle with bf16-rounded weights
+    rng = np.random.default_rng(5)
+    hid = O.make_hidden(77, 9, 512)
+    rwb = O.bf16_round((rng.standard_normal((32, 512), np.float32) * np.float32(0.05)).astype(np.float32))
+    bias = (rng.standard_normal(32, np.float32) * np.float32(0.01)).astype(np.float32)
+    idx = torch.empty((9, 4), dtype=torch.int32, device="cuda")
+    sc = torch.empty((9, 4), dtype=torch.float32, device="cuda")
+    wt = torch.empty((9, 4), dtype=torch.float32, device="cuda")
+    xb, wb, bb = bf16_tensor(hid), bf16_tensor(rwb), torch.from_numpy(bias).cuda()
+    lib.call("glmrt_cuda_router_topk_bf16", ptr(xb), ptr(wb), ptr(bb), ptr(idx), ptr(sc), ptr(wt), C.c_size_t(9),
+             C.c_size_t(512), C.c_size_t(32), C.c_size_t(4))
+    oi, ow, _, _ = O.router_topk(O.bf16_to_f32(hid), O.bf16_to_f32(rwb), bias, 4)
+    np.testing.assert_array_equal(idx.cpu().numpy(), oi.astype(np.int32))
+    np.testing.assert_allclose(wt.cpu().numpy(), ow, atol=2e-6)
+
+
+def test_router_ties_go_to_lower_expert_and_nonfinite_scores_are_skipped(lib):
+    H, E, K = 256, 8, 3
+    x = np.zeros((2, H), np.float32)
+    x[:, 0] = 1.0
+    rw = np.zeros((E, H), np.float32)
+    rw[:, 0] = [0.5, 1.0, 1.0, 0.25, 1.0, -1.0, 0.0, 0.0]   # experts 1, 2, 4 tie
+    bias = np.zeros(E, np.float32)
+    bias[7] = np.inf                                         # non-finite corrected score: never selected
+    xt = bf16_tensor(O.bf16_round(x))
+    logits = torch.empty(2 * E, dtype=torch.float32, device="cuda")
+    idx = torch.empty((2, K), dtype=torch.int32, device="cuda")
+    sc = torch.empty((2, K), dtype=torch.float32, device="cuda")
+    wt = torch.empty((2, K), dtype=torch.float32, device="cuda")
+    w, b = torch.from_numpy(rw).cuda(), torch.from_numpy(bias).cuda()
+    lib.call("glmrt_b200_router_topk_bf16_f32w_async", ptr(xt), ptr(w), ptr(b), ptr(logits), ptr(idx), ptr(sc),
+             ptr(wt), C.c_size_t(2), C.c_size_t(H), C.c_size_t(E), C.c_size_t(K), stream())
+    torch.cuda.synchronize()
+    assert idx.cpu().numpy().tolist() == [[1, 2, 4], [1, 2, 4]]
+    oi, _, _, _ = O.router_topk(x, rw, bias, K)
+    assert oi.tolist() == [[1, 2, 4], [1, 2, 4]]
+
+
+# ---------------------------------------------------------------------------------- codecs
+@pytest.mark.parametrize("rule,name", [(0, "rne_payload"), (1, "nearest_low")])
+@pytest.mark.parametrize("T,H", [(1, 6144), (37, 6144), (5, 48), (64, 256)])
+def test_payload_quantiser_bit_exact(lib, rule, name, T, H):
+    rng = np.random.default_rng(T * 31 + H)
+    x = rng.standard_normal((T, H), np.float32)
+    x[0, :16] = 0.0                                  # zero block -> zero scale
+    if H >= 48:
+        x[0, 16:32] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0]
+        x[0, 32:48] *= 1e-4                          # sub-normal E4M3 scale range
+    bits = O.bf16_round(x)
+    xin = bf16_tensor(bits)
+    out = torch.zeros(T * (H // 2 + H // 16), dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_b200_quantize_bf16_nvfp4_row_payload_async", dbuf(xin), dbuf(out), C.c_size_t(T),
+             C.c_size_t(H), C.c_uint32(rule), stream())
+    torch.cuda.synchronize()
+    codes, sb = O.quantize_rows_nvfp4(O.bf16_to_f32(bits), name)
+    np.testing.assert_array_equal(out.cpu().numpy().reshape(T, -1), O.payload_rows(codes, sb))
+    if rule == 0:  # the reference-named symbol is the RNE rule
+        out2 = torch.zeros_like(out)
+        lib.call("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", dbuf(xin), dbuf(out2), C.c_size_t(T),
+                 C.c_size_t(H), stream())
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+
+
+def test_payload_quantiser_many_values_including_every_tie(lib):
+    # >= 10^7 values: every bf16 bit pattern with a finite value appears, scaled copies of the ties too
+    allb = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    fin = allb[np.isfinite(O.bf16_to_f32(allb))]
+    rng = np.random.default_rng(0)
+    bits = np.concatenate([fin, O.bf16_round(rng.standard_normal(10_400_000 - fin.size, np.float32) * 3)])
+    bits = bits[: bits.size // 6144 * 6144].reshape(-1, 6144)
+    xin = bf16_tensor(bits)
+    T = bits.shape[0]
+    out = torch.zeros(T * 3456, dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_b200_quantize_bf16_nvfp4_row_payload_async", dbuf(xin), dbuf(out), C.c_size_t(T),
+             C.c_size_t(6144), C.c_uint32(1), stream())
+    torch.cuda.synchronize()
+    codes, sb = O.quantize_rows_nvfp4(O.bf16_to_f32(bits), "nearest_low")
+    np.testing.assert_array_equal(out.cpu().numpy().reshape(T, -1), O.payload_rows(codes, sb))
+
+
+def test_weight_quantiser_known_answer_and_random(lib):
+    # native/tests/cuda_selftest.cc:2736-2765
+    vals = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], np.float32)
+    xin = bf16_tensor(O.bf16_truncate(vals).reshape(1, 16))
+    packed = torch.zeros(8, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(1, dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_cuda_quantize_bf16_weight_nvfp4_async", dbuf(xin), dbuf(packed), dbuf(scales), C.c_size_t(1),
+             C.c_size_t(16), C.c_float(448.0), stream())
+    torch.cuda.synchronize()
+    assert packed.cpu().numpy().tolist() == [0x10, 0x32, 0x54, 0x76, 0x98, 0xBA, 0xDC, 0xFE]
+    assert scales.cpu().numpy().tolist() == [0x7E]
+    rng = np.random.default_rng(9)
+    wb = O.bf16_round(rng.standard_normal((64, 256), np.float32) * np.float32(0.02))
+    xin = bf16_tensor(wb)
+    packed = torch.zeros(64 * 128, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(64 * 16, dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_cuda_quantize_bf16_weight_nvfp4_async", dbuf(xin), dbuf(packed), dbuf(scales), C.c_size_t(64),
+             C.c_size_t(256), C.c_float(3000.0), stream())
+    torch.cuda.synchronize()
+    codes, sb = O.quantize_weight_bf16_multiplicative(wb, 3000.0)
+    np.testing.assert_array_equal(scales.cpu().numpy().reshape(64, 16), sb)
+    np.testing.assert_array_equal(packed.cpu().numpy(), O.pack_nibbles(codes))
+
+
+def test_f32_weight_quantiser_matches_oracle_recipe(lib):
+    rng = np.random.default_rng(4)
+    w = (rng.standard_normal((256, 512), np.float32) * np.float32(0.02)).astype(np.float32)
+    w[3, :16] = 0.0
+    win = torch.from_numpy(w).cuda()
+    packed = torch.zeros(256 * 256, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(256 * 32, dtype=torch.uint8, device="cuda")
+    s2 = torch.zeros(1, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.call("glmrt_b200_quantize_f32_weight_nvfp4_async", dbuf(win), dbuf(packed), dbuf(scales), dbuf(s2),
+             dbuf(scratch), C.c_size_t(256), C.c_size_t(512), stream())
+    torch.cuda.synchronize()
+    codes, sb, g = O.quantize_weight_baseline(w)
+    assert float(s2.cpu()[0]) == float(g)
+    np.testing.assert_array_equal(scales.cpu().numpy().reshape(256, 32), sb)
+    np.testing.assert_array_equal(packed.cpu().numpy(), O.pack_nibbles(codes))
+
+
+def test_gather_payload_rows_to_bf16(lib):
+    rng = np.random.default_rng(2)
+    x = O.bf16_to_f32(O.bf16_round(rng.standard_normal((6, 64), np.float32)))
+    codes, sb = O.quantize_rows_nvfp4(x, "rne_payload")
+    pay = O.payload_rows(codes, sb)
+    rows = np.array([5, 0, 3, 3], np.uint32)
+    p = torch.from_numpy(pay).cuda()
+    ri = torch.from_numpy(rows.view(np.int32)).cuda()
+    out = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    lib.call("glmrt_cuda_b12x_gather_nvfp4_rows_bf16_async", dbuf(p), C.c_size_t(6), C.c_size_t(36), dbuf(ri),
+             dbuf(out), C.c_size_t(4), C.c_size_t(64), stream())
+    torch.cuda.synchronize()
+    want = O.bf16_truncate(O.dequantize_payload_rows(pay, 64)[rows.astype(np.int64)])
+    np.testing.assert_array_equal(out.cpu().view(torch.int16).numpy().view(np.uint16), want)
+
+
+# ---------------------------------------------------------------------------------- combine
+def test_sum_topk8_and_weighted_scatter_and_gather(lib):
+    rng = np.random.default_rng(8)
+    y = O.bf16_round(rng.standard_normal((3, 8, 6144), np.float32))
+    yt = bf16_tensor(y.reshape(24, 6144))
+    out = torch.zeros((3, 6144), dtype=torch.bfloat16, device="cuda")
+    lib.call("glmrt_cuda_b12x_spark_sum_topk8_bf16_async", dbuf(yt), dbuf(out), C.c_size_t(3), stream())
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.cpu().view(torch.int16).numpy().view(np.uint16), O.sum_topk_bf16(y))
+    # weighted scatter-add: distinct destination rows -> deterministic
+    src = O.bf16_round(rng.standard_normal((4, 96), np.float32))
+    ri = np.array([2, 0, 3, 1], np.uint32)
+    w = rng.random(4, np.float32)
+    dst0 = rng.standard_normal((4, 96), np.float32)
+    dst = torch.from_numpy(dst0.copy()).cuda()
+    st, rt, wt = bf16_tensor(src), torch.from_numpy(ri.view(np.int32)).cuda(), torch.from_numpy(w).cuda()
+    lib.call("glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32", ptr(st), ptr(rt), ptr(wt), ptr(dst), C.c_size_t(4),
+             C.c_size_t(96))
+    want = O.scatter_add_rows_bf16_weighted_to_f32(src, ri, w, dst0)
+    np.testing.assert_allclose(dst.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+    g = torch.zeros((4, 96), dtype=torch.bfloat16, device="cuda")
+    lib.call("glmrt_cuda_gather_rows_bf16_async", ptr(st), ptr(rt), ptr(g), C.c_size_t(4), C.c_size_t(96), stream())
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(g.cpu().view(torch.int16).numpy().view(np.uint16), src[ri.astype(np.int64)])
+
+
+def test_infra_alloc_copy_events(lib, pkg):
+    from glmrt_b200 import native as N
+    b = N.DeviceBuffer()
+    lib.call("glmrt_alloc_device_buffer", C.c_size_t(4096), C.byref(b))
+    host = np.arange(1024, dtype=np.int32)
+    lib.call("glmrt_copy_h2d", b, C.c_void_p(host.ctypes.data), C.c_size_t(4096))
+    back = np.zeros_like(host)
+    lib.call("glmrt_copy_d2h", C.c_void_p(back.ctypes.data), b, C.c_size_t(4096))
+    np.testing.assert_array_equal(host, back)
+    assert lib.call_status("glmrt_copy_h2d", b, C.c_void_p(host.ctypes.data), C.c_size_t(8192)) == 2
+    ev0, ev1, ms = C.c_void_p(), C.c_void_p(), C.c_float()
+    lib.call("glmrt_cuda_event_create", C.byref(ev0))
+    lib.call("glmrt_cuda_event_create", C.byref(ev1))
+    lib.call("glmrt_cuda_event_record", ev0, None)
+    lib.call("glmrt_cuda_event_record", ev1, None)
+    lib.call("glmrt_cuda_event_synchronize", ev1)
+    lib.call("glmrt_cuda_event_elapsed_ms", ev0, ev1, C.byref(ms))
+    assert ms.value >= 0
+    lib.call("glmrt_cuda_event_destroy", ev0)
+    lib.call("glmrt_cuda_event_destroy", ev1)
+    lib.call("glmrt_free_device_buffer", C.byref(b))
+    info = N.DeviceInfo()
+    lib.call("glmrt_cuda_device_info", C.c_int(0), C.byref(info))
+    assert info.cuda_available == 1 and info.compute_capability_major == 10
