@@ -76,8 +76,10 @@ __device__ __forceinline__ uint32_t f32_to_e4m3_satfinite(float v) {
 }
 
 __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
-  // 0, .5, 1, 1.5, 2, 3, 4, 6 with the sign in bit 3
+  // 0, .5, 1, 1.5, 2, 3, 4, 6 with the sign in bit 3; code 8 is +0 as in the reference's
+  // codebook (native/cuda/kernels/common.h:32-38)
   const uint32_t m = code & 7u;
+  if (m == 0u) return 0.0f;
   const float mag = m < 2 ? 0.5f * static_cast<float>(m)
                           : __uint_as_float((((m >> 1) + 126u) << 23) | ((m & 1u) << 22));
   return (code & 8u) ? -mag : mag;

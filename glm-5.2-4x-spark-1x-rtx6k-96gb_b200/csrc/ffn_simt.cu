@@ -80,9 +80,13 @@ __global__ void __launch_bounds__(128) simt_fc2_kernel(FfnArgs a) {
 
 }  // namespace
 
-glmrt_status_t launch_ffn_simt(const FfnArgs& a, cudaStream_t stream) {
+glmrt_status_t launch_fc1_simt(const FfnArgs& a, cudaStream_t stream) {
   simt_fc1_kernel<<<dim3(a.max_chunks, a.inter / 128), 128, 0, stream>>>(a);
   GLMRT_LAUNCH_CHECK("simt_fc1_kernel");
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream) {
   simt_fc2_kernel<<<dim3(a.max_chunks, a.hidden / 128), 128, 0, stream>>>(a);
   GLMRT_LAUNCH_CHECK("simt_fc2_kernel");
   return GLMRT_STATUS_OK;

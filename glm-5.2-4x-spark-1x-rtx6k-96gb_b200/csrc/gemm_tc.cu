@@ -180,7 +180,9 @@ struct Cfg {
   static constexpr int kTmemCols = kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128
                                    : kColsUsed <= 256 ? 256 : 512;
   static constexpr uint32_t kTxBytes = kStageBytes;
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kChunkCache = 256;  // work items of this CTA's first tiles, staged in shared memory
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
+                                       kChunkCache * sizeof(Chunk);
 };
 
 template <bool kFC1, int kBN>
@@ -198,6 +200,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  Chunk* chunk_cache = reinterpret_cast<Chunk*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -229,6 +232,16 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
 
   const int num_chunks = static_cast<int>(a.counters[kCntChunks]);
   const int num_tiles = num_chunks * feat_tiles;
+  // The work items of this CTA's tiles are fetched once, up front: a global load at the head of
+  // every tile would stall each role for a memory round trip and drain the TMA pipeline.
+  for (int i = threadIdx.x; i < C::kChunkCache; i += kThreadsTC) {
+    const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
+    if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
+  }
+  __syncthreads();
+  auto chunk_of = [&](int it, int tile) -> Chunk {
+    return it < C::kChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
+  };
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -241,8 +254,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const Chunk ch = a.chunks[tile / feat_tiles];
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
+        const Chunk ch = chunk_of(it, tile);
         const int ft = tile % feat_tiles;
         const int w_row = ch.expert * out_rows + ft * kTileRows;
         const size_t sfa_tile0 = static_cast<size_t>(w_row / 128) * k_tiles64;
@@ -281,8 +295,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       bool alive = true;
       const uint32_t t_sfa0 = tmem_base + C::kSfCol;
       const uint32_t t_sfb = t_sfa0 + 16 * C::kNumA;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-        const Chunk ch = a.chunks[tile / feat_tiles];
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
+        const Chunk ch = chunk_of(it, tile);
         const uint32_t n_mma = static_cast<uint32_t>(max(16, (ch.tokens + 15) & ~15));
         const uint32_t idesc = idesc_nvf4(n_mma);
         const uint32_t sfb_q = static_cast<uint32_t>((ch.slot_base & 127) >> 5);  // 32-row quadrant inside the scale tile
@@ -330,10 +345,17 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
     int abuf = 0;
     uint32_t aphase = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-      const Chunk ch = a.chunks[tile / feat_tiles];
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
+      const Chunk ch = chunk_of(it, tile);
       const int ft = tile % feat_tiles;
       const int feature = ft * kTileRows + quad * 32 + lane;   // output row of this lane inside the expert
+      // everything the epilogue needs from global memory is fetched before the accumulators are
+      // awaited, so these latencies overlap the tile's main loop
+      const float s2a = a.scale2[ch.expert * 3 + (kFC1 ? 0 : 2)];
+      const float s2b = kFC1 ? a.scale2[ch.expert * 3 + 1] : 0.0f;
+      uint16_t* dst_lane = nullptr;   // FC2: lane j holds the destination row of token column j (of the current 32)
+      if (!kFC1 && lane < ch.tokens) dst_lane = a.slot_out[ch.slot_base + lane];
       // lane 0 waits (bounded) and the warp takes one common decision, so that the full-mask
       // shuffles of the epilogue can never run with part of the warp gone
       uint32_t ready = lane == 0 ? (mbar_wait(&acc_full[abuf], aphase, abort_flag) ? 1u : 0u) : 0u;
@@ -343,7 +365,6 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       tc_fence_after();
       const uint32_t t_acc = tmem_base + lane_base + abuf * C::kAccCols;
       if (kFC1) {
-        const float sg2 = a.scale2[ch.expert * 3 + 0], su2 = a.scale2[ch.expert * 3 + 1];
         for (int c0 = 0; c0 < ch.tokens; c0 += 8) {
           uint32_t g[8], u[8];
           tc_load8(t_acc + c0, g);
@@ -352,23 +373,24 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < ch.tokens)  // uniform across the warp
-              swiglu_requant_store(__fmul_rn(__uint_as_float(g[j]), sg2), __fmul_rn(__uint_as_float(u[j]), su2),
+              swiglu_requant_store(__fmul_rn(__uint_as_float(g[j]), s2a), __fmul_rn(__uint_as_float(u[j]), s2b),
                                    feature, static_cast<size_t>(ch.slot_base) + c0 + j, a.inter, a.act2_codes,
                                    a.act2_sf);
           }
         }
       } else {
-        const float sd2 = a.scale2[ch.expert * 3 + 2];
         for (int c0 = 0; c0 < ch.tokens; c0 += 8) {
+          if (c0 != 0 && (c0 & 31) == 0)
+            dst_lane = (c0 + lane < ch.tokens) ? a.slot_out[ch.slot_base + c0 + lane] : nullptr;
           uint32_t y[8];
           tc_load8(t_acc + c0, y);
           tc_wait_ld();
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            if (c0 + j < ch.tokens) {
-              uint16_t* dst = a.slot_out[ch.slot_base + c0 + j];
-              dst[feature] = f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[j]), sd2));
-            }
+            const unsigned long long p =
+                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_lane), (c0 + j) & 31);
+            if (c0 + j < ch.tokens)
+              reinterpret_cast<uint16_t*>(p)[feature] = f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[j]), s2a));
           }
         }
       }
@@ -442,17 +464,16 @@ glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_
   return GLMRT_STATUS_OK;
 }
 
-glmrt_status_t launch_ffn_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  if (a.chunk_tokens == 32) {
-    GLMRT_RETURN_IF_ERROR((launch_one<true, 32>(a, m.gate, m.up, m.act1, sm_count, stream)));
-    GLMRT_RETURN_IF_ERROR((launch_one<false, 32>(a, m.down, m.down, m.act2, sm_count, stream)));
-  } else if (a.chunk_tokens == 128) {
-    GLMRT_RETURN_IF_ERROR((launch_one<true, 128>(a, m.gate, m.up, m.act1, sm_count, stream)));
-    GLMRT_RETURN_IF_ERROR((launch_one<false, 128>(a, m.down, m.down, m.act2, sm_count, stream)));
-  } else {
-    return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
-  }
-  return GLMRT_STATUS_OK;
+glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
+  if (a.chunk_tokens == 32) return launch_one<true, 32>(a, m.gate, m.up, m.act1, sm_count, stream);
+  if (a.chunk_tokens == 128) return launch_one<true, 128>(a, m.gate, m.up, m.act1, sm_count, stream);
+  return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
+}
+
+glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
+  if (a.chunk_tokens == 32) return launch_one<false, 32>(a, m.down, m.down, m.act2, sm_count, stream);
+  if (a.chunk_tokens == 128) return launch_one<false, 128>(a, m.down, m.down, m.act2, sm_count, stream);
+  return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
 }
 
 }  // namespace glmrt

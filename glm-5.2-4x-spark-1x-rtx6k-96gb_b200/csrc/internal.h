@@ -92,7 +92,8 @@ struct FfnArgs {
   int hidden, inter, max_chunks, chunk_tokens;
   uint32_t* error_word;
 };
-glmrt_status_t launch_ffn_simt(const FfnArgs& a, cudaStream_t stream);
+glmrt_status_t launch_fc1_simt(const FfnArgs& a, cudaStream_t stream);
+glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);
 
 // ---- gemm_tc.cu (tcgen05 engine) ----
 struct TensorMaps {
@@ -102,6 +103,7 @@ struct TensorMaps {
 // Encodes a 2D uint8 tensor map [rows, row_bytes] with a {128 B, box_rows} box and 128-byte swizzle.
 glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
                                      uint32_t box_rows);
-glmrt_status_t launch_ffn_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
+glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
+glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 
 }  // namespace glmrt

@@ -47,7 +47,15 @@ struct Layer {
   bool have_maps = false;
   uint32_t launches_last = 0;
   uint32_t last_rows = 0;
+  // optional per-stage timing of the last forward (events recorded on the caller's stream)
+  bool profiling = false;
+  cudaEvent_t stage_events[GLMRT_B200_STAGE_COUNT + 1] = {};
+  bool stage_valid = false;
 };
+
+void mark(Layer* l, int stage_begin, cudaStream_t s) {
+  if (l->profiling) cudaEventRecord(l->stage_events[stage_begin], s);
+}
 
 size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
 
@@ -67,6 +75,8 @@ glmrt_status_t dev_alloc(Layer* l, T** out, size_t count, bool zero = false) {
 }
 
 void destroy(Layer* l) {
+  for (cudaEvent_t e : l->stage_events)
+    if (e != nullptr) cudaEventDestroy(e);
   for (void* p : l->allocations) cudaFree(p);
   delete l;
 }
@@ -135,10 +145,10 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
 glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream) {
   const auto& c = l->cfg;
   const int chunk_tokens = rows <= 256 ? 32 : 128;
-  cudaError_t err = cudaMemsetAsync(l->counters, 0, kCntWords * sizeof(uint32_t), stream);
-  if (err != cudaSuccess) return status_from_cuda(err, "cudaMemsetAsync(counters)");
+  mark(l, GLMRT_B200_STAGE_QUANTIZE, stream);
   GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
                                                      GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
+  mark(l, GLMRT_B200_STAGE_PLAN, stream);
   PlanArgs p{};
   p.topk_indices = l->topk_idx;
   p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
@@ -147,22 +157,32 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
   p.chunks = l->chunks; p.counters = l->counters;
   GLMRT_RETURN_IF_ERROR(launch_route_plan(p, stream));
+  mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
   DispatchArgs d{};
   d.payload = l->payload; d.route_slot = l->route_slot;
   d.rows = static_cast<int>(rows); d.top_k = static_cast<int>(c.top_k); d.hidden = static_cast<int>(c.hidden_dim);
   d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
   GLMRT_RETURN_IF_ERROR(launch_dispatch(d, stream));
   FfnArgs f = ffn_args(l, chunk_tokens);
+  mark(l, GLMRT_B200_STAGE_FC1, stream);
   if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
-    GLMRT_RETURN_IF_ERROR(launch_ffn_simt(f, stream));
+    GLMRT_RETURN_IF_ERROR(launch_fc1_simt(f, stream));
+    mark(l, GLMRT_B200_STAGE_FC2, stream);
+    GLMRT_RETURN_IF_ERROR(launch_fc2_simt(f, stream));
   } else {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
-    GLMRT_RETURN_IF_ERROR(launch_ffn_tc(f, chunk_tokens == 32 ? l->maps32 : l->maps128, l->sm_count, stream));
+    const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
+    GLMRT_RETURN_IF_ERROR(launch_fc1_tc(f, maps, l->sm_count, stream));
+    mark(l, GLMRT_B200_STAGE_FC2, stream);
+    GLMRT_RETURN_IF_ERROR(launch_fc2_tc(f, maps, l->sm_count, stream));
   }
+  mark(l, GLMRT_B200_STAGE_COMBINE, stream);
   // with one shard every route is local; a shard of an expert-parallel layer only sums its own
   const int32_t* mask = c.ep_world > 1 ? l->route_slot : nullptr;
   GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
                                               static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream));
+  mark(l, GLMRT_B200_STAGE_COUNT, stream);
+  l->stage_valid = l->profiling;
   l->last_rows = static_cast<uint32_t>(rows);
   return GLMRT_STATUS_OK;
 }
@@ -343,6 +363,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_async(void* layer, glmrt_
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward: hidden and output must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
   const uint64_t before = launches_total();
+  mark(l, GLMRT_B200_STAGE_ROUTER, s);
   GLMRT_RETURN_IF_ERROR(launch_router(hidden_bf16.ptr, true, l->router_w, false, l->router_b, l->logits, l->topk_idx,
                                       l->topk_scores, l->topk_w, rows, l->cfg.hidden_dim, l->cfg.experts,
                                       l->cfg.top_k, l->cfg.routed_scaling, s));
@@ -372,6 +393,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_routed_async(
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_routed: hidden and output must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
   const uint64_t before = launches_total();
+  mark(l, GLMRT_B200_STAGE_ROUTER, s);
   cudaError_t err = cudaMemcpyAsync(l->topk_idx, topk_indices.ptr, routes * 4, cudaMemcpyDeviceToDevice, s);
   if (err == cudaSuccess) err = cudaMemcpyAsync(l->topk_w, topk_weights.ptr, routes * 4, cudaMemcpyDeviceToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_routed route copy", err);
@@ -468,5 +490,31 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_lay
   out->slots = host[kCntSlots];
   out->distinct_experts = host[kCntDistinct];
   out->device_error = host[kCntError];
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_set_profiling(void* layer, int enable) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  if (enable != 0 && l->stage_events[0] == nullptr) {
+    for (cudaEvent_t& e : l->stage_events) {
+      cudaError_t err = cudaEventCreate(&e);
+      if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaEventCreate", err);
+    }
+  }
+  l->profiling = enable != 0;
+  l->stage_valid = false;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_stage_times(void* layer, float* out_ms, size_t count) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr || out_ms == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "stage_times: null argument");
+  if (count < GLMRT_B200_STAGE_COUNT) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "stage_times: need GLMRT_B200_STAGE_COUNT floats");
+  if (!l->stage_valid) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "stage_times: no profiled forward has run");
+  cudaError_t err = cudaEventSynchronize(l->stage_events[GLMRT_B200_STAGE_COUNT]);
+  for (int i = 0; i < GLMRT_B200_STAGE_COUNT && err == cudaSuccess; ++i)
+    err = cudaEventElapsedTime(&out_ms[i], l->stage_events[i], l->stage_events[i + 1]);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "stage_times", err);
   return ok();
 }

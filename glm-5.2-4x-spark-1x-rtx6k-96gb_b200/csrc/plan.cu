@@ -39,39 +39,63 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
     a.route_slot[r] = pos;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int running = 0, chunks = 0, distinct = 0, routes = 0;
-    int err = s_error;
-    for (int le = 0; le < local_experts; ++le) {
+  if (threadIdx.x < 32) {
+    // warp 0: each lane owns a contiguous run of experts; exclusive scan of slots and chunks
+    const int lane = threadIdx.x;
+    const int per_lane = (local_experts + 31) / 32;
+    const int le0 = lane * per_lane, le1 = min(local_experts, le0 + per_lane);
+    int slots = 0, chunks = 0, distinct = 0, routes = 0;
+    for (int le = le0; le < le1; ++le) {
       const int c = cnt[le];
-      base[le] = running;
-      a.expert_counts[le] = c;
-      if (c == 0) continue;
-      ++distinct;
+      slots += (c + 127) & ~127;
+      chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
+      distinct += c != 0;
       routes += c;
-      for (int off = 0; off < c; off += a.chunk_tokens) {
-        if (chunks < a.max_chunks) {
+    }
+    int slot_off = slots, chunk_off = chunks;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int s = __shfl_up_sync(0xffffffffu, slot_off, d);
+      const int c = __shfl_up_sync(0xffffffffu, chunk_off, d);
+      if (lane >= d) { slot_off += s; chunk_off += c; }
+    }
+    const int total_slots = __shfl_sync(0xffffffffu, slot_off, 31);
+    const int total_chunks = __shfl_sync(0xffffffffu, chunk_off, 31);
+    slot_off -= slots;    // inclusive -> exclusive
+    chunk_off -= chunks;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      distinct += __shfl_xor_sync(0xffffffffu, distinct, d);
+      routes += __shfl_xor_sync(0xffffffffu, routes, d);
+    }
+    int err = s_error;
+    if (total_slots > a.max_slots) err |= static_cast<int>(kErrSlotOverflow);
+    if (total_chunks > a.max_chunks) err |= static_cast<int>(kErrChunkOverflow);
+    for (int le = le0; le < le1; ++le) {
+      const int c = cnt[le];
+      base[le] = slot_off;
+      a.expert_counts[le] = c;
+      if (err == 0) {
+        for (int off = 0; off < c; off += a.chunk_tokens) {
           Chunk ch;
           ch.expert = le;
-          ch.slot_base = running + off;
+          ch.slot_base = slot_off + off;
           ch.tokens = min(a.chunk_tokens, c - off);
           ch.reserved = 0;
-          a.chunks[chunks] = ch;
-        } else {
-          err |= static_cast<int>(kErrChunkOverflow);
+          a.chunks[chunk_off++] = ch;
         }
-        ++chunks;
       }
-      running += (c + 127) & ~127;
+      slot_off += (c + 127) & ~127;
     }
-    if (running > a.max_slots) err |= static_cast<int>(kErrSlotOverflow);
-    if (err != 0) chunks = 0;  // never launch expert work on an inconsistent plan
-    s_error = err;
-    a.counters[kCntChunks] = static_cast<uint32_t>(min(chunks, a.max_chunks));
-    a.counters[kCntSlots] = static_cast<uint32_t>(running);
-    a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
-    a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
-    if (err != 0) atomicOr(&a.counters[kCntError], static_cast<uint32_t>(err));
+    if (lane == 0) {
+      s_error = err;
+      // never launch expert work on an inconsistent plan
+      a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(total_chunks);
+      a.counters[kCntSlots] = static_cast<uint32_t>(total_slots);
+      a.counters[kCntError] = static_cast<uint32_t>(err);   // also clears the word for the kernels that follow
+      a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+      a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+    }
   }
   __syncthreads();
   const bool bad = s_error != 0;

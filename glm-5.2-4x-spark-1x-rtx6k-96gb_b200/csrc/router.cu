@@ -64,6 +64,74 @@ router_logits_kernel(const XT* __restrict__ x, const WT* __restrict__ w, float* 
     logits[static_cast<size_t>(row0 + tm) * experts + exp0 + tn] = acc;
 }
 
+// Decode-sized batches: one CTA per pair of experts, each warp takes four rows per pass and its
+// lanes split the reduction dimension, so the float32 router weight is streamed from HBM exactly
+// once by 128 CTAs while the few activation rows are served by L2.  hidden % 128 == 0.
+// The per-lane partial sums and the butterfly reduction have a fixed order: results are
+// bit-reproducible.
+template <typename WT>
+__device__ __forceinline__ float4 load_w4(const WT* p);
+template <>
+__device__ __forceinline__ float4 load_w4<float>(const float* p) {
+  return __ldg(reinterpret_cast<const float4*>(p));
+}
+template <>
+__device__ __forceinline__ float4 load_w4<uint16_t>(const uint16_t* p) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                     __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+}
+
+constexpr int kSmallThreads = 512;   // 16 warps
+constexpr int kSmallRows = 4;        // rows per warp pass
+
+template <typename WT>
+__global__ void __launch_bounds__(kSmallThreads)
+router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict__ w, float* __restrict__ logits,
+                           int rows, int hidden, int experts) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int e0 = blockIdx.x * 2;
+  const int e1 = min(e0 + 1, experts - 1);
+  const WT* w0 = w + static_cast<size_t>(e0) * hidden;
+  const WT* w1 = w + static_cast<size_t>(e1) * hidden;
+  for (int r0 = warp * kSmallRows; r0 < rows; r0 += (kSmallThreads / 32) * kSmallRows) {
+    const uint16_t* xr[kSmallRows];
+    float acc0[kSmallRows], acc1[kSmallRows];
+#pragma unroll
+    for (int i = 0; i < kSmallRows; ++i) {
+      xr[i] = x + static_cast<size_t>(min(r0 + i, rows - 1)) * hidden;
+      acc0[i] = 0.0f;
+      acc1[i] = 0.0f;
+    }
+#pragma unroll 4
+    for (int k = lane * 4; k < hidden; k += 128) {
+      const float4 wa = load_w4<WT>(w0 + k), wb = load_w4<WT>(w1 + k);
+#pragma unroll
+      for (int i = 0; i < kSmallRows; ++i) {
+        const uint2 p = *reinterpret_cast<const uint2*>(xr[i] + k);
+        const float x0 = __uint_as_float(p.x << 16), x1 = __uint_as_float(p.x & 0xffff0000u);
+        const float x2 = __uint_as_float(p.y << 16), x3 = __uint_as_float(p.y & 0xffff0000u);
+        acc0[i] = fmaf(x0, wa.x, acc0[i]); acc0[i] = fmaf(x1, wa.y, acc0[i]);
+        acc0[i] = fmaf(x2, wa.z, acc0[i]); acc0[i] = fmaf(x3, wa.w, acc0[i]);
+        acc1[i] = fmaf(x0, wb.x, acc1[i]); acc1[i] = fmaf(x1, wb.y, acc1[i]);
+        acc1[i] = fmaf(x2, wb.z, acc1[i]); acc1[i] = fmaf(x3, wb.w, acc1[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kSmallRows; ++i) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        acc0[i] += __shfl_xor_sync(0xffffffffu, acc0[i], off);
+        acc1[i] += __shfl_xor_sync(0xffffffffu, acc1[i], off);
+      }
+      if (lane == 0 && r0 + i < rows) {
+        logits[static_cast<size_t>(r0 + i) * experts + e0] = acc0[i];
+        if (e0 + 1 < experts) logits[static_cast<size_t>(r0 + i) * experts + e0 + 1] = acc1[i];
+      }
+    }
+  }
+}
+
 // One warp per row.  Shared memory: per warp `experts` selection scores.
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
@@ -150,7 +218,17 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
                              cudaStream_t stream) {
   const dim3 grid(static_cast<unsigned>((rows + kTM - 1) / kTM), static_cast<unsigned>((experts + kTN - 1) / kTN));
   const int r = static_cast<int>(rows), h = static_cast<int>(hidden_dim), e = static_cast<int>(experts);
-  if (hidden_bf16 && weight_bf16)
+  const bool small = hidden_bf16 && rows <= 128 && hidden_dim % 128 == 0 &&
+                     reinterpret_cast<uintptr_t>(hidden) % 8 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
+  if (small) {
+    const unsigned ctas = static_cast<unsigned>((experts + 1) / 2);
+    if (weight_bf16)
+      router_logits_small_kernel<uint16_t><<<ctas, kSmallThreads, 0, stream>>>(
+          static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e);
+    else
+      router_logits_small_kernel<float><<<ctas, kSmallThreads, 0, stream>>>(
+          static_cast<const uint16_t*>(hidden), static_cast<const float*>(weight), logits, r, h, e);
+  } else if (hidden_bf16 && weight_bf16)
     router_logits_kernel<uint16_t, uint16_t><<<grid, kTM * kTN, 0, stream>>>(
         static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e);
   else if (hidden_bf16)

@@ -135,6 +135,17 @@ class MoeLayer:
                       C.c_size_t(rows), C.c_void_p(out_host.data_ptr()), _stream())
 
     # ---- introspection ----
+    STAGES = ("router", "quantize", "plan", "dispatch", "fc1", "fc2", "combine")
+
+    def set_profiling(self, enable: bool) -> None:
+        self.lib.call("glmrt_b200_moe_layer_set_profiling", self.handle, C.c_int(1 if enable else 0))
+
+    def stage_times_ms(self) -> dict:
+        """Device time of each stage of the last forward (CUDA events on the launching stream)."""
+        arr = (C.c_float * len(self.STAGES))()
+        self.lib.call("glmrt_b200_moe_layer_stage_times", self.handle, arr, C.c_size_t(len(self.STAGES)))
+        return dict(zip(self.STAGES, (float(v) for v in arr)))
+
     def check(self) -> None:
         self.lib.call("glmrt_b200_moe_layer_check", self.handle, _stream())
 

@@ -286,6 +286,23 @@ typedef struct glmrt_b200_layer_stats_t {
 } glmrt_b200_layer_stats_t;
 glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_layer_stats_t* out);
 
+/* Per-stage device times of the last forward, measured with CUDA events recorded on the
+ * caller's stream between the kernels (reference precedent: the CUDA-event timeline behind
+ * GLMRT_REAL_FULL_NVFP4_ROUTE_CUDA_EVENT_TIMING, sparse_mlp/route.rs:1010-1062). */
+typedef enum glmrt_b200_stage_t {
+  GLMRT_B200_STAGE_ROUTER = 0,
+  GLMRT_B200_STAGE_QUANTIZE = 1,
+  GLMRT_B200_STAGE_PLAN = 2,
+  GLMRT_B200_STAGE_DISPATCH = 3,
+  GLMRT_B200_STAGE_FC1 = 4,
+  GLMRT_B200_STAGE_FC2 = 5,
+  GLMRT_B200_STAGE_COMBINE = 6,
+  GLMRT_B200_STAGE_COUNT = 7
+} glmrt_b200_stage_t;
+glmrt_status_t glmrt_b200_moe_layer_set_profiling(void* layer, int enable);
+/* out_ms receives GLMRT_B200_STAGE_COUNT floats; waits for the last forward to finish. */
+glmrt_status_t glmrt_b200_moe_layer_stage_times(void* layer, float* out_ms, size_t count);
+
 #ifdef __cplusplus
 }
 #endif
