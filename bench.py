@@ -301,6 +301,7 @@ NCU_TRAFFIC_BYTES: dict = {}
 
 
 def main():
+    global E, ROUTER_BYTES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -308,7 +309,11 @@ def main():
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=E,
+                    help="routed experts in the layer (256 = GLM-5.2; smaller values give a profiler-sized case)")
     args = ap.parse_args()
+    E = args.experts
+    ROUTER_BYTES = E * H * 4
     if args.impl == "reference":
         run_reference(args)
     else:

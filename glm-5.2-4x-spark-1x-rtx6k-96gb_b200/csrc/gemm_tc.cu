@@ -32,7 +32,7 @@
 namespace glmrt {
 namespace {
 
-constexpr int kThreadsTC = 192;
+constexpr int kThreadsTC = 224;   // producer, issuer 0, four epilogue warps, issuer 1
 constexpr int kStageBytesK = 128;   // bytes of packed FP4 per row per pipeline stage (256 elements)
 constexpr int kTileRows = 128;      // weight rows per MMA tile (UMMA M)
 constexpr int kSfStageBytes = 2048; // 4 scale tiles of 512 B per operand per stage
@@ -173,7 +173,15 @@ struct Cfg {
   static constexpr int kSfbTiles = (kBN + 127) / 128;                      // scale tiles per k-block for B
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes + kNumA * kSfStageBytes + kSfbTiles * kSfStageBytes;
   static constexpr int kStages = (221184 / kStageBytes) > 10 ? 10 : (221184 / kStageBytes);
-  static constexpr int kAccCols = kNumA * kBN;                             // accumulator columns per buffer
+  // Successive MMAs into one accumulator form a dependent chain; at decode sizes (tiny N) the
+  // chain latency, not the math, bounds the tensor pipe.  The k-blocks of a stage therefore
+  // rotate over kSplit independent accumulator sets that the epilogue adds in a fixed order.
+  static constexpr int kSplit = kBN <= 32 ? (kFC1 ? 2 : 4) : 1;
+  // With several accumulator sets the k-blocks are also divided between two issuing warps
+  // (tcgen05 instructions of one thread execute in order; two threads issue concurrently).
+  static constexpr int kIssuers = kSplit >= 2 ? 2 : 1;
+  static constexpr int kSetCols = kNumA * kBN;                             // columns of one accumulator set
+  static constexpr int kAccCols = kSplit * kSetCols;                       // accumulator columns per buffer
   static constexpr int kAccBufs = (2 * kAccCols + 16 * kNumA + 16 * kSfbTiles <= 512) ? 2 : 1;
   static constexpr int kSfCol = kAccBufs * kAccCols;                       // first scale column
   static constexpr int kColsUsed = kSfCol + 16 * kNumA + 16 * kSfbTiles;
@@ -214,10 +222,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], C::kIssuers);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_full[b], C::kIssuers);
       mbar_init(&acc_empty[b], 4);
     }
     *abort_flag = 0u;
@@ -285,9 +293,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         }
       }
     }
-  } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 6) {
+    // ================= MMA issuers =================
+    const int issuer = warp == 1 ? 0 : 1;
+    if (lane == 0 && issuer < C::kIssuers) {
       int stage = 0;
       uint32_t phase = 0;
       int abuf = 0;
@@ -313,7 +322,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           const uint32_t s_sfa0 = s_b + C::kBBytes;
           const uint32_t s_sfb = s_sfa0 + C::kNumA * kSfStageBytes;
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
+          for (int kb = issuer; kb < 4; kb += C::kIssuers) {
             tc_copy_sf(t_sfa0 + kb * 4, desc_sf(s_sfa0 + kb * 512));
             if (kFC1) tc_copy_sf(t_sfa0 + 16 + kb * 4, desc_sf(s_sfa0 + kSfStageBytes + kb * 512));
 #pragma unroll
@@ -321,13 +330,14 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
               tc_copy_sf(t_sfb + kb * 4 * C::kSfbTiles + t * 4, desc_sf(s_sfb + t * kSfStageBytes + kb * 512));
           }
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            const uint32_t acc = (ks | kb) != 0 ? 1u : 0u;
+          for (int kb = issuer; kb < 4; kb += C::kIssuers) {
+            const uint32_t acc = (ks != 0 || kb >= C::kSplit) ? 1u : 0u;
+            const uint32_t dset = d0 + (kb % C::kSplit) * C::kSetCols;
             const uint64_t bdesc = desc_sw128(s_b + kb * 32);
             const uint32_t sfb_addr = t_sfb + kb * 4 * C::kSfbTiles + sfb_q;
-            tc_mma_nvf4(d0, desc_sw128(s_a0 + kb * 32), bdesc, idesc, t_sfa0 + kb * 4, sfb_addr, acc);
+            tc_mma_nvf4(dset, desc_sw128(s_a0 + kb * 32), bdesc, idesc, t_sfa0 + kb * 4, sfb_addr, acc);
             if (kFC1)
-              tc_mma_nvf4(d0 + kBN, desc_sw128(s_a0 + C::kABytes + kb * 32), bdesc, idesc, t_sfa0 + 16 + kb * 4,
+              tc_mma_nvf4(dset + kBN, desc_sw128(s_a0 + C::kABytes + kb * 32), bdesc, idesc, t_sfa0 + 16 + kb * 4,
                           sfb_addr, acc);
           }
           tc_commit(&empty_bar[stage]);  // frees the stage once the MMAs above have read it
@@ -371,6 +381,18 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           tc_load8(t_acc + kBN + c0, u);
           tc_wait_ld();
 #pragma unroll
+          for (int sp = 1; sp < C::kSplit; ++sp) {   // add the other accumulator sets, ascending
+            uint32_t g2[8], u2[8];
+            tc_load8(t_acc + sp * C::kSetCols + c0, g2);
+            tc_load8(t_acc + sp * C::kSetCols + kBN + c0, u2);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              g[j] = __float_as_uint(__fadd_rn(__uint_as_float(g[j]), __uint_as_float(g2[j])));
+              u[j] = __float_as_uint(__fadd_rn(__uint_as_float(u[j]), __uint_as_float(u2[j])));
+            }
+          }
+#pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < ch.tokens)  // uniform across the warp
               swiglu_requant_store(__fmul_rn(__uint_as_float(g[j]), s2a), __fmul_rn(__uint_as_float(u[j]), s2b),
@@ -385,6 +407,14 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           uint32_t y[8];
           tc_load8(t_acc + c0, y);
           tc_wait_ld();
+#pragma unroll
+          for (int sp = 1; sp < C::kSplit; ++sp) {   // add the other accumulator sets, ascending
+            uint32_t y2[8];
+            tc_load8(t_acc + sp * C::kSetCols + c0, y2);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = __float_as_uint(__fadd_rn(__uint_as_float(y[j]), __uint_as_float(y2[j])));
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const unsigned long long p =
