@@ -8,6 +8,8 @@
 // glm_moe_dsa_layer_ref.py:62-83 and, for non-finite scores, router.cu:112-116.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -312,5 +314,58 @@ extern "C" glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
   GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, router_weight, false, correction_bias, logits_scratch,
                                       topk_indices, topk_scores, topk_weights, rows, hidden_dim, experts, top_k,
                                       2.5f, static_cast<cudaStream_t>(cuda_stream)));
+  return ok();
+}
+
+// ---- allocation-free variant -------------------------------------------------------------
+// Logits scratch that lives in the library image instead of in allocated memory.  Every GPU that
+// loads the library holds these 1 MiB until the process exits.
+namespace {
+constexpr size_t kStaticLogitsFloats = 262144;  // rows * experts may not exceed this
+static __device__ __align__(256) float g_static_logits[kStaticLogitsFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_ptr[kMaxDevices] = {};
+
+// Device address of g_static_logits on the current device.  In host code the symbol's name is
+// only a handle; the address a kernel can use has to be asked for, once per device, while that
+// device is current.
+glmrt_status_t static_logits_ptr(float** out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaGetDevice", err);
+  if (dev < 0 || dev >= kMaxDevices) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router (static scratch): device index out of range");
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_logits);
+    if (err != cudaSuccess || p == nullptr)
+      return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaGetSymbolAddress(static logits scratch)", err);
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return GLMRT_STATUS_OK;
+}
+}  // namespace
+
+extern "C" glmrt_status_t glmrt_b200_router_topk_bf16_f32w_static_async(
+    const uint16_t* hidden, const float* router_weight, const float* correction_bias, uint32_t* topk_indices,
+    float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim, size_t experts, size_t top_k,
+    void* cuda_stream) {
+  GLMRT_RETURN_IF_ERROR(validate(hidden, router_weight, correction_bias, topk_indices, topk_weights, rows,
+                                 hidden_dim, experts, top_k));
+  if (rows * experts > kStaticLogitsFloats)
+    return fail(GLMRT_STATUS_BUFFER_TOO_SMALL,
+                "router (static scratch): rows * experts exceeds the built-in scratch of 262144 floats; use "
+                "glmrt_b200_router_topk_bf16_f32w_async with caller-provided scratch");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  float* logits = nullptr;
+  GLMRT_RETURN_IF_ERROR(static_logits_ptr(&logits));
+  // Every logit the selection kernel reads is written by the logits kernel of the same call, so
+  // nothing left behind by an earlier call has to be cleared.
+  GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, router_weight, false, correction_bias, logits, topk_indices,
+                                      topk_scores, topk_weights, rows, hidden_dim, experts, top_k, 2.5f,
+                                      static_cast<cudaStream_t>(cuda_stream)));
   return ok();
 }

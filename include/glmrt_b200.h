@@ -125,6 +125,22 @@ glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
     float* logits_scratch, uint32_t* topk_indices, float* topk_scores, float* topk_weights,
     size_t rows, size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
 
+/* No counterpart in the reference.  Same computation as
+ * glmrt_b200_router_topk_bf16_f32w_async, for callers that must not allocate device memory and
+ * have no scratch buffer to lend: code running where cudaMalloc is off limits (inside a
+ * latency-critical serving loop whose memory is fully pre-assigned, or after the process has
+ * handed all remaining device memory to another component).  The rows * experts float logits
+ * live in an array built into the library (1 MiB, held by every GPU that loads the library until
+ * the process exits), so rows * experts must not exceed 262144; larger problems are rejected
+ * with GLMRT_STATUS_BUFFER_TOO_SMALL.  The entry point calls no allocator.  The first call on a
+ * device looks up the array's device address; make that first call outside any stream capture.
+ * All calls on one device share the array: calls that may overlap on the GPU (different streams)
+ * race on it and must be ordered by the caller. */
+glmrt_status_t glmrt_b200_router_topk_bf16_f32w_static_async(
+    const uint16_t* hidden, const float* router_weight, const float* correction_bias,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim,
+    size_t experts, size_t top_k, void* cuda_stream);
+
 /* ------------------------------------------------------------------------ */
 /* NVFP4 codecs                                                               */
 /* ------------------------------------------------------------------------ */
