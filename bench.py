@@ -289,15 +289,18 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "kernel": "expert_gemm_kernel<FC1>", "achieved": fc1_gbs, "peak": peak,
                      "unit": "GB/s", "frac": fc1_gbs / peak, "peak_source": peak_kind,
                      "algorithmic_bytes_per_launch": fc1_bytes, "ms_per_launch": stage_ms["fc1"],
-                     "traffic": NCU_TRAFFIC_BYTES.get(T)},
+                     "traffic": NCU_FC1_TRAFFIC_PER_EXPERT * distinct,
+                     "traffic_source": "ncu dram read+write of one FC1 launch on a 64-expert T=16 case "
+                                       "(profiles/expert_gemm_fc1_fc2_E64_T16_ncu_full.md), per expert touched, "
+                                       "times the experts touched here"},
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch from an ncu capture of this
-# command, keyed by T (see profiles/); None where no capture exists.
-NCU_TRAFFIC_BYTES: dict = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch (818.80 MB, 57 experts touched)
+# from the ncu capture summarised under profiles/: DRAM traffic per expert touched.
+NCU_FC1_TRAFFIC_PER_EXPERT = 818.80e6 / 57
 
 
 def main():
