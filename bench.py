@@ -195,8 +195,7 @@ def run_gpu(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        from glmrt_b200.ep import run_ep_bench
-        return run_ep_bench(args, dist, rank, world, local_rank)
+        return run_ep(args, dist, rank, world, local_rank)
 
     T, steps, warmup = args.tokens, args.steps, max(3, args.warmup)
     sampler = ClockSampler(local_rank)
@@ -296,6 +295,110 @@ def run_gpu(args):
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_ep(args, dist, rank, world, local_rank):
+    """N > 1: the same layer and the same global batch, experts sharded e % N over the ranks
+    (256/N per GPU), each rank home to T/N rows; rows and results cross NVLink as in-kernel peer
+    stores.  Total work is fixed as N grows (strong scaling)."""
+    import torch
+    from glmrt_b200 import ep as EP
+    from glmrt_b200.layer import MoeLayer
+
+    T, steps, warmup = args.tokens, args.steps, max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    layer = MoeLayer(H, I, E, K_TOP, max_tokens=T, ep_world=world, ep_rank=rank)
+    layer.fill_synthetic(0, 0.02)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    layer.set_router(torch.randn(E, H, generator=g) * 0.02, torch.zeros(E))
+    EP.attach_distributed(layer, dist)
+    r0, rn = EP.partition_rows(T, world, rank)
+    n_batches = 4
+    host_batches = [torch.randn(T, H, generator=g).to(torch.bfloat16)[r0:r0 + rn].contiguous().pin_memory()
+                    for _ in range(n_batches)]
+    dev_batches = [b.cuda() for b in host_batches]
+    out = torch.empty(rn, H, dtype=torch.bfloat16, device="cuda")
+    host_out = torch.empty(rn, H, dtype=torch.bfloat16).pin_memory()
+
+    def timed(fn, n):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(n):
+            fn(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / n
+
+    for i in range(warmup):
+        EP.forward_ep(layer, dev_batches[i % n_batches], out)
+    layer.check()
+    st0 = layer.stats()
+    ms_per_step = timed(lambda i: EP.forward_ep(layer, dev_batches[i % n_batches], out), steps)
+    st1 = layer.stats()
+    launches = int(st1.launches_total - st0.launches_total)
+
+    layer.set_profiling(True)
+    stage_sum, distinct_sum = {}, 0
+    for i in range(steps):
+        EP.forward_ep(layer, dev_batches[i % n_batches], out)
+        for k, v in layer.stage_times_ms().items():
+            stage_sum[k] = stage_sum.get(k, 0.0) + v
+        distinct_sum += layer.stats().distinct_experts
+    layer.set_profiling(False)
+    stage_ms = {k: v / steps for k, v in stage_sum.items()}
+    distinct = distinct_sum / steps
+    routes_owned = T * K_TOP / world
+    fc1_bytes = distinct * FC1_EXPERT_BYTES + routes_owned * ((H // 2 + H // 16) + (I // 2 + I // 16))
+    peak, peak_kind = measured_peak_gbs()
+    fc1_gbs = fc1_bytes / (stage_ms["fc1"] * 1e-3) / 1e9
+
+    e2e_ms = timed(lambda i: EP.forward_ep_host(layer, host_batches[i % n_batches], host_out), steps)
+    layer.check()
+    sampler.stop()
+    sampler.join(timeout=2)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {"distinct": distinct, "fc1_ms": stage_ms["fc1"], "fc2_ms": stage_ms["fc2"],
+                                      "clocks": sampler.summary()})
+    if rank == 0:
+        total_distinct = sum(x["distinct"] for x in gathered)
+        layer_bytes = layer_algorithmic_bytes(T, total_distinct)
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": T / (ms_per_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4",
+            "data": "synthetic",
+            "config": {"workload": f"glm52_moe_layer_decode_T{T}", "tokens": T, "hidden": H, "experts": E,
+                       "top_k": K_TOP, "intermediate": I, "experts_per_gpu": E // world,
+                       "parallelism": f"ep{world}: expert e on rank e % {world}, rows block-partitioned, "
+                                      "dispatch/combine = in-kernel NVLink peer stores",
+                       "l2": f"no flush: each step streams {layer_bytes / 1e9:.2f} GB of expert weights over "
+                             f"{world} GPUs, far above the 126 MB L2",
+                       "distinct_experts_per_step": total_distinct, "stage_ms_rank0": stage_ms,
+                       "max_over_ranks_imbalance": max(x["distinct"] for x in gathered) /
+                                                   max(1e-9, total_distinct / world),
+                       "layer_hbm_gbs_aggregate": layer_bytes / (ms_per_step * 1e-3) / 1e9,
+                       "layer_frac_of_aggregate_peak": layer_bytes / (ms_per_step * 1e-3) / 1e9 / (peak * world)},
+            "clocks": gathered[0]["clocks"],
+            "clocks_all_ranks": [x["clocks"] for x in gathered],
+            "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
+                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_ms},
+            "gpu_launches": launches * world,
+            "roofline": {"bound": "hbm", "kernel": "expert_gemm_kernel<FC1> (rank 0)", "achieved": fc1_gbs,
+                         "peak": peak, "unit": "GB/s", "frac": fc1_gbs / peak, "peak_source": peak_kind,
+                         "algorithmic_bytes_per_launch": fc1_bytes, "ms_per_launch": stage_ms["fc1"],
+                         "traffic": NCU_FC1_TRAFFIC_PER_EXPERT * distinct},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    layer.close()
+    dist.destroy_process_group()
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch (818.80 MB, 57 experts touched)

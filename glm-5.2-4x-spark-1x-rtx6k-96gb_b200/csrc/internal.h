@@ -74,6 +74,43 @@ struct DispatchArgs {
 };
 glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
 
+// ---- ep.cu (expert-parallel exchange over peer memory) ----
+constexpr int kEpMaxExperts = 1024;
+constexpr int kEpMaxWorld = 8;
+struct EpControl {
+  // written by peers
+  int32_t counts_all[kEpMaxWorld * kEpMaxExperts];  // [source rank][global expert] routes
+  uint32_t flag_counts[kEpMaxWorld];                 // epoch of the last histogram received from each rank
+  uint32_t flag_dispatch[kEpMaxWorld];               // epoch of the last completed row push from each rank
+  uint32_t flag_combine[kEpMaxWorld];                // epoch of the last completed result push from each owner
+  // local only
+  int32_t total[kEpMaxExperts];       // routes per expert over all ranks
+  int32_t my_offset[kEpMaxExperts];   // first position of this rank's routes inside the expert's slot range
+  int32_t base_slot[kEpMaxExperts];   // first slot of the expert at its owner
+  int32_t cursor[kEpMaxExperts];      // next free position among this rank's routes
+  int32_t done;
+  int32_t plan_error;
+};
+struct EpArgs {
+  int world, rank, experts;
+  uint32_t epoch;
+  EpControl* ctrl;
+  uint32_t* counters;
+  EpControl* peer_ctrl[kEpMaxWorld];
+  uint8_t* peer_act_codes[kEpMaxWorld];
+  uint8_t* peer_act_sf[kEpMaxWorld];
+  uint16_t** peer_slot_out[kEpMaxWorld];
+  uint16_t* my_rows_in_peer[kEpMaxWorld];   // this rank's route_rows as addressed from each peer
+};
+glmrt_status_t launch_ep_count(const EpArgs& a, const uint32_t* topk_indices, int routes, cudaStream_t stream);
+glmrt_status_t launch_ep_plan(const EpArgs& a, const PlanArgs& p, cudaStream_t stream);
+glmrt_status_t launch_ep_dispatch(const EpArgs& a, const uint8_t* payload, const uint32_t* topk_indices,
+                                  int32_t* route_slot, int rows, int top_k, int hidden, const uint32_t* counters,
+                                  cudaStream_t stream);
+glmrt_status_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, uint32_t* error_word,
+                              uint32_t* chunk_count, cudaStream_t stream);
+glmrt_status_t launch_ep_signal(const EpArgs& a, int which, cudaStream_t stream);
+
 // ---- combine.cu ----
 glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,

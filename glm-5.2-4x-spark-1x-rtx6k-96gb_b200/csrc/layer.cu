@@ -51,6 +51,12 @@ struct Layer {
   bool profiling = false;
   cudaEvent_t stage_events[GLMRT_B200_STAGE_COUNT + 1] = {};
   bool stage_valid = false;
+  // expert-parallel exchange
+  EpControl* ep_ctrl = nullptr;
+  EpArgs ep{};
+  bool ep_attached = false;
+  uint32_t ep_epoch = 0;
+  std::vector<void*> ipc_mappings;
 };
 
 void mark(Layer* l, int stage_begin, cudaStream_t s) {
@@ -75,6 +81,7 @@ glmrt_status_t dev_alloc(Layer* l, T** out, size_t count, bool zero = false) {
 }
 
 void destroy(Layer* l) {
+  for (void* p : l->ipc_mappings) cudaIpcCloseMemHandle(p);
   for (cudaEvent_t e : l->stage_events)
     if (e != nullptr) cudaEventDestroy(e);
   for (void* p : l->allocations) cudaFree(p);
@@ -209,8 +216,8 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: experts must be 1..1024 and top_k 1..min(16, experts)");
   if (c.max_tokens == 0 || c.max_tokens > (1u << 20))
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: max_tokens must be 1..1048576");
-  if (c.ep_world == 0 || c.ep_rank >= c.ep_world || c.ep_world > c.experts)
-    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: need 0 <= ep_rank < ep_world <= experts");
+  if (c.ep_world == 0 || c.ep_rank >= c.ep_world || c.ep_world > c.experts || c.ep_world > kEpMaxWorld)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: need 0 <= ep_rank < ep_world <= min(experts, 8)");
   if (!(c.routed_scaling > 0.0f)) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: routed_scaling must be positive");
   GLMRT_RETURN_IF_ERROR(require_cuda());
   Layer* l = new (std::nothrow) Layer();
@@ -256,6 +263,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
   A(dev_alloc(l, &l->sftmp, I * H / 16));
   A(dev_alloc(l, &l->amax_tmp, 1, true));
+  if (c.ep_world > 1) A(dev_alloc(l, &l->ep_ctrl, 1, true));
   if (st != GLMRT_STATUS_OK) {
     destroy(l);
     return st;
@@ -516,5 +524,233 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_stage_times(void* layer, float* o
   for (int i = 0; i < GLMRT_B200_STAGE_COUNT && err == cudaSuccess; ++i)
     err = cudaEventElapsedTime(&out_ms[i], l->stage_events[i], l->stage_events[i + 1]);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "stage_times", err);
+  return ok();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel forward
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+glmrt_status_t require_ep(Layer* l, bool attached) {
+  if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  if (l->cfg.ep_world < 2 || l->ep_ctrl == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel entry point on a layer created with ep_world == 1");
+  if (attached && !l->ep_attached)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel forward before glmrt_b200_ep_attach");
+  return GLMRT_STATUS_OK;
+}
+
+void local_ep_buffers(Layer* l, glmrt_b200_ep_buffers_t* out) {
+  out->act_codes = l->act1_codes;
+  out->act_sf = l->act1_sf;
+  out->slot_out = l->slot_out;
+  out->route_rows = l->route_rows;
+  out->control = l->ep_ctrl;
+}
+
+glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t rows, uint16_t* out,
+                        cudaStream_t s) {
+  const auto& c = l->cfg;
+  const int chunk_tokens = c.max_tokens <= 256 ? 32 : 128;   // same on every rank (same configuration)
+  const int routes = static_cast<int>(rows * c.top_k);
+  EpArgs a = l->ep;
+  a.epoch = l->ep_epoch;
+  switch (phase) {
+    case 0: {
+      mark(l, GLMRT_B200_STAGE_ROUTER, s);
+      if (rows > 0)
+        GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, l->router_w, false, l->router_b, l->logits, l->topk_idx,
+                                            l->topk_scores, l->topk_w, rows, c.hidden_dim, c.experts, c.top_k,
+                                            c.routed_scaling, s));
+      mark(l, GLMRT_B200_STAGE_QUANTIZE, s);
+      if (rows > 0)
+        GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
+                                                           GLMRT_B200_FP4_RULE_NEAREST_LOW, s));
+      mark(l, GLMRT_B200_STAGE_PLAN, s);
+      return launch_ep_count(a, l->topk_idx, routes, s);
+    }
+    case 1: {
+      PlanArgs p{};
+      p.topk_indices = l->topk_idx;
+      p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
+      p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
+      p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
+      p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
+      p.chunks = l->chunks; p.counters = l->counters;
+      GLMRT_RETURN_IF_ERROR(launch_ep_plan(a, p, s));
+      mark(l, GLMRT_B200_STAGE_DISPATCH, s);
+      if (routes > 0)
+        return launch_ep_dispatch(a, l->payload, l->topk_idx, l->route_slot, static_cast<int>(rows),
+                                  static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), l->counters, s);
+      return launch_ep_signal(a, 0, s);   // nothing to push: just tell the owners
+    }
+    case 2: {
+      GLMRT_RETURN_IF_ERROR(launch_ep_wait(l->ep_ctrl->flag_dispatch, static_cast<int>(c.ep_world), a.epoch,
+                                           l->counters + kCntError, l->counters + kCntChunks, s));
+      FfnArgs f = ffn_args(l, chunk_tokens);
+      mark(l, GLMRT_B200_STAGE_FC1, s);
+      if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
+        GLMRT_RETURN_IF_ERROR(launch_fc1_simt(f, s));
+        mark(l, GLMRT_B200_STAGE_FC2, s);
+        GLMRT_RETURN_IF_ERROR(launch_fc2_simt(f, s));
+      } else {
+        if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
+        const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
+        GLMRT_RETURN_IF_ERROR(launch_fc1_tc(f, maps, l->sm_count, s));
+        mark(l, GLMRT_B200_STAGE_FC2, s);
+        GLMRT_RETURN_IF_ERROR(launch_fc2_tc(f, maps, l->sm_count, s));
+      }
+      mark(l, GLMRT_B200_STAGE_COMBINE, s);
+      return launch_ep_signal(a, 1, s);   // results of this owner have been stored to their home ranks
+    }
+    case 3: {
+      GLMRT_RETURN_IF_ERROR(launch_ep_wait(l->ep_ctrl->flag_combine, static_cast<int>(c.ep_world), a.epoch,
+                                           l->counters + kCntError, nullptr, s));
+      if (rows > 0)
+        GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, nullptr, out, static_cast<int>(rows),
+                                                    static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), s));
+      mark(l, GLMRT_B200_STAGE_COUNT, s);
+      l->stage_valid = l->profiling;
+      return GLMRT_STATUS_OK;
+    }
+    default:
+      return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep: phase must be 0..3");
+  }
+}
+
+glmrt_status_t validate_ep_forward(Layer* l, glmrt_device_buffer_t hidden, size_t rows, glmrt_device_buffer_t out) {
+  GLMRT_RETURN_IF_ERROR(require_ep(l, true));
+  if (rows > l->cfg.max_tokens) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep: rows exceed max_tokens");
+  if (rows > 0) {
+    const size_t bytes = rows * static_cast<size_t>(l->cfg.hidden_dim) * 2;
+    GLMRT_RETURN_IF_ERROR(check_buf(hidden, bytes, "forward_ep hidden"));
+    GLMRT_RETURN_IF_ERROR(check_buf(out, bytes, "forward_ep output"));
+    if (reinterpret_cast<uintptr_t>(hidden.ptr) % 16 != 0 || reinterpret_cast<uintptr_t>(out.ptr) % 16 != 0)
+      return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep: hidden and output must be 16-byte aligned");
+  }
+  return GLMRT_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" glmrt_status_t glmrt_b200_ep_local_buffers(void* layer, glmrt_b200_ep_buffers_t* out) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, false));
+  if (out == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_local_buffers: null output");
+  local_ep_buffers(l, out);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_ep_ipc_export(void* layer, void* out_handles, size_t bytes) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, false));
+  if (out_handles == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_ipc_export: null output");
+  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_export: need 320 bytes");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle size");
+  glmrt_b200_ep_buffers_t b;
+  local_ep_buffers(l, &b);
+  void* ptrs[5] = {b.act_codes, b.act_sf, b.slot_out, b.route_rows, b.control};
+  for (int i = 0; i < 5; ++i) {
+    cudaIpcMemHandle_t h;
+    cudaError_t err = cudaIpcGetMemHandle(&h, ptrs[i]);
+    if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaIpcGetMemHandle", err);
+    std::memcpy(static_cast<uint8_t*>(out_handles) + 64 * i, &h, 64);
+  }
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handles, size_t bytes,
+                                                 glmrt_b200_ep_buffers_t* out_mapped) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, false));
+  if (handles == nullptr || out_mapped == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_ipc_open: null argument");
+  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_open: need 320 bytes");
+  void* ptrs[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int i = 0; i < 5; ++i) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * i, 64);
+    cudaError_t err = cudaIpcOpenMemHandle(&ptrs[i], h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaIpcOpenMemHandle (peer access between the GPUs is required)", err);
+    l->ipc_mappings.push_back(ptrs[i]);
+  }
+  out_mapped->act_codes = ptrs[0];
+  out_mapped->act_sf = ptrs[1];
+  out_mapped->slot_out = ptrs[2];
+  out_mapped->route_rows = ptrs[3];
+  out_mapped->control = ptrs[4];
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_ep_attach(void* layer, const glmrt_b200_ep_buffers_t* peers, size_t world,
+                                               const uint64_t* my_rows_in_peer) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, false));
+  if (peers == nullptr || my_rows_in_peer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: null argument");
+  if (world != l->cfg.ep_world) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: world differs from the layer's ep_world");
+  EpArgs a{};
+  a.world = static_cast<int>(world);
+  a.rank = static_cast<int>(l->cfg.ep_rank);
+  a.experts = static_cast<int>(l->cfg.experts);
+  a.ctrl = l->ep_ctrl;
+  a.counters = l->counters;
+  for (size_t p = 0; p < world; ++p) {
+    if (peers[p].act_codes == nullptr || peers[p].act_sf == nullptr || peers[p].slot_out == nullptr ||
+        peers[p].control == nullptr || my_rows_in_peer[p] == 0)
+      return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: a peer buffer is null");
+    a.peer_ctrl[p] = static_cast<EpControl*>(peers[p].control);
+    a.peer_act_codes[p] = static_cast<uint8_t*>(peers[p].act_codes);
+    a.peer_act_sf[p] = static_cast<uint8_t*>(peers[p].act_sf);
+    a.peer_slot_out[p] = static_cast<uint16_t**>(peers[p].slot_out);
+    a.my_rows_in_peer[p] = reinterpret_cast<uint16_t*>(static_cast<uintptr_t>(my_rows_in_peer[p]));
+  }
+  if (a.peer_ctrl[a.rank] != l->ep_ctrl)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: the entry of this rank must be its own local buffers");
+  l->ep = a;
+  l->ep_attached = true;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_ep_phase_async(void* layer, uint32_t phase,
+                                                                      glmrt_device_buffer_t hidden_bf16, size_t rows,
+                                                                      glmrt_device_buffer_t output_bf16,
+                                                                      void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_ep_forward(l, hidden_bf16, rows, output_bf16));
+  if (phase > 3) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep: phase must be 0..3");
+  if (phase == 0) ++l->ep_epoch;
+  const uint64_t before = launches_total();
+  GLMRT_RETURN_IF_ERROR(ep_phase(l, phase, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                 static_cast<uint16_t*>(output_bf16.ptr), static_cast<cudaStream_t>(cuda_stream)));
+  l->launches_last = (phase == 0 ? 0 : l->launches_last) + static_cast<uint32_t>(launches_total() - before);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_ep_async(void* layer, glmrt_device_buffer_t hidden_bf16,
+                                                                size_t rows, glmrt_device_buffer_t output_bf16,
+                                                                void* cuda_stream) {
+  for (uint32_t phase = 0; phase < 4; ++phase)
+    GLMRT_RETURN_IF_ERROR(glmrt_b200_moe_layer_forward_ep_phase_async(layer, phase, hidden_bf16, rows, output_bf16,
+                                                                      cuda_stream));
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_ep_host(void* layer, const void* hidden_host, size_t rows,
+                                                               void* output_host, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, true));
+  if (rows > l->cfg.max_tokens) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep_host: rows exceed max_tokens");
+  if (rows > 0 && (hidden_host == nullptr || output_host == nullptr))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep_host: null host pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const size_t bytes = rows * static_cast<size_t>(l->cfg.hidden_dim) * 2;
+  cudaError_t err = cudaSuccess;
+  if (rows > 0) err = cudaMemcpyAsync(l->hidden_stage, hidden_host, bytes, cudaMemcpyHostToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_ep_host input copy", err);
+  glmrt_device_buffer_t in{l->hidden_stage, bytes, l->device, 0}, out{l->out_stage, bytes, l->device, 0};
+  GLMRT_RETURN_IF_ERROR(glmrt_b200_moe_layer_forward_ep_async(layer, in, rows, out, cuda_stream));
+  if (rows > 0) err = cudaMemcpyAsync(output_host, l->out_stage, bytes, cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_ep_host output copy", err);
   return ok();
 }

@@ -302,6 +302,48 @@ typedef struct glmrt_b200_layer_stats_t {
 } glmrt_b200_layer_stats_t;
 glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_layer_stats_t* out);
 
+/* ------------------------------------------------------------------------ */
+/* Expert-parallel forward over NVLink peer memory (additions).               */
+/* Replaces the ExpertProtocolV2 TCP/RDMA transport between coordinator and    */
+/* expert hosts (rust/crates/glmrt-transport/src/protocol_v2.rs:236-310) and   */
+/* the NCCL row all-to-all between shards (native/src/glmrt_native.cc:         */
+/* 1593-1659): rank r owns experts e % ep_world == r and is home to its own    */
+/* rows; routed rows and results travel as in-kernel stores into the peer's    */
+/* memory.  Set-up: every rank exports its buffers (ipc_export), opens every    */
+/* peer's (ipc_open), tells the others where it sees their result rows, and    */
+/* attaches.  A single process driving several layer objects on one device     */
+/* may attach with glmrt_b200_ep_local_buffers pointers directly.              */
+/* ------------------------------------------------------------------------ */
+typedef struct glmrt_b200_ep_buffers_t {
+  void* act_codes;   /* [slots, H/2] rows pushed by home ranks */
+  void* act_sf;      /* tiled scales of the same */
+  void* slot_out;    /* [slots] result-row address per slot */
+  void* route_rows;  /* bf16 [rows * top_k, H] result rows pushed by owners */
+  void* control;     /* histograms and epoch flags */
+} glmrt_b200_ep_buffers_t;
+#define GLMRT_B200_EP_IPC_BYTES 320 /* five 64-byte CUDA IPC handles */
+glmrt_status_t glmrt_b200_ep_local_buffers(void* layer, glmrt_b200_ep_buffers_t* out);
+glmrt_status_t glmrt_b200_ep_ipc_export(void* layer, void* out_handles, size_t bytes);
+glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handles, size_t bytes,
+                                      glmrt_b200_ep_buffers_t* out_mapped);
+/* peers[p] = rank p's buffers as addressable from this process (own rank: local buffers);
+ * my_rows_in_peer[p] = the address under which rank p sees THIS rank's route_rows. */
+glmrt_status_t glmrt_b200_ep_attach(void* layer, const glmrt_b200_ep_buffers_t* peers, size_t world,
+                                    const uint64_t* my_rows_in_peer);
+/* Collective: every rank calls it once per step with its own rows (rows may differ per rank and
+ * may be 0).  Phases: 0 route + publish counts, 1 plan + push rows, 2 expert GEMMs + push results,
+ * 3 combine.  forward_ep_async runs 0..3; the phase entry point lets one process step several
+ * ranks that share a device (kernels that wait on one another must not be queued behind each
+ * other).  Waits are bounded; expiry is reported by glmrt_b200_moe_layer_check. */
+glmrt_status_t glmrt_b200_moe_layer_forward_ep_async(void* layer, glmrt_device_buffer_t hidden_bf16,
+                                                     size_t rows, glmrt_device_buffer_t output_bf16,
+                                                     void* cuda_stream);
+glmrt_status_t glmrt_b200_moe_layer_forward_ep_phase_async(void* layer, uint32_t phase,
+                                                           glmrt_device_buffer_t hidden_bf16, size_t rows,
+                                                           glmrt_device_buffer_t output_bf16, void* cuda_stream);
+glmrt_status_t glmrt_b200_moe_layer_forward_ep_host(void* layer, const void* hidden_host, size_t rows,
+                                                    void* output_host, void* cuda_stream);
+
 /* Per-stage device times of the last forward, measured with CUDA events recorded on the
  * caller's stream between the kernels (reference precedent: the CUDA-event timeline behind
  * GLMRT_REAL_FULL_NVFP4_ROUTE_CUDA_EVENT_TIMING, sparse_mlp/route.rs:1010-1062). */
