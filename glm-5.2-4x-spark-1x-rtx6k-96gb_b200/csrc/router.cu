@@ -85,38 +85,63 @@ __device__ __forceinline__ float4 load_w4<uint16_t>(const uint16_t* p) {
 }
 
 constexpr int kSmallThreads = 512;   // 16 warps
-constexpr int kSmallRows = 4;        // rows per warp pass
+constexpr int kSmallWarps = kSmallThreads / 32;
+constexpr int kSmallRows = 4;        // rows per pass
+constexpr int kSmallMaxRows = 128;
+constexpr int kSmallMaxSteps = 4;     // 128-element steps per warp: hidden <= 8192
 
+// The 128-element steps of the reduction are dealt round-robin to the 16 warps; each warp keeps
+// its slice of the two weight rows in registers and sweeps all rows, then the 16 partial sums of
+// every logit are added in warp order.  The summation order depends on hidden only, never on
+// the number of rows, so a row routed alone gets the same logits as inside any batch.
 template <typename WT>
 __global__ void __launch_bounds__(kSmallThreads)
 router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict__ w, float* __restrict__ logits,
                            int rows, int hidden, int experts) {
+  __shared__ float partial[kSmallWarps][kSmallMaxRows][2];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int e0 = blockIdx.x * 2;
   const int e1 = min(e0 + 1, experts - 1);
   const WT* w0 = w + static_cast<size_t>(e0) * hidden;
   const WT* w1 = w + static_cast<size_t>(e1) * hidden;
-  for (int r0 = warp * kSmallRows; r0 < rows; r0 += (kSmallThreads / 32) * kSmallRows) {
-    const uint16_t* xr[kSmallRows];
-    float acc0[kSmallRows], acc1[kSmallRows];
+  const int steps = hidden / 128;
+  // this warp's slice of both weight rows stays in registers for the whole sweep over the rows
+  float4 wa[kSmallMaxSteps], wb[kSmallMaxSteps];
 #pragma unroll
-    for (int i = 0; i < kSmallRows; ++i) {
-      xr[i] = x + static_cast<size_t>(min(r0 + i, rows - 1)) * hidden;
-      acc0[i] = 0.0f;
-      acc1[i] = 0.0f;
+  for (int s = 0; s < kSmallMaxSteps; ++s) {
+    const int j = warp + s * kSmallWarps;
+    if (j < steps) {
+      wa[s] = load_w4<WT>(w0 + j * 128 + lane * 4);
+      wb[s] = load_w4<WT>(w1 + j * 128 + lane * 4);
+    } else {
+      wa[s] = wb[s] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-#pragma unroll 4
-    for (int k = lane * 4; k < hidden; k += 128) {
-      const float4 wa = load_w4<WT>(w0 + k), wb = load_w4<WT>(w1 + k);
+  }
+  for (int r0 = 0; r0 < rows; r0 += kSmallRows) {
+    float acc0[kSmallRows], acc1[kSmallRows];
+    uint2 px[kSmallMaxSteps][kSmallRows];
+#pragma unroll
+    for (int s = 0; s < kSmallMaxSteps; ++s) {
+      const int j = warp + s * kSmallWarps;
+#pragma unroll
+      for (int i = 0; i < kSmallRows; ++i)
+        px[s][i] = j < steps ? *reinterpret_cast<const uint2*>(
+                                   x + static_cast<size_t>(min(r0 + i, rows - 1)) * hidden + j * 128 + lane * 4)
+                             : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < kSmallRows; ++i) acc0[i] = acc1[i] = 0.0f;
+#pragma unroll
+    for (int s = 0; s < kSmallMaxSteps; ++s) {
 #pragma unroll
       for (int i = 0; i < kSmallRows; ++i) {
-        const uint2 p = *reinterpret_cast<const uint2*>(xr[i] + k);
+        const uint2 p = px[s][i];
         const float x0 = __uint_as_float(p.x << 16), x1 = __uint_as_float(p.x & 0xffff0000u);
         const float x2 = __uint_as_float(p.y << 16), x3 = __uint_as_float(p.y & 0xffff0000u);
-        acc0[i] = fmaf(x0, wa.x, acc0[i]); acc0[i] = fmaf(x1, wa.y, acc0[i]);
-        acc0[i] = fmaf(x2, wa.z, acc0[i]); acc0[i] = fmaf(x3, wa.w, acc0[i]);
-        acc1[i] = fmaf(x0, wb.x, acc1[i]); acc1[i] = fmaf(x1, wb.y, acc1[i]);
-        acc1[i] = fmaf(x2, wb.z, acc1[i]); acc1[i] = fmaf(x3, wb.w, acc1[i]);
+        acc0[i] = fmaf(x0, wa[s].x, acc0[i]); acc0[i] = fmaf(x1, wa[s].y, acc0[i]);
+        acc0[i] = fmaf(x2, wa[s].z, acc0[i]); acc0[i] = fmaf(x3, wa[s].w, acc0[i]);
+        acc1[i] = fmaf(x0, wb[s].x, acc1[i]); acc1[i] = fmaf(x1, wb[s].y, acc1[i]);
+        acc1[i] = fmaf(x2, wb[s].z, acc1[i]); acc1[i] = fmaf(x3, wb[s].w, acc1[i]);
       }
     }
 #pragma unroll
@@ -127,10 +152,18 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
         acc1[i] += __shfl_xor_sync(0xffffffffu, acc1[i], off);
       }
       if (lane == 0 && r0 + i < rows) {
-        logits[static_cast<size_t>(r0 + i) * experts + e0] = acc0[i];
-        if (e0 + 1 < experts) logits[static_cast<size_t>(r0 + i) * experts + e0 + 1] = acc1[i];
+        partial[warp][r0 + i][0] = acc0[i];
+        partial[warp][r0 + i][1] = acc1[i];
       }
     }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < rows * 2; t += kSmallThreads) {
+    const int r = t >> 1, which = t & 1;
+    float sum = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < kSmallWarps; ++wv) sum += partial[wv][r][which];
+    if (e0 + which < experts) logits[static_cast<size_t>(r) * experts + e0 + which] = sum;
   }
 }
 
@@ -220,7 +253,7 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
                              cudaStream_t stream) {
   const dim3 grid(static_cast<unsigned>((rows + kTM - 1) / kTM), static_cast<unsigned>((experts + kTN - 1) / kTN));
   const int r = static_cast<int>(rows), h = static_cast<int>(hidden_dim), e = static_cast<int>(experts);
-  const bool small = hidden_bf16 && rows <= 128 && hidden_dim % 128 == 0 &&
+  const bool small = hidden_bf16 && rows <= kSmallMaxRows && hidden_dim <= 128 * kSmallWarps * kSmallMaxSteps && hidden_dim % 128 == 0 &&
                      reinterpret_cast<uintptr_t>(hidden) % 8 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
   if (small) {
     const unsigned ctas = static_cast<unsigned>((experts + 1) / 2);

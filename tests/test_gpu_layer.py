@@ -239,3 +239,30 @@ def test_glm52_shape_tc_matches_simt_at_bench_sizes(pkg, T):
     err = O.rel_l2_per_token(outs["tc"][0], outs["simt"][0])
     print(f"glm52 T={T}: tc vs simt max per-token rel L2 = {err.max():.3e}")
     assert err.max() <= 1e-2
+
+
+@pytest.mark.parametrize("T", [16, 300, 1000])
+def test_zipf_skewed_routing_matches_oracle(pkg, T):
+    """Load-skewed routing: a router bias makes expert popularity follow rank^-1.2, so a few experts
+    receive most rows (several token chunks each, some none).  T=16 is the speculative-verify
+    batch 4 x (1 + 3 drafts); the larger sizes take the 128-token chunk kernels."""
+    H, I, E, K = 512, 256, 16, 4
+    ref = O.make_layer(33, H, I, E)
+    # bias in logit space of the selection score: popular experts get a head start
+    pop = (np.arange(1, E + 1, dtype=np.float64) ** -1.2)
+    ref.bias = (0.35 * np.log(pop / pop.max())).astype(np.float32) * np.float32(0.25)
+    layer = make(pkg, ref, K, 1024, "tc")
+    hid = O.make_hidden(7000 + T, T, H)
+    out, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    layer.check()
+    oi, ow, oo = O.layer_forward(ref, hid, K, mode="O1")
+    gi = idx.cpu().numpy()
+    assert O.router_indices_equivalent(gi, oi, sel64(ref, hid))
+    counts = np.bincount(gi.reshape(-1), minlength=E)
+    assert counts.max() >= 2.5 * max(1, counts.min())          # the routing really is skewed
+    same = np.all(gi == oi.astype(np.int32), axis=1)
+    err = O.rel_l2_per_token(to_bits(out)[same], oo[same])
+    assert err.max() <= TOL
+    ec = layer.debug("EXPERT_COUNTS", np.int32)[:E]
+    np.testing.assert_array_equal(ec, counts)
+    layer.close()
