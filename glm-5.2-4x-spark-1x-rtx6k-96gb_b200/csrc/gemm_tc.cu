@@ -32,7 +32,7 @@
 namespace glmrt {
 namespace {
 
-constexpr int kThreadsTC = 224;   // producer, issuer 0, four epilogue warps, issuer 1
+constexpr int kThreadsTC = 192;   // producer, MMA issuer, four epilogue warps
 constexpr int kStageBytesK = 128;   // bytes of packed FP4 per row per pipeline stage (256 elements)
 constexpr int kTileRows = 128;      // weight rows per MMA tile (UMMA M)
 constexpr int kSfStageBytes = 2048; // 4 scale tiles of 512 B per operand per stage
@@ -83,6 +83,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       }
     }
   }
+}
+
+// Warp-uniform bounded wait: lane 0 polls, every lane learns the outcome and then observes the
+// (already complete) phase itself.  Keeps the calling warp converged.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  uint32_t ok = (threadIdx.x & 31) == 0 ? (mbar_wait(bar, parity, abort_flag) ? 1u : 0u) : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok != 0u) (void)mbar_try_wait(bar, parity);
+  return ok != 0u;
+}
+// One leader lane of a converged warp (the form the compiler recognises as warp-uniform issue).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0u;
 }
 
 // ---- TMA --------------------------------------------------------------------------------
@@ -173,13 +192,12 @@ struct Cfg {
   static constexpr int kSfbTiles = (kBN + 127) / 128;                      // scale tiles per k-block for B
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes + kNumA * kSfStageBytes + kSfbTiles * kSfStageBytes;
   static constexpr int kStages = (221184 / kStageBytes) > 10 ? 10 : (221184 / kStageBytes);
-  // Successive MMAs into one accumulator form a dependent chain; at decode sizes (tiny N) the
-  // chain latency, not the math, bounds the tensor pipe.  The k-blocks of a stage therefore
-  // rotate over kSplit independent accumulator sets that the epilogue adds in a fixed order.
-  static constexpr int kSplit = kBN <= 32 ? (kFC1 ? 2 : 4) : 1;
-  // With several accumulator sets the k-blocks are also divided between two issuing warps
-  // (tcgen05 instructions of one thread execute in order; two threads issue concurrently).
-  static constexpr int kIssuers = kSplit >= 2 ? 2 : 1;
+  // The k-blocks of a stage may rotate over kSplit independent accumulator sets, issued by
+  // kIssuers warps, that the epilogue adds in a fixed order.  Measured on B200: neither helps once
+  // the issuing warp stays converged and hands the instructions to one elected lane (elect.sync);
+  // issuing from a divergent `lane == 0` branch was what had limited the tensor pipe.  Both stay 1.
+  static constexpr int kSplit = 1;
+  static constexpr int kIssuers = 1;
   static constexpr int kSetCols = kNumA * kBN;                             // columns of one accumulator set
   static constexpr int kAccCols = kSplit * kSetCols;                       // accumulator columns per buffer
   static constexpr int kAccBufs = (2 * kAccCols + 16 * kNumA + 16 * kSfbTiles <= 512) ? 2 : 1;
@@ -293,10 +311,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         }
       }
     }
-  } else if (warp == 1 || warp == 6) {
-    // ================= MMA issuers =================
-    const int issuer = warp == 1 ? 0 : 1;
-    if (lane == 0 && issuer < C::kIssuers) {
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    const int issuer = 0;
+    if (issuer < C::kIssuers) {   // the whole warp runs the loop; one elected lane issues
       int stage = 0;
       uint32_t phase = 0;
       int abuf = 0;
@@ -310,17 +328,18 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         const uint32_t n_mma = static_cast<uint32_t>(max(16, (ch.tokens + 15) & ~15));
         const uint32_t idesc = idesc_nvf4(n_mma);
         const uint32_t sfb_q = static_cast<uint32_t>((ch.slot_base & 127) >> 5);  // 32-row quadrant inside the scale tile
-        if (!mbar_wait(&acc_empty[abuf], aphase ^ 1u, abort_flag)) { alive = false; break; }
+        if (!mbar_wait_warp(&acc_empty[abuf], aphase ^ 1u, abort_flag)) { alive = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + abuf * C::kAccCols;
         for (int ks = 0; ks < k_stages; ++ks) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { alive = false; break; }
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { alive = false; break; }
           tc_fence_after();
           uint8_t* st = smem + static_cast<size_t>(stage) * C::kStageBytes;
           const uint32_t s_a0 = smem_u32(st);
           const uint32_t s_b = s_a0 + C::kNumA * C::kABytes;
           const uint32_t s_sfa0 = s_b + C::kBBytes;
           const uint32_t s_sfb = s_sfa0 + C::kNumA * kSfStageBytes;
+          if (elect_one()) {
 #pragma unroll
           for (int kb = issuer; kb < 4; kb += C::kIssuers) {
             tc_copy_sf(t_sfa0 + kb * 4, desc_sf(s_sfa0 + kb * 512));
@@ -341,10 +360,13 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
                           sfb_addr, acc);
           }
           tc_commit(&empty_bar[stage]);  // frees the stage once the MMAs above have read it
+          }
+          __syncwarp();
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
-        tc_commit(&acc_full[abuf]);      // accumulators complete
+        if (elect_one()) tc_commit(&acc_full[abuf]);      // accumulators complete
+        __syncwarp();
         if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
       }
     }
