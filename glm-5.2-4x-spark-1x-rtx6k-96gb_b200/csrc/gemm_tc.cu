@@ -28,161 +28,12 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 #include "internal.h"
+#include "tc_ptx.cuh"
 
 namespace glmrt {
 namespace {
 
-constexpr int kThreadsTC = 192;   // producer, MMA issuer, four epilogue warps
-constexpr int kStageBytesK = 128;   // bytes of packed FP4 per row per pipeline stage (256 elements)
-constexpr int kTileRows = 128;      // weight rows per MMA tile (UMMA M)
-constexpr int kSfStageBytes = 2048; // 4 scale tiles of 512 B per operand per stage
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// ---- mbarrier ---------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this or another wait expired).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
-      if (*abort_flag != 0u) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1u;
-        return false;
-      }
-    }
-  }
-}
-
-// Warp-uniform bounded wait: lane 0 polls, every lane learns the outcome and then observes the
-// (already complete) phase itself.  Keeps the calling warp converged.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  uint32_t ok = (threadIdx.x & 31) == 0 ? (mbar_wait(bar, parity, abort_flag) ? 1u : 0u) : 0u;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (ok != 0u) (void)mbar_try_wait(bar, parity);
-  return ok != 0u;
-}
-// One leader lane of a converged warp (the form the compiler recognises as warp-uniform issue).
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0u;
-}
-
-// ---- TMA --------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y,
-                                            uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
-      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
-      : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar,
-                                          uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1], %2, [%3], %4;" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
-      : "memory");
-}
-__device__ __forceinline__ uint64_t policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-
-// ---- tcgen05 ----------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
-               "r"(cols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_copy_sf(uint32_t tmem_addr, uint64_t smem_desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]^T with per-16 UE4M3 block scales read from tensor memory.
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-      : "memory");
-}
-__device__ __forceinline__ void tc_load8(uint32_t taddr, uint32_t (&v)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-               : "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major rows of 128 bytes with the 128-byte swizzle TMA
-// wrote them with: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-  return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// Descriptor of one 512-byte scale tile (32 rows x 16 bytes, no swizzle, 8-row groups 128 B apart).
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-  return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (8ull << 32) | (1ull << 46);
-}
-// Instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major A and B, M = 128, N = n.
-__device__ __forceinline__ uint32_t idesc_nvf4(uint32_t n) {
-  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
+using namespace tc;
 
 template <bool kFC1, int kBN>
 struct Cfg {
@@ -503,8 +354,8 @@ glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_
                                      uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(GLMRT_STATUS_CUDA_UNAVAILABLE, "cuTensorMapEncodeTiled is not available");
-  if (row_bytes % 128 != 0 || reinterpret_cast<uintptr_t>(base) % 128 != 0 || box_rows == 0 || box_rows > 256)
-    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "tensor map: rows must be multiples of 128 bytes on a 128-byte aligned base");
+  if (row_bytes % 128 != 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0 || box_rows == 0 || box_rows > 256)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "tensor map: rows must be multiples of 128 bytes on a 16-byte aligned base");
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};
   const cuuint32_t box[2] = {128, box_rows};
@@ -518,13 +369,11 @@ glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_
 
 glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
   if (a.chunk_tokens == 32) return launch_one<true, 32>(a, m.gate, m.up, m.act1, sm_count, stream);
-  if (a.chunk_tokens == 128) return launch_one<true, 128>(a, m.gate, m.up, m.act1, sm_count, stream);
   return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
 }
 
 glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
   if (a.chunk_tokens == 32) return launch_one<false, 32>(a, m.down, m.down, m.act2, sm_count, stream);
-  if (a.chunk_tokens == 128) return launch_one<false, 128>(a, m.down, m.down, m.act2, sm_count, stream);
   return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
 }
 

@@ -25,9 +25,12 @@ struct Layer {
   std::vector<void*> allocations;
   // weights (local experts stacked)
   uint8_t *gate_codes = nullptr, *up_codes = nullptr, *down_codes = nullptr;
-  uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr;
+  uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr, *gu_sf64 = nullptr;
   float* scale2 = nullptr;
   float *router_w = nullptr, *router_b = nullptr;
+  uint16_t* router_w3 = nullptr;   // [experts, 3 * hidden] bf16 split of router_w for the tensor-core router
+  CUtensorMap map_w3{};
+  bool have_w3 = false;
   // work buffers
   float *logits = nullptr, *topk_w = nullptr, *topk_scores = nullptr;
   uint32_t* topk_idx = nullptr;
@@ -41,7 +44,7 @@ struct Layer {
   uint16_t *hidden_stage = nullptr, *out_stage = nullptr;
   // scratch for weight loading
   float* wtmp = nullptr;
-  uint8_t* sftmp = nullptr;
+  uint8_t *sftmp = nullptr, *sftmp2 = nullptr;
   uint32_t* amax_tmp = nullptr;
   TensorMaps maps32{}, maps128{};
   bool have_maps = false;
@@ -126,6 +129,8 @@ glmrt_status_t build_maps(Layer* l) {
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->gate, l->gate_codes, wrows_fc1, c.hidden_dim / 2, 128));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->up, l->up_codes, wrows_fc1, c.hidden_dim / 2, 128));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->down, l->down_codes, wrows_fc2, c.intermediate_dim / 2, 128));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->gate64, l->gate_codes, wrows_fc1, c.hidden_dim / 2, 64));
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->up64, l->up_codes, wrows_fc1, c.hidden_dim / 2, 64));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act1, l->act1_codes, l->max_slots, c.hidden_dim / 2, box));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act2, l->act2_codes, l->max_slots, c.intermediate_dim / 2, box));
   }
@@ -137,6 +142,7 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
   FfnArgs a{};
   a.gate_codes = l->gate_codes; a.up_codes = l->up_codes; a.down_codes = l->down_codes;
   a.gate_sf = l->gate_sf; a.up_sf = l->up_sf; a.down_sf = l->down_sf;
+  a.gu_sf64 = l->gu_sf64;
   a.scale2 = l->scale2;
   a.act1_codes = l->act1_codes; a.act1_sf = l->act1_sf;
   a.act2_codes = l->act2_codes; a.act2_sf = l->act2_sf;
@@ -146,6 +152,20 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
   a.max_chunks = l->max_chunks; a.chunk_tokens = chunk_tokens;
   a.error_word = l->counters + kCntError;
   return a;
+}
+
+// Router: tensor-core logits for prefill-sized batches, SIMT kernels otherwise.
+glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_t s) {
+  const auto& c = l->cfg;
+  if (l->have_w3 && router_tc_supported(rows, c.hidden_dim, c.experts, hidden)) {
+    GLMRT_RETURN_IF_ERROR(launch_router_logits_tc(static_cast<const uint16_t*>(hidden), l->map_w3, l->logits, rows,
+                                                  c.hidden_dim, c.experts, l->counters + kCntRouterError,
+                                                  l->sm_count, s));
+    return launch_router_select(l->logits, l->router_b, l->topk_idx, l->topk_scores, l->topk_w, rows, c.experts,
+                                c.top_k, c.routed_scaling, s);
+  }
+  return launch_router(hidden, true, l->router_w, false, l->router_b, l->logits, l->topk_idx, l->topk_scores,
+                       l->topk_w, rows, c.hidden_dim, c.experts, c.top_k, c.routed_scaling, s);
 }
 
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
@@ -179,9 +199,11 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   } else {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
     const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
-    GLMRT_RETURN_IF_ERROR(launch_fc1_tc(f, maps, l->sm_count, stream));
+    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, stream)
+                                             : launch_fc1_tc_prefill(f, maps, l->sm_count, stream));
     mark(l, GLMRT_B200_STAGE_FC2, stream);
-    GLMRT_RETURN_IF_ERROR(launch_fc2_tc(f, maps, l->sm_count, stream));
+    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, stream)
+                                             : launch_fc2_tc_prefill(f, maps, l->sm_count, stream));
   }
   mark(l, GLMRT_B200_STAGE_COMBINE, stream);
   // with one shard every route is local; a shard of an expert-parallel layer only sums its own
@@ -238,9 +260,11 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->gate_sf, E * I * H / 16));
   A(dev_alloc(l, &l->up_sf, E * I * H / 16));
   A(dev_alloc(l, &l->down_sf, E * H * I / 16));
+  A(dev_alloc(l, &l->gu_sf64, 2 * E * I * H / 16));
   A(dev_alloc(l, &l->scale2, E * 3, true));
   A(dev_alloc(l, &l->router_w, static_cast<size_t>(c.experts) * H, true));
   A(dev_alloc(l, &l->router_b, c.experts, true));
+  A(dev_alloc(l, &l->router_w3, static_cast<size_t>(c.experts) * 3 * H, true));
   A(dev_alloc(l, &l->logits, T * c.experts));
   A(dev_alloc(l, &l->topk_w, routes));
   A(dev_alloc(l, &l->topk_scores, routes));
@@ -262,6 +286,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->out_stage, T * H));
   A(dev_alloc(l, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
   A(dev_alloc(l, &l->sftmp, I * H / 16));
+  A(dev_alloc(l, &l->sftmp2, I * H / 16));
   A(dev_alloc(l, &l->amax_tmp, 1, true));
   if (c.ep_world > 1) A(dev_alloc(l, &l->ep_ctrl, 1, true));
   if (st != GLMRT_STATUS_OK) {
@@ -290,6 +315,12 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_dev
   cudaError_t err = cudaMemcpyAsync(l->router_w, weight_f32.ptr, wbytes, cudaMemcpyDeviceToDevice, s);
   if (err == cudaSuccess) err = cudaMemcpyAsync(l->router_b, bias_f32.ptr, bbytes, cudaMemcpyDeviceToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_router copy", err);
+  GLMRT_RETURN_IF_ERROR(launch_split_router_weight(l->router_w, l->router_w3, l->cfg.experts, l->cfg.hidden_dim, s));
+  if (!l->have_w3 && l->cfg.experts % 128 == 0 && l->cfg.hidden_dim % 64 == 0) {
+    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&l->map_w3, l->router_w3, l->cfg.experts,
+                                                static_cast<uint64_t>(l->cfg.hidden_dim) * 3 * 2, 128));
+    l->have_w3 = true;
+  }
   return ok();
 }
 
@@ -321,6 +352,9 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_set_expert(
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(gate_scales.ptr), l->gate_sf, I, H / 16, le * I, s));
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(up_scales.ptr), l->up_sf, I, H / 16, le * I, s));
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(down_scales.ptr), l->down_sf, H, I / 16, le * H, s));
+  GLMRT_RETURN_IF_ERROR(launch_tile_scales_stacked64(static_cast<const uint8_t*>(gate_scales.ptr),
+                                                     static_cast<const uint8_t*>(up_scales.ptr), l->gu_sf64, I, H / 16,
+                                                     le * (I / 64), s));
   const float s2[3] = {gate_scale_2, up_scale_2, down_scale_2};
   err = cudaMemcpyAsync(l->scale2 + le * 3, s2, sizeof(s2), cudaMemcpyHostToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_expert scale copy", err);
@@ -344,9 +378,13 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_fill_synthetic(void* layer, uint6
       uint8_t* codes = t == 0 ? l->gate_codes : t == 1 ? l->up_codes : l->down_codes;
       uint8_t* sf = t == 0 ? l->gate_sf : t == 1 ? l->up_sf : l->down_sf;
       const size_t rows = t == 2 ? H : I, cols = t == 2 ? I : H;
-      GLMRT_RETURN_IF_ERROR(launch_quantize_weight_f32(l->wtmp, codes + static_cast<size_t>(le) * n / 2, l->sftmp,
+      uint8_t* rowmajor = t == 1 ? l->sftmp2 : l->sftmp;   // gate scales survive until up is done
+      GLMRT_RETURN_IF_ERROR(launch_quantize_weight_f32(l->wtmp, codes + static_cast<size_t>(le) * n / 2, rowmajor,
                                                        l->scale2 + le * 3 + t, l->amax_tmp, rows, cols, s));
-      GLMRT_RETURN_IF_ERROR(launch_tile_scales(l->sftmp, sf, rows, cols / 16, static_cast<size_t>(le) * rows, s));
+      GLMRT_RETURN_IF_ERROR(launch_tile_scales(rowmajor, sf, rows, cols / 16, static_cast<size_t>(le) * rows, s));
+      if (t == 1)
+        GLMRT_RETURN_IF_ERROR(launch_tile_scales_stacked64(l->sftmp, l->sftmp2, l->gu_sf64, I, H / 16,
+                                                           static_cast<size_t>(le) * (I / 64), s));
     }
   }
   return ok();
@@ -372,9 +410,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_async(void* layer, glmrt_
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
   const uint64_t before = launches_total();
   mark(l, GLMRT_B200_STAGE_ROUTER, s);
-  GLMRT_RETURN_IF_ERROR(launch_router(hidden_bf16.ptr, true, l->router_w, false, l->router_b, l->logits, l->topk_idx,
-                                      l->topk_scores, l->topk_w, rows, l->cfg.hidden_dim, l->cfg.experts,
-                                      l->cfg.top_k, l->cfg.routed_scaling, s));
+  GLMRT_RETURN_IF_ERROR(run_router(l, hidden_bf16.ptr, rows, s));
   GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
                                    static_cast<uint16_t*>(output_bf16.ptr), s));
   l->launches_last = static_cast<uint32_t>(launches_total() - before);
@@ -438,7 +474,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_check(void* layer, void* cuda_str
   cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
   if (err == cudaSuccess) err = cudaMemcpy(host, l->counters, sizeof(host), cudaMemcpyDeviceToHost);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "layer check", err);
-  const uint32_t e = host[kCntError];
+  const uint32_t e = host[kCntError] | host[kCntRouterError];
   if (e == 0) return ok();
   std::string msg = "device reported:";
   if (e & kErrWaitTimeout) msg += " a bounded wait expired;";
@@ -497,7 +533,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_lay
   out->chunks = host[kCntChunks];
   out->slots = host[kCntSlots];
   out->distinct_experts = host[kCntDistinct];
-  out->device_error = host[kCntError];
+  out->device_error = host[kCntError] | host[kCntRouterError];
   return ok();
 }
 
@@ -560,9 +596,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
     case 0: {
       mark(l, GLMRT_B200_STAGE_ROUTER, s);
       if (rows > 0)
-        GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, l->router_w, false, l->router_b, l->logits, l->topk_idx,
-                                            l->topk_scores, l->topk_w, rows, c.hidden_dim, c.experts, c.top_k,
-                                            c.routed_scaling, s));
+        GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s));
       mark(l, GLMRT_B200_STAGE_QUANTIZE, s);
       if (rows > 0)
         GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
@@ -597,9 +631,11 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       } else {
         if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
         const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
-        GLMRT_RETURN_IF_ERROR(launch_fc1_tc(f, maps, l->sm_count, s));
+        GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, s)
+                                                 : launch_fc1_tc_prefill(f, maps, l->sm_count, s));
         mark(l, GLMRT_B200_STAGE_FC2, s);
-        GLMRT_RETURN_IF_ERROR(launch_fc2_tc(f, maps, l->sm_count, s));
+        GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, s)
+                                                 : launch_fc2_tc_prefill(f, maps, l->sm_count, s));
       }
       mark(l, GLMRT_B200_STAGE_COMBINE, s);
       return launch_ep_signal(a, 1, s);   // results of this owner have been stored to their home ranks

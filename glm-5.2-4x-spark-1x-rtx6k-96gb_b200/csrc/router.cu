@@ -275,10 +275,17 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
   else
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: float32 hidden with bf16 weights is not supported");
   GLMRT_LAUNCH_CHECK("router_logits_kernel");
+  return launch_router_select(logits, bias, idx, scores, weights, rows, experts, top_k, scaling, stream);
+}
+
+glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
+                                    float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
+                                    cudaStream_t stream) {
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * 2 * experts * sizeof(float);
   router_select_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, smem, stream>>>(
-      logits, bias, idx, scores, weights, r, e, static_cast<int>(top_k), scaling);
+      logits, bias, idx, scores, weights, static_cast<int>(rows), static_cast<int>(experts),
+      static_cast<int>(top_k), scaling);
   GLMRT_LAUNCH_CHECK("router_select_kernel");
   return GLMRT_STATUS_OK;
 }

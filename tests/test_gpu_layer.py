@@ -266,3 +266,30 @@ def test_zipf_skewed_routing_matches_oracle(pkg, T):
     ec = layer.debug("EXPERT_COUNTS", np.int32)[:E]
     np.testing.assert_array_equal(ec, counts)
     layer.close()
+
+
+@pytest.mark.parametrize("T", [129, 1024, 4100])
+def test_tensor_core_router_matches_oracle_at_prefill_sizes(pkg, T):
+    """Above 128 rows the logits come from the bf16 x (hi|mid|lo) tensor-core GEMM; indices must
+    agree with the float32 oracle up to 1e-6 near-ties, weights to float32 round-off."""
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K = 6144, 256, 256, 8
+    rng = np.random.default_rng(T)
+    rw = (rng.standard_normal((E, H), np.float32) * np.float32(0.02)).astype(np.float32)
+    bias = (rng.standard_normal(E, np.float32) * np.float32(0.01)).astype(np.float32)
+    layer = MoeLayer(H, I, E, K, max_tokens=T)
+    layer.fill_synthetic(3, 0.02)
+    layer.set_router(torch.from_numpy(rw), torch.from_numpy(bias))
+    hid = O.make_hidden(T, T, H)
+    out, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    layer.check()
+    oi, ow, _, _ = O.router_topk(O.bf16_to_f32(hid), rw, bias, K)
+    x64 = O.bf16_to_f32(hid).astype(np.float64)
+    s64 = 1.0 / (1.0 + np.exp(-(x64 @ rw.astype(np.float64).T))) + bias
+    gi = idx.cpu().numpy()
+    assert O.router_indices_equivalent(gi, oi, s64, tol=1e-6)
+    same = np.all(gi == oi.astype(np.int32), axis=1)
+    assert same.mean() > 0.98
+    np.testing.assert_allclose(w.cpu().numpy()[same], ow[same], atol=3e-6, rtol=1e-5)
+    assert torch.isfinite(out.float()).all()
+    layer.close()
