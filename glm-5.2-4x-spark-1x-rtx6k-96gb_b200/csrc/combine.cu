@@ -27,20 +27,34 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-  for (int k = 0; k < top_k; ++k) {
-    const int r = row * top_k + k;
-    if (route_slot != nullptr && route_slot[r] < 0) continue;
-    const float w = bf16_bits_to_f32(f32_to_bf16_rne(topk_weights[r]));
-    const uint4 y4 = reinterpret_cast<const uint4*>(route_rows + static_cast<size_t>(r) * hidden)[v];
-    const uint32_t yw[4] = {y4.x, y4.y, y4.z, y4.w};
+  // rows are fetched eight routes at a time before any arithmetic, so the loads overlap
+  for (int k0 = 0; k0 < top_k; k0 += 8) {
+    uint4 y4[8];
+    float w[8];
+    bool use[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float y0 = __uint_as_float(yw[i] << 16);
-      const float y1 = __uint_as_float(yw[i] & 0xffff0000u);
-      const float p0 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w, y0)));
-      const float p1 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w, y1)));
-      acc[2 * i] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i], p0)));
-      acc[2 * i + 1] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i + 1], p1)));
+    for (int j = 0; j < 8; ++j) {
+      const int k = k0 + j;
+      const int r = row * top_k + k;
+      use[j] = k < top_k && (route_slot == nullptr || route_slot[r] >= 0);
+      if (use[j]) {
+        y4[j] = reinterpret_cast<const uint4*>(route_rows + static_cast<size_t>(r) * hidden)[v];
+        w[j] = bf16_bits_to_f32(f32_to_bf16_rne(topk_weights[r]));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (!use[j]) continue;
+      const uint32_t yw[4] = {y4[j].x, y4[j].y, y4[j].z, y4[j].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float y0 = __uint_as_float(yw[i] << 16);
+        const float y1 = __uint_as_float(yw[i] & 0xffff0000u);
+        const float p0 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w[j], y0)));
+        const float p1 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w[j], y1)));
+        acc[2 * i] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i], p0)));
+        acc[2 * i + 1] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i + 1], p1)));
+      }
     }
   }
   uint4 o;

@@ -2,6 +2,7 @@
 // numeric formats of the routed-MoE path (E2M1 codes, E4M3 scales, bf16).
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -50,12 +51,9 @@ inline bool checked_mul(size_t a, size_t b, size_t* out) {
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t v) {
   return __uint_as_float(static_cast<uint32_t>(v) << 16);
 }
-// Round-to-nearest-even (torch semantics; the Python oracle's rounding).
+// Round-to-nearest-even (torch semantics; the Python oracle's rounding): one cvt.rn.bf16.f32.
 __device__ __forceinline__ uint16_t f32_to_bf16_rne(float f) {
-  uint32_t u = __float_as_uint(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x40u);
-  u += 0x7fffu + ((u >> 16) & 1u);
-  return static_cast<uint16_t>(u >> 16);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 // Truncation (the reference's native kernels: native/cuda/kernels/common.h:64-66).
 __device__ __forceinline__ uint16_t f32_to_bf16_trunc(float f) {

@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(128) simt_fc1_kernel(FfnArgs a) {
     }
     const float g = __fmul_rn(static_cast<float>(accg), sg2);
     const float u = __fmul_rn(static_cast<float>(accu), su2);
-    swiglu_requant_store(g, u, f, slot, a.inter, a.act2_codes, a.act2_sf);
+    swiglu_requant_store<false>(g, u, f, slot, a.inter, a.act2_codes, a.act2_sf);
   }
 }
 

@@ -268,7 +268,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < ch.tokens)  // uniform across the warp
-              swiglu_requant_store(__fmul_rn(__uint_as_float(g[j]), s2a), __fmul_rn(__uint_as_float(u[j]), s2b),
+              swiglu_requant_store<true>(__fmul_rn(__uint_as_float(g[j]), s2a), __fmul_rn(__uint_as_float(u[j]), s2b),
                                    feature, static_cast<size_t>(ch.slot_base) + c0 + j, a.inter, a.act2_codes,
                                    a.act2_sf);
           }

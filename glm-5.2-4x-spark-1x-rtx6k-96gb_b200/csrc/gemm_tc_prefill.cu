@@ -18,7 +18,10 @@
 // cache are as in gemm_tc.cu.  TMA loads read local memory only and use no cluster multicast.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
+#include "epilogue.cuh"
 #include "internal.h"
 #include "tc_ptx.cuh"
 
@@ -27,15 +30,31 @@ namespace {
 
 using namespace tc;
 
-constexpr int kPfStages = 6;
-constexpr int kPfABytes = 128 * kStageBytesK;   // 128 token rows
-constexpr int kPfBBytes = 128 * kStageBytesK;   // 128 weight rows
-constexpr int kPfStageBytes = kPfABytes + kPfBBytes + 2 * kSfStageBytes;   // 36 KiB
-constexpr int kPfChunkCache = 256;
-constexpr size_t kPfSmemBytes = static_cast<size_t>(kPfStages) * kPfStageBytes + 1024 + 256 + kPfChunkCache * sizeof(Chunk);
-constexpr int kPfAccCols = 128;
-constexpr int kPfSfCol = 2 * kPfAccCols;        // scales after the two accumulator buffers
-constexpr int kPfTmemCols = 512;
+// Tile geometry.  kWN = weight rows (UMMA N) per tile: 128 (64 gate + 64 up for FC1) with the
+// accumulators double-buffered, or 256 (128 gate + 128 up) with a single accumulator buffer: twice
+// the math per scale copy and per byte brought into shared memory, at the price of an epilogue
+// that no longer overlaps the MMAs.
+template <bool kFC1, int kWN>
+struct PfCfg {
+  static constexpr int kBTiles = kWN / 128;                          // 128-row boxes / scale tiles of B
+  static constexpr int kABytes = 128 * kStageBytesK;                 // 128 token rows
+  static constexpr int kBBytes = kWN * kStageBytesK;
+  static constexpr int kStageBytes = kABytes + kBBytes + (1 + kBTiles) * kSfStageBytes;
+  static constexpr int kStages = 221184 / kStageBytes;               // 6 (N=128) or 4 (N=256)
+  static constexpr int kAccBufs = kWN == 128 ? 2 : 1;
+  static constexpr int kSfSetCols = 16 + 16 * kBTiles;               // scale columns of one stage
+  static constexpr int kSfCol = kAccBufs * kWN;                      // two alternating sets follow the accumulators
+  static constexpr int kTmemCols = 512;
+  static constexpr int kFeatPerTile = kFC1 ? kWN / 2 : kWN;
+  // The FC1 epilogue is arithmetic-heavy (SwiGLU, quantisation): with one warp per scheduler it
+  // could not hide its own latencies and bounded the kernel, so it gets sixteen warps, four per
+  // tensor-memory quadrant.  FC2's scale-and-round needs one warp per 128 columns and quadrant.
+  static constexpr int kEpiWarps = kFC1 ? 16 : 4 * kBTiles;
+  static constexpr int kParts = kEpiWarps / 4;
+  static constexpr int kThreads = 32 * (2 + kEpiWarps);
+  static constexpr int kChunkCache = 256;
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk);
+};
 
 __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
@@ -46,16 +65,17 @@ __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 
-template <bool kFC1>
-__global__ void __launch_bounds__(kThreadsTC, 1)
+template <bool kFC1, int kWN>
+__global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
 expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act,
                           const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1) {
+  using C = PfCfg<kFC1, kWN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kPfStages) * kPfStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + kPfStages;
-  uint64_t* acc_full = bars + 2 * kPfStages;
+  uint64_t* empty_bar = bars + C::kStages;
+  uint64_t* acc_full = bars + 2 * C::kStages;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -66,24 +86,23 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   const int k_bytes = (kFC1 ? a.hidden : a.inter) / 2;
   const int k_stages = k_bytes / kStageBytesK;
   const int k_tiles64 = k_bytes / 32;
-  const int feat_per_tile = kFC1 ? 64 : 128;
   const int out_rows = kFC1 ? a.inter : a.hidden;
-  const int feat_tiles = out_rows / feat_per_tile;
+  const int feat_tiles = out_rows / C::kFeatPerTile;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPfStages; ++s) {
+    for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);
+      mbar_init(&acc_empty[b], C::kEpiWarps);
     }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  if (warp == 1) tmem_alloc(tmem_slot, kPfTmemCols);
+  if (warp == 1) tmem_alloc(tmem_slot, C::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -91,21 +110,19 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
 
   const int num_chunks = static_cast<int>(a.counters[kCntChunks]);
   const int num_tiles = num_chunks * feat_tiles;
-  for (int i = threadIdx.x; i < kPfChunkCache; i += kThreadsTC) {
+  for (int i = threadIdx.x; i < C::kChunkCache; i += C::kThreads) {
     const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
     if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
   }
   __syncthreads();
   auto chunk_of = [&](int it, int tile) -> Chunk {
-    return it < kPfChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
+    return it < C::kChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
   };
 
   if (warp == 0) {
     // ================= TMA producer =================
-    const uint64_t pol_w = policy_evict_last();   // a weight tile is used by every chunk of its expert
-    const uint64_t pol_x = policy_evict_last();   // a chunk's rows are used by every feature tile
+    const uint64_t pol = policy_evict_last();   // weight tiles serve every chunk of their expert, rows every feature tile
     const uint8_t* sfa = kFC1 ? a.act1_sf : a.act2_sf;
-    const uint8_t* sfb = kFC1 ? a.gu_sf64 : a.down_sf;
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -113,30 +130,45 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
       const Chunk ch = chunk_of(it, tile);
       const int ft = tile % feat_tiles;
-      const int w_row = ch.expert * out_rows + ft * feat_per_tile;
+      const int w_row = ch.expert * out_rows + ft * C::kFeatPerTile;   // first weight row (per projection)
       const size_t sfa_tile0 = static_cast<size_t>(ch.slot_base / 128) * k_tiles64;
-      const size_t sfb_tile0 =
-          (kFC1 ? static_cast<size_t>(ch.expert) * feat_tiles + ft : static_cast<size_t>(w_row / 128)) * k_tiles64;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
         if (elect_one()) {
-          const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * kPfStageBytes);
-          const uint32_t s_b = s_a + kPfABytes;
-          const uint32_t s_sfa = s_b + kPfBBytes;
+          const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
+          const uint32_t s_b = s_a + C::kABytes;
+          const uint32_t s_sfa = s_b + C::kBBytes;
           const uint32_t s_sfb = s_sfa + kSfStageBytes;
-          mbar_expect_tx(&full_bar[stage], kPfStageBytes);
-          tma_load_2d(s_a, &map_act, &full_bar[stage], ks * kStageBytesK, ch.slot_base, pol_x);
-          if (kFC1) {
-            tma_load_2d(s_b, &map_w0, &full_bar[stage], ks * kStageBytesK, w_row, pol_w);                // 64 gate rows
-            tma_load_2d(s_b + 64 * kStageBytesK, &map_w1, &full_bar[stage], ks * kStageBytesK, w_row, pol_w);  // 64 up rows
+          const int kx = ks * kStageBytesK;
+          const size_t ksf = static_cast<size_t>(ks) * 4;
+          mbar_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(s_a, &map_act, &full_bar[stage], kx, ch.slot_base, pol);
+          bulk_load(s_sfa, sfa + (sfa_tile0 + ksf) * 512, kSfStageBytes, &full_bar[stage], pol);
+          if (kFC1 && kWN == 128) {
+            // 64 gate rows stacked on 64 up rows; their scales are pre-tiled in the same stacking
+            tma_load_2d(s_b, &map_w0, &full_bar[stage], kx, w_row, pol);
+            tma_load_2d(s_b + 64 * kStageBytesK, &map_w1, &full_bar[stage], kx, w_row, pol);
+            bulk_load(s_sfb, a.gu_sf64 + ((static_cast<size_t>(ch.expert) * feat_tiles + ft) * k_tiles64 + ksf) * 512,
+                      kSfStageBytes, &full_bar[stage], pol);
+          } else if (kFC1) {
+            // 128 gate rows, then 128 up rows, each with its own scale tile
+            tma_load_2d(s_b, &map_w0, &full_bar[stage], kx, w_row, pol);
+            tma_load_2d(s_b + 128 * kStageBytesK, &map_w1, &full_bar[stage], kx, w_row, pol);
+            const size_t t0 = static_cast<size_t>(w_row / 128) * k_tiles64 + ksf;
+            bulk_load(s_sfb, a.gate_sf + t0 * 512, kSfStageBytes, &full_bar[stage], pol);
+            bulk_load(s_sfb + kSfStageBytes, a.up_sf + t0 * 512, kSfStageBytes, &full_bar[stage], pol);
           } else {
-            tma_load_2d(s_b, &map_w0, &full_bar[stage], ks * kStageBytesK, w_row, pol_w);                // 128 down rows
+#pragma unroll
+            for (int t = 0; t < C::kBTiles; ++t) {
+              tma_load_2d(s_b + t * 128 * kStageBytesK, &map_w0, &full_bar[stage], kx, w_row + t * 128, pol);
+              bulk_load(s_sfb + t * kSfStageBytes,
+                        a.down_sf + ((static_cast<size_t>(w_row / 128) + t) * k_tiles64 + ksf) * 512, kSfStageBytes,
+                        &full_bar[stage], pol);
+            }
           }
-          bulk_load(s_sfa, sfa + (sfa_tile0 + static_cast<size_t>(ks) * 4) * 512, kSfStageBytes, &full_bar[stage], pol_x);
-          bulk_load(s_sfb, sfb + (sfb_tile0 + static_cast<size_t>(ks) * 4) * 512, kSfStageBytes, &full_bar[stage], pol_w);
         }
         __syncwarp();
-        if (++stage == kPfStages) { stage = 0; phase ^= 1u; }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
@@ -146,45 +178,49 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     int abuf = 0;
     uint32_t aphase = 0;
     bool alive = true;
-    const uint32_t t_sfa = tmem_base + kPfSfCol;
-    const uint32_t t_sfb = t_sfa + 16;
-    const uint32_t idesc = idesc_nvf4(128);
+    const uint32_t idesc = idesc_nvf4(kWN);
+    uint32_t sf_flip = 0;   // scale columns alternate between two sets: copies of one stage run under the MMAs of the previous
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       if (!mbar_wait_warp(&acc_empty[abuf], aphase ^ 1u, abort_flag)) { alive = false; break; }
       tc_fence_after();
-      const uint32_t d0 = tmem_base + abuf * kPfAccCols;
+      const uint32_t d0 = tmem_base + abuf * kWN;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { alive = false; break; }
         tc_fence_after();
+        const uint32_t t_sfa = tmem_base + C::kSfCol + sf_flip * C::kSfSetCols;
+        const uint32_t t_sfb = t_sfa + 16;
+        sf_flip ^= 1u;
         if (elect_one()) {
-          const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * kPfStageBytes);
-          const uint32_t s_b = s_a + kPfABytes;
-          const uint32_t s_sfa = s_b + kPfBBytes;
+          const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
+          const uint32_t s_b = s_a + C::kABytes;
+          const uint32_t s_sfa = s_b + C::kBBytes;
           const uint32_t s_sfb = s_sfa + kSfStageBytes;
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             tc_copy_sf(t_sfa + kb * 4, desc_sf(s_sfa + kb * 512));
-            tc_copy_sf(t_sfb + kb * 4, desc_sf(s_sfb + kb * 512));
+#pragma unroll
+            for (int t = 0; t < C::kBTiles; ++t)   // rows 128t.. of B live in columns 4t.. of the k-block's group
+              tc_copy_sf(t_sfb + kb * 4 * C::kBTiles + t * 4, desc_sf(s_sfb + t * kSfStageBytes + kb * 512));
           }
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
             tc_mma_nvf4(d0, desc_sw128(s_a + kb * 32), desc_sw128(s_b + kb * 32), idesc, t_sfa + kb * 4,
-                        t_sfb + kb * 4, (ks | kb) != 0 ? 1u : 0u);
+                        t_sfb + kb * 4 * C::kBTiles, (ks | kb) != 0 ? 1u : 0u);
           tc_commit(&empty_bar[stage]);
         }
         __syncwarp();
-        if (++stage == kPfStages) { stage = 0; phase ^= 1u; }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
       if (!alive) break;
       if (elect_one()) tc_commit(&acc_full[abuf]);
       __syncwarp();
-      abuf ^= 1;
-      if (abuf == 0) aphase ^= 1u;
+      if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }
   } else {
-    // ================= epilogue (warps 2..5): one thread per token slot =================
-    const int quad = warp & 3;
-    const int row = quad * 32 + lane;                 // token slot inside the chunk = tensor-memory lane
+    // ================= epilogue: one thread per (token slot, share of the columns) =================
+    const int quad = warp & 3;                        // tensor-memory lanes 32*quad .. 32*quad+31
+    const int part = (warp - 2) >> 2;                 // which share of the tile's columns
+    const int row = quad * 32 + lane;                 // token slot inside the chunk
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     int abuf = 0;
     uint32_t aphase = 0;
@@ -200,42 +236,30 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       uint16_t* dst = (!kFC1 && valid) ? a.slot_out[slot] : nullptr;
       if (!mbar_wait_warp(&acc_full[abuf], aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
-      const uint32_t t_acc = tmem_base + lane_base + abuf * kPfAccCols;
+      const uint32_t t_acc = tmem_base + lane_base + abuf * kWN;
       if (kFC1) {
-        uint32_t sbytes = 0;
+        // gate occupies columns [0, kWN/2), up [kWN/2, kWN); 16 warps share the 16-feature blocks
+        constexpr int kBlocksPerWarp = (kWN / 32) / C::kParts;   // 1 (N=128) or 2 (N=256)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {              // four 16-feature blocks of this 64-feature tile
+        for (int j = 0; j < kBlocksPerWarp; ++j) {
+          const int b = part * kBlocksPerWarp + j;
           uint32_t g[16], u[16];
           tc_load16(t_acc + b * 16, g);
-          tc_load16(t_acc + 64 + b * 16, u);
+          tc_load16(t_acc + kWN / 2 + b * 16, u);
           tc_wait_ld();
-          float v[16];
-          float amax = 0.0f;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float gg = __fmul_rn(__uint_as_float(g[i]), s2a);
-            const float uu = __fmul_rn(__uint_as_float(u[i]), s2b);
-            v[i] = __fmul_rn(__fmul_rn(gg, sigmoid_f32(gg)), uu);   // moe_ref.py:18-20
-            amax = fmaxf(amax, fabsf(v[i]));
-          }
-          const uint32_t sbyte = f32_to_e4m3_satfinite(__fdiv_rn(amax, 6.0f));
-          const float scale = e4m3_to_f32(sbyte);
-          uint32_t lo = 0, hi = 0;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint32_t c = scale == 0.0f ? 0u : fp4_code_nearest_low(__fdiv_rn(v[i], scale));
-            if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-          }
-          sbytes |= sbyte << (8 * b);
-          if (valid)
-            *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + (ft * 64 + b * 16) / 2) =
+          uint32_t lo, hi, sbyte;
+          swiglu_requant_block16(g, u, s2a, s2b, lo, hi, sbyte);
+          if (valid) {
+            const int feature = ft * C::kFeatPerTile + b * 16;
+            *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + feature / 2) =
                 make_uint2(lo, hi);
+            a.act2_sf[sf_tile_offset(slot, feature / 16, a.inter / 16)] = static_cast<uint8_t>(sbyte);
+          }
         }
-        // the four scale bytes of this tile are consecutive in the tiled layout (blocks ft*4 .. ft*4+3)
-        if (valid) *reinterpret_cast<uint32_t*>(a.act2_sf + sf_tile_offset(slot, ft * 4, a.inter / 16)) = sbytes;
       } else {
+        constexpr int kColsPerPart = kWN / C::kParts;   // 128
 #pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 16) {
+        for (int c0 = part * kColsPerPart; c0 < (part + 1) * kColsPerPart; c0 += 16) {
           uint32_t y[16];
           tc_load16(t_acc + c0, y);
           tc_wait_ld();
@@ -245,7 +269,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
             for (int i = 0; i < 8; ++i)
               w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[2 * i]), s2a))) |
                      (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[2 * i + 1]), s2a))) << 16);
-            uint4* d4 = reinterpret_cast<uint4*>(dst + ft * 128 + c0);
+            uint4* d4 = reinterpret_cast<uint4*>(dst + ft * C::kFeatPerTile + c0);
             d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
             d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
           }
@@ -254,8 +278,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[abuf]);
-      abuf ^= 1;
-      if (abuf == 0) aphase ^= 1u;
+      if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }
   }
 
@@ -267,32 +290,48 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kPfTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
-template <bool kFC1>
+template <bool kFC1, int kWN>
 glmrt_status_t launch_tokens(const FfnArgs& a, const CUtensorMap& act, const CUtensorMap& w0, const CUtensorMap& w1,
                              int sm_count, cudaStream_t stream) {
+  using C = PfCfg<kFC1, kWN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(expert_gemm_tokens_kernel<kFC1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kPfSmemBytes));
+    cudaError_t err = cudaFuncSetAttribute(expert_gemm_tokens_kernel<kFC1, kWN>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C::kSmemBytes));
     if (err != cudaSuccess)
       return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)", err);
     configured = true;
   }
-  expert_gemm_tokens_kernel<kFC1><<<sm_count, kThreadsTC, kPfSmemBytes, stream>>>(a, act, w0, w1);
+  expert_gemm_tokens_kernel<kFC1, kWN><<<sm_count, C::kThreads, C::kSmemBytes, stream>>>(a, act, w0, w1);
   GLMRT_LAUNCH_CHECK("expert_gemm_tokens_kernel");
   return GLMRT_STATUS_OK;
+}
+
+// Tile width: 256 weight rows by default; GLMRT_B200_PREFILL_TILE_N=128 selects the narrower,
+// double-buffered tile (kept for comparison and for shapes whose dimensions 256 does not divide).
+int prefill_tile_n(const FfnArgs& a) {
+  static const int env = [] {
+    const char* v = std::getenv("GLMRT_B200_PREFILL_TILE_N");
+    return v != nullptr ? std::atoi(v) : 0;
+  }();
+  if (env == 128 || env == 256) return env;
+  return 256;
 }
 
 }  // namespace
 
 glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  return launch_tokens<true>(a, m.act1, m.gate64, m.up64, sm_count, stream);
+  if (prefill_tile_n(a) == 256 && a.inter % 128 == 0)
+    return launch_tokens<true, 256>(a, m.act1, m.gate, m.up, sm_count, stream);
+  return launch_tokens<true, 128>(a, m.act1, m.gate64, m.up64, sm_count, stream);
 }
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  return launch_tokens<false>(a, m.act2, m.down, m.down, sm_count, stream);
+  if (prefill_tile_n(a) == 256 && a.hidden % 256 == 0)
+    return launch_tokens<false, 256>(a, m.act2, m.down, m.down, sm_count, stream);
+  return launch_tokens<false, 128>(a, m.act2, m.down, m.down, sm_count, stream);
 }
 
 }  // namespace glmrt

@@ -73,6 +73,8 @@ struct PlanArgs {
   int32_t* route_slot;           // [rows * top_k] -> slot or -1
   int32_t* slot_route;           // [max_slots] -> route or -1
   int32_t* expert_counts;        // [local experts]
+  int32_t* expert_base;          // [local experts] first slot of each expert (large-batch plan)
+  int32_t* block_hist;           // [ceil(routes / 256)][local experts] per-block counts, then prefixes
   Chunk* chunks;                 // [max_chunks]
   uint32_t* counters;            // [kCntWords]
 };

@@ -35,7 +35,8 @@ struct Layer {
   float *logits = nullptr, *topk_w = nullptr, *topk_scores = nullptr;
   uint32_t* topk_idx = nullptr;
   uint8_t* payload = nullptr;
-  int32_t *route_slot = nullptr, *slot_route = nullptr, *expert_counts = nullptr;
+  int32_t *route_slot = nullptr, *slot_route = nullptr, *expert_counts = nullptr, *expert_base = nullptr,
+          *block_hist = nullptr;
   Chunk* chunks = nullptr;
   uint32_t* counters = nullptr;
   uint8_t *act1_codes = nullptr, *act1_sf = nullptr, *act2_codes = nullptr, *act2_sf = nullptr;
@@ -182,6 +183,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
   p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
   p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
+  p.expert_base = l->expert_base; p.block_hist = l->block_hist;
   p.chunks = l->chunks; p.counters = l->counters;
   GLMRT_RETURN_IF_ERROR(launch_route_plan(p, stream));
   mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
@@ -273,6 +275,8 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->route_slot, routes));
   A(dev_alloc(l, &l->slot_route, static_cast<size_t>(l->max_slots)));
   A(dev_alloc(l, &l->expert_counts, E));
+  A(dev_alloc(l, &l->expert_base, E));
+  A(dev_alloc(l, &l->block_hist, ((routes + 255) / 256 + 1) * E));
   A(dev_alloc(l, &l->chunks, static_cast<size_t>(l->max_chunks)));
   A(dev_alloc(l, &l->counters, kCntWords, true));
   // slot-ordered operands; zero-filled once so that padding slots hold finite values
@@ -611,6 +615,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
       p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
       p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
+  p.expert_base = l->expert_base; p.block_hist = l->block_hist;
       p.chunks = l->chunks; p.counters = l->counters;
       GLMRT_RETURN_IF_ERROR(launch_ep_plan(a, p, s));
       mark(l, GLMRT_B200_STAGE_DISPATCH, s);

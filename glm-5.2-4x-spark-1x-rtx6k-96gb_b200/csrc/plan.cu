@@ -113,6 +113,118 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
   }
 }
 
+// ---- large batches: the same plan in three grid-wide steps ---------------------------------
+// Slots follow the order of the routes block by block (256 routes = 32 rows of a top-8 batch), so
+// the rows an expert's chunk reads and the result rows it writes stay close together in memory;
+// a purely atomic assignment scatters them over the whole batch and costs DRAM locality.
+constexpr int kPlanBlock = 256;
+
+// count: per-block histogram; each route keeps its arrival position inside (block, expert)
+__global__ void __launch_bounds__(kPlanBlock) plan_count_kernel(PlanArgs a, int local_experts) {
+  extern __shared__ int hist[];
+  for (int i = threadIdx.x; i < local_experts; i += kPlanBlock) hist[i] = 0;
+  __syncthreads();
+  const int r = blockIdx.x * kPlanBlock + threadIdx.x;
+  if (r < a.rows * a.top_k) {
+    const uint32_t e = a.topk_indices[r];
+    int pos = -1;
+    if (e >= static_cast<uint32_t>(a.experts)) {
+      atomicOr(&a.counters[kCntError], static_cast<uint32_t>(kErrBadExpert));
+    } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
+      pos = atomicAdd(&hist[e / a.ep_world], 1);
+    }
+    a.route_slot[r] = pos;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < local_experts; i += kPlanBlock)
+    a.block_hist[static_cast<size_t>(blockIdx.x) * local_experts + i] = hist[i];
+}
+// scan: per expert, exclusive prefix over the blocks; then one warp turns the totals into slot
+// bases and the chunk list
+__global__ void __launch_bounds__(1024) plan_scan_kernel(PlanArgs a, int local_experts, int blocks) {
+  for (int le = threadIdx.x; le < local_experts; le += 1024) {
+    int running = 0;
+#pragma unroll 8
+    for (int b = 0; b < blocks; ++b) {
+      const size_t i = static_cast<size_t>(b) * local_experts + le;
+      const int c = a.block_hist[i];
+      a.block_hist[i] = running;
+      running += c;
+    }
+    a.expert_counts[le] = running;
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  const int per_lane = (local_experts + 31) / 32;
+  const int le0 = lane * per_lane, le1 = min(local_experts, le0 + per_lane);
+  int slots = 0, chunks = 0, distinct = 0, routes = 0;
+  for (int le = le0; le < le1; ++le) {
+    const int c = a.expert_counts[le];
+    slots += (c + 127) & ~127;
+    chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
+    distinct += c != 0;
+    routes += c;
+  }
+  int slot_off = slots, chunk_off = chunks;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int s = __shfl_up_sync(0xffffffffu, slot_off, d);
+    const int c = __shfl_up_sync(0xffffffffu, chunk_off, d);
+    if (lane >= d) { slot_off += s; chunk_off += c; }
+  }
+  const int total_slots = __shfl_sync(0xffffffffu, slot_off, 31);
+  const int total_chunks = __shfl_sync(0xffffffffu, chunk_off, 31);
+  slot_off -= slots;
+  chunk_off -= chunks;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    distinct += __shfl_xor_sync(0xffffffffu, distinct, d);
+    routes += __shfl_xor_sync(0xffffffffu, routes, d);
+  }
+  uint32_t err = a.counters[kCntError];
+  if (total_slots > a.max_slots) err |= kErrSlotOverflow;
+  if (total_chunks > a.max_chunks) err |= kErrChunkOverflow;
+  for (int le = le0; le < le1; ++le) {
+    const int c = a.expert_counts[le];
+    a.expert_base[le] = slot_off;
+    if (err == 0) {
+      for (int off = 0; off < c; off += a.chunk_tokens) {
+        Chunk ch;
+        ch.expert = le;
+        ch.slot_base = slot_off + off;
+        ch.tokens = min(a.chunk_tokens, c - off);
+        ch.reserved = 0;
+        a.chunks[chunk_off++] = ch;
+      }
+    }
+    slot_off += (c + 127) & ~127;
+  }
+  if (lane == 0) {
+    a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(total_chunks);
+    a.counters[kCntSlots] = static_cast<uint32_t>(total_slots);
+    a.counters[kCntError] = err;
+    a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+    a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+  }
+}
+// place: position inside the expert -> slot
+__global__ void __launch_bounds__(kPlanBlock) plan_place_kernel(PlanArgs a, int local_experts) {
+  const int r = blockIdx.x * kPlanBlock + threadIdx.x;
+  if (r >= a.rows * a.top_k) return;
+  const int pos = a.route_slot[r];
+  if (pos < 0) return;
+  const bool bad = a.counters[kCntError] != 0;
+  const int le = static_cast<int>(a.topk_indices[r] / a.ep_world);
+  const int slot = a.expert_base[le] + a.block_hist[static_cast<size_t>(blockIdx.x) * local_experts + le] + pos;
+  if (bad || slot >= a.max_slots) {
+    a.route_slot[r] = -1;
+  } else {
+    a.route_slot[r] = slot;
+    a.slot_route[slot] = r;
+  }
+}
+
 // One warp per route.
 __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
@@ -136,8 +248,22 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
 }  // namespace
 
 glmrt_status_t launch_route_plan(const PlanArgs& a, cudaStream_t stream) {
-  route_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);
-  GLMRT_LAUNCH_CHECK("route_plan_kernel");
+  const int n = a.rows * a.top_k;
+  if (n <= 8192) {   // one CTA, one launch
+    route_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);
+    GLMRT_LAUNCH_CHECK("route_plan_kernel");
+    return GLMRT_STATUS_OK;
+  }
+  const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
+  const int blocks = (n + kPlanBlock - 1) / kPlanBlock;
+  cudaError_t err = cudaMemsetAsync(a.counters + kCntError, 0, sizeof(uint32_t), stream);
+  if (err != cudaSuccess) return status_from_cuda(err, "cudaMemsetAsync(route plan)");
+  plan_count_kernel<<<blocks, kPlanBlock, local_experts * sizeof(int), stream>>>(a, local_experts);
+  GLMRT_LAUNCH_CHECK("plan_count_kernel");
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(a, local_experts, blocks);
+  GLMRT_LAUNCH_CHECK("plan_scan_kernel");
+  plan_place_kernel<<<blocks, kPlanBlock, 0, stream>>>(a, local_experts);
+  GLMRT_LAUNCH_CHECK("plan_place_kernel");
   return GLMRT_STATUS_OK;
 }
 
