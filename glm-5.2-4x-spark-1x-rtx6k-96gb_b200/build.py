@@ -70,7 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     print(out)
     if jobs or not os.path.exists(LIB):
         run([nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-             "-Xcompiler", "-fPIC", "-cudart", "static"])
+             "-Xcompiler", "-fPIC", "-cudart", "static", "-ldl"])
     return LIB
 
 

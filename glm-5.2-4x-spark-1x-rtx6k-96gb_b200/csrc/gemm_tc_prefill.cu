@@ -5,20 +5,21 @@
 // b12x_direct.cu:479-647, and SIMT route MLP, mlp.cu:218-314), for token chunks of up to 128 rows:
 // the 128 rows of the UMMA tile are the token slots of one expert, the 128 columns are weight rows.
 //
-//   FC1  B = 64 gate rows stacked on the 64 up rows of the same features (two TMA boxes into one
-//        shared-memory tile, scales pre-tiled in the same stacking), so one thread of the epilogue
-//        owns one token and finds gate and up of 16 consecutive features in its own registers:
-//        SwiGLU, block amax, E4M3 scale, FP4 codes and packing need no cross-lane traffic, and the
-//        result leaves as one 8-byte store per block plus one 4-byte store of scales per tile.
-//   FC2  B = 128 down rows; the epilogue thread scales, rounds to bf16 and writes 256 contiguous
+//   FC1  B = 128 gate rows followed by the 128 up rows of the same features (two TMA boxes into one
+//        256-row shared-memory tile, one scale tile each), so one thread of the epilogue owns one
+//        token and finds gate and up of 16 consecutive features in its own registers: SwiGLU, block
+//        amax, E4M3 scale, FP4 codes and packing need no cross-lane traffic, and the result leaves
+//        as one 8-byte store of codes and one scale byte per block.
+//   FC2  B = 256 down rows; the epilogue thread scales, rounds to bf16 and writes 256 contiguous
 //        bytes of its token's result row.
 //
-// Accumulators (128 columns) are double-buffered in tensor memory, so the epilogue of one tile runs
-// under the MMAs of the next.  Producer, issuer and epilogue roles, bounded waits and the work-item
-// cache are as in gemm_tc.cu.  TMA loads read local memory only and use no cluster multicast.
+// N = 256 halves the scale copies and the bytes brought into shared memory per unit of math
+// compared with N = 128 (measured: FC1 1.63 -> 1.33 ms at T = 8192); the single accumulator buffer
+// it leaves room for means the epilogue does not overlap the MMAs, which sixteen (FC1) / eight
+// (FC2) epilogue warps keep short.  Producer, issuer and epilogue roles, bounded waits and the
+// work-item cache are as in gemm_tc.cu.  TMA loads read local memory only and use no cluster
+// multicast.
 #include <cuda.h>
-
-#include <cstdlib>
 
 #include "common.cuh"
 #include "epilogue.cuh"
@@ -144,13 +145,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
           tma_load_2d(s_a, &map_act, &full_bar[stage], kx, ch.slot_base, pol);
           bulk_load(s_sfa, sfa + (sfa_tile0 + ksf) * 512, kSfStageBytes, &full_bar[stage], pol);
-          if (kFC1 && kWN == 128) {
-            // 64 gate rows stacked on 64 up rows; their scales are pre-tiled in the same stacking
-            tma_load_2d(s_b, &map_w0, &full_bar[stage], kx, w_row, pol);
-            tma_load_2d(s_b + 64 * kStageBytesK, &map_w1, &full_bar[stage], kx, w_row, pol);
-            bulk_load(s_sfb, a.gu_sf64 + ((static_cast<size_t>(ch.expert) * feat_tiles + ft) * k_tiles64 + ksf) * 512,
-                      kSfStageBytes, &full_bar[stage], pol);
-          } else if (kFC1) {
+          if (kFC1) {
             // 128 gate rows, then 128 up rows, each with its own scale tile
             tma_load_2d(s_b, &map_w0, &full_bar[stage], kx, w_row, pol);
             tma_load_2d(s_b + 128 * kStageBytesK, &map_w1, &full_bar[stage], kx, w_row, pol);
@@ -310,28 +305,13 @@ glmrt_status_t launch_tokens(const FfnArgs& a, const CUtensorMap& act, const CUt
   return GLMRT_STATUS_OK;
 }
 
-// Tile width: 256 weight rows by default; GLMRT_B200_PREFILL_TILE_N=128 selects the narrower,
-// double-buffered tile (kept for comparison and for shapes whose dimensions 256 does not divide).
-int prefill_tile_n(const FfnArgs& a) {
-  static const int env = [] {
-    const char* v = std::getenv("GLMRT_B200_PREFILL_TILE_N");
-    return v != nullptr ? std::atoi(v) : 0;
-  }();
-  if (env == 128 || env == 256) return env;
-  return 256;
-}
-
 }  // namespace
 
 glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  if (prefill_tile_n(a) == 256 && a.inter % 128 == 0)
-    return launch_tokens<true, 256>(a, m.act1, m.gate, m.up, sm_count, stream);
-  return launch_tokens<true, 128>(a, m.act1, m.gate64, m.up64, sm_count, stream);
+  return launch_tokens<true, 256>(a, m.act1, m.gate, m.up, sm_count, stream);
 }
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  if (prefill_tile_n(a) == 256 && a.hidden % 256 == 0)
-    return launch_tokens<false, 256>(a, m.act2, m.down, m.down, sm_count, stream);
-  return launch_tokens<false, 128>(a, m.act2, m.down, m.down, sm_count, stream);
+  return launch_tokens<false, 256>(a, m.act2, m.down, m.down, sm_count, stream);
 }
 
 }  // namespace glmrt

@@ -57,9 +57,6 @@ glmrt_status_t launch_quantize_rows_payload(const uint16_t* in, uint8_t* payload
                                             uint32_t rule, cudaStream_t stream);
 glmrt_status_t launch_tile_scales(const uint8_t* in, uint8_t* out, size_t rows, size_t kblocks,
                                   size_t out_row_offset, cudaStream_t stream);
-// gate and up scales [rows, kblocks] -> tiles of 64 gate rows + 64 up rows; tile index = first_tile + row / 64
-glmrt_status_t launch_tile_scales_stacked64(const uint8_t* gate_in, const uint8_t* up_in, uint8_t* out, size_t rows,
-                                            size_t kblocks, size_t first_tile, cudaStream_t stream);
 glmrt_status_t launch_quantize_weight_f32(const float* in, uint8_t* packed, uint8_t* scales, float* scale_2_out,
                                           uint32_t* amax_scratch, size_t rows, size_t cols, cudaStream_t stream);
 
@@ -138,7 +135,6 @@ struct FfnArgs {
   // weights of local experts, stacked
   const uint8_t* gate_codes; const uint8_t* up_codes; const uint8_t* down_codes;   // [E_l*I, H/2] x2, [E_l*H, I/2]
   const uint8_t* gate_sf; const uint8_t* up_sf; const uint8_t* down_sf;            // tiled scales
-  const uint8_t* gu_sf64;   // gate/up scales re-tiled as 128-row tiles of 64 gate rows followed by 64 up rows
   const float* scale2;                                                                // [E_l][3]
   const uint8_t* act1_codes; const uint8_t* act1_sf;                                   // dispatch output
   uint8_t* act2_codes; uint8_t* act2_sf;                                               // FC1 output
@@ -153,7 +149,6 @@ glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);
 // ---- gemm_tc.cu (tcgen05 engine) ----
 struct TensorMaps {
   CUtensorMap gate, up, down;   // weight codes, 128-row boxes
-  CUtensorMap gate64, up64;     // the same tensors with 64-row boxes (prefill FC1 stacks gate and up)
   CUtensorMap act1, act2;       // activation codes (box rows = chunk_tokens)
 };
 // Encodes a 2D uint8 tensor map [rows, row_bytes] with a {128 B, box_rows} box and 128-byte swizzle.

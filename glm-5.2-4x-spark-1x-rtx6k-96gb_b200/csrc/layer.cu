@@ -25,7 +25,7 @@ struct Layer {
   std::vector<void*> allocations;
   // weights (local experts stacked)
   uint8_t *gate_codes = nullptr, *up_codes = nullptr, *down_codes = nullptr;
-  uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr, *gu_sf64 = nullptr;
+  uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr;
   float* scale2 = nullptr;
   float *router_w = nullptr, *router_b = nullptr;
   uint16_t* router_w3 = nullptr;   // [experts, 3 * hidden] bf16 split of router_w for the tensor-core router
@@ -45,7 +45,7 @@ struct Layer {
   uint16_t *hidden_stage = nullptr, *out_stage = nullptr;
   // scratch for weight loading
   float* wtmp = nullptr;
-  uint8_t *sftmp = nullptr, *sftmp2 = nullptr;
+  uint8_t* sftmp = nullptr;
   uint32_t* amax_tmp = nullptr;
   TensorMaps maps32{}, maps128{};
   bool have_maps = false;
@@ -130,8 +130,6 @@ glmrt_status_t build_maps(Layer* l) {
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->gate, l->gate_codes, wrows_fc1, c.hidden_dim / 2, 128));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->up, l->up_codes, wrows_fc1, c.hidden_dim / 2, 128));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->down, l->down_codes, wrows_fc2, c.intermediate_dim / 2, 128));
-    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->gate64, l->gate_codes, wrows_fc1, c.hidden_dim / 2, 64));
-    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->up64, l->up_codes, wrows_fc1, c.hidden_dim / 2, 64));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act1, l->act1_codes, l->max_slots, c.hidden_dim / 2, box));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act2, l->act2_codes, l->max_slots, c.intermediate_dim / 2, box));
   }
@@ -143,7 +141,6 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
   FfnArgs a{};
   a.gate_codes = l->gate_codes; a.up_codes = l->up_codes; a.down_codes = l->down_codes;
   a.gate_sf = l->gate_sf; a.up_sf = l->up_sf; a.down_sf = l->down_sf;
-  a.gu_sf64 = l->gu_sf64;
   a.scale2 = l->scale2;
   a.act1_codes = l->act1_codes; a.act1_sf = l->act1_sf;
   a.act2_codes = l->act2_codes; a.act2_sf = l->act2_sf;
@@ -262,7 +259,6 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->gate_sf, E * I * H / 16));
   A(dev_alloc(l, &l->up_sf, E * I * H / 16));
   A(dev_alloc(l, &l->down_sf, E * H * I / 16));
-  A(dev_alloc(l, &l->gu_sf64, 2 * E * I * H / 16));
   A(dev_alloc(l, &l->scale2, E * 3, true));
   A(dev_alloc(l, &l->router_w, static_cast<size_t>(c.experts) * H, true));
   A(dev_alloc(l, &l->router_b, c.experts, true));
@@ -290,7 +286,6 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   A(dev_alloc(l, &l->out_stage, T * H));
   A(dev_alloc(l, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
   A(dev_alloc(l, &l->sftmp, I * H / 16));
-  A(dev_alloc(l, &l->sftmp2, I * H / 16));
   A(dev_alloc(l, &l->amax_tmp, 1, true));
   if (c.ep_world > 1) A(dev_alloc(l, &l->ep_ctrl, 1, true));
   if (st != GLMRT_STATUS_OK) {
@@ -356,9 +351,6 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_set_expert(
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(gate_scales.ptr), l->gate_sf, I, H / 16, le * I, s));
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(up_scales.ptr), l->up_sf, I, H / 16, le * I, s));
   GLMRT_RETURN_IF_ERROR(launch_tile_scales(static_cast<const uint8_t*>(down_scales.ptr), l->down_sf, H, I / 16, le * H, s));
-  GLMRT_RETURN_IF_ERROR(launch_tile_scales_stacked64(static_cast<const uint8_t*>(gate_scales.ptr),
-                                                     static_cast<const uint8_t*>(up_scales.ptr), l->gu_sf64, I, H / 16,
-                                                     le * (I / 64), s));
   const float s2[3] = {gate_scale_2, up_scale_2, down_scale_2};
   err = cudaMemcpyAsync(l->scale2 + le * 3, s2, sizeof(s2), cudaMemcpyHostToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_expert scale copy", err);
@@ -382,13 +374,9 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_fill_synthetic(void* layer, uint6
       uint8_t* codes = t == 0 ? l->gate_codes : t == 1 ? l->up_codes : l->down_codes;
       uint8_t* sf = t == 0 ? l->gate_sf : t == 1 ? l->up_sf : l->down_sf;
       const size_t rows = t == 2 ? H : I, cols = t == 2 ? I : H;
-      uint8_t* rowmajor = t == 1 ? l->sftmp2 : l->sftmp;   // gate scales survive until up is done
-      GLMRT_RETURN_IF_ERROR(launch_quantize_weight_f32(l->wtmp, codes + static_cast<size_t>(le) * n / 2, rowmajor,
+      GLMRT_RETURN_IF_ERROR(launch_quantize_weight_f32(l->wtmp, codes + static_cast<size_t>(le) * n / 2, l->sftmp,
                                                        l->scale2 + le * 3 + t, l->amax_tmp, rows, cols, s));
-      GLMRT_RETURN_IF_ERROR(launch_tile_scales(rowmajor, sf, rows, cols / 16, static_cast<size_t>(le) * rows, s));
-      if (t == 1)
-        GLMRT_RETURN_IF_ERROR(launch_tile_scales_stacked64(l->sftmp, l->sftmp2, l->gu_sf64, I, H / 16,
-                                                           static_cast<size_t>(le) * (I / 64), s));
+      GLMRT_RETURN_IF_ERROR(launch_tile_scales(l->sftmp, sf, rows, cols / 16, static_cast<size_t>(le) * rows, s));
     }
   }
   return ok();

@@ -184,20 +184,6 @@ tile_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, si
   out[sf_tile_offset(out_row_offset + r, j, kblocks)] = in[gid];
 }
 
-// Tiles of 128 scale rows made of 64 gate rows followed by the 64 up rows of the same features.
-__global__ void __launch_bounds__(kThreads)
-tile_scales_stacked64_kernel(const uint8_t* __restrict__ gate_in, const uint8_t* __restrict__ up_in,
-                             uint8_t* __restrict__ out, size_t rows, int kblocks, size_t first_tile) {
-  const size_t total = rows * static_cast<size_t>(kblocks);
-  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
-  if (gid >= total) return;
-  const size_t r = gid / kblocks;
-  const size_t j = gid % kblocks;
-  const size_t tile_row = (first_tile + r / 64) * 128;
-  out[sf_tile_offset(tile_row + (r % 64), j, kblocks)] = gate_in[gid];
-  out[sf_tile_offset(tile_row + 64 + (r % 64), j, kblocks)] = up_in[gid];
-}
-
 unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / kThreads); }
 
 }  // namespace
@@ -224,14 +210,6 @@ glmrt_status_t launch_tile_scales(const uint8_t* in, uint8_t* out, size_t rows, 
   tile_scales_kernel<<<grid_for(rows * kblocks), kThreads, 0, stream>>>(in, out, rows, static_cast<int>(kblocks),
                                                                         out_row_offset);
   GLMRT_LAUNCH_CHECK("tile_scales_kernel");
-  return GLMRT_STATUS_OK;
-}
-
-glmrt_status_t launch_tile_scales_stacked64(const uint8_t* gate_in, const uint8_t* up_in, uint8_t* out, size_t rows,
-                                            size_t kblocks, size_t first_tile, cudaStream_t stream) {
-  tile_scales_stacked64_kernel<<<grid_for(rows * kblocks), kThreads, 0, stream>>>(gate_in, up_in, out, rows,
-                                                                                  static_cast<int>(kblocks), first_tile);
-  GLMRT_LAUNCH_CHECK("tile_scales_stacked64_kernel");
   return GLMRT_STATUS_OK;
 }
 

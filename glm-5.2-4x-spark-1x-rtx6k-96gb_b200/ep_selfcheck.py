@@ -78,10 +78,52 @@ def main() -> int:
         ok = bool(np.array_equal(got, ref)) and bool(np.isfinite(ref.view(np.uint16).astype(np.float32)).all())
         print(("EP_SELFCHECK_OK" if ok else "EP_SELFCHECK_MISMATCH") + f" world={world}", flush=True)
         single.close()
+    ok = nccl_row_all_to_all_check(layer.lib, rank, world) and ok
     dist.barrier()
     layer.close()
     dist.destroy_process_group()
     return 0 if ok else 1
+
+
+def nccl_row_all_to_all_check(lib, rank, world) -> bool:
+    """The reference-ABI NCCL row all-to-all (glmrt_nccl_row_all_to_all_u8_async) between the same
+    ranks: rank r must receive every peer's copy of row slice r."""
+    import ctypes as C
+    from glmrt_b200 import native as N
+    n = C.c_size_t(0)
+    if lib.call_status("glmrt_nccl_unique_id_bytes", C.byref(n)) != 0:
+        if rank == 0:
+            print("NCCL_WRAPPERS_SKIPPED (library not loadable)", flush=True)
+        return True
+    uid = C.create_string_buffer(128)
+    if rank == 0:
+        lib.call("glmrt_nccl_get_unique_id", uid, C.c_size_t(128))
+    box = [bytes(uid.raw)]
+    dist.broadcast_object_list(box, src=0)
+    uid = C.create_string_buffer(box[0], 128)
+    comm = C.c_void_p()
+    lib.call("glmrt_nccl_comm_init_rank", uid, C.c_size_t(128), C.c_int(world), C.c_int(rank), C.byref(comm))
+    rows, stride = 4 * world + 1, 64
+    send = torch.full((rows, stride), rank, dtype=torch.uint8, device="cuda")
+    send[:, 0] = torch.arange(rows, dtype=torch.uint8, device="cuda")
+    base, extra = divmod(rows, world)
+    mine = base + (1 if rank < extra else 0)
+    recv = torch.zeros(((world - 1) * mine, stride), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    db = lambda t: N.DeviceBuffer.of(t.data_ptr(), t.numel(), torch.cuda.current_device())
+    lib.call("glmrt_nccl_row_all_to_all_u8_async", comm, db(send), db(recv), C.c_size_t(rows), C.c_size_t(stride),
+             C.c_void_p(stream.cuda_stream))
+    stream.synchronize()
+    start = rank * base + min(rank, extra)
+    got = recv.cpu().numpy().reshape(world - 1, mine, stride)
+    peers = [p for p in range(world) if p != rank]
+    good = all((got[i, :, 1] == p).all() and (got[i, :, 0] == np.arange(start, start + mine)).all()
+               for i, p in enumerate(peers))
+    lib.call("glmrt_nccl_comm_destroy", comm)
+    if rank == 0:
+        print("NCCL_ROW_ALL_TO_ALL_OK" if good else "NCCL_ROW_ALL_TO_ALL_MISMATCH", flush=True)
+    return bool(good)
 
 
 if __name__ == "__main__":

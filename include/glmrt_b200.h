@@ -303,6 +303,34 @@ typedef struct glmrt_b200_layer_stats_t {
 glmrt_status_t glmrt_b200_moe_layer_stats(void* layer, glmrt_b200_layer_stats_t* out);
 
 /* ------------------------------------------------------------------------ */
+/* NCCL wrappers (native/include/glmrt_native.h:428-444; implementation       */
+/* native/src/glmrt_native.cc:1453-1757).  Same signatures and argument rules. */
+/* NCCL is resolved at run time (GLMRT_NCCL_LIB or libnccl.so.2); without it    */
+/* every entry point returns GLMRT_STATUS_NCCL_UNAVAILABLE.  Not on the data   */
+/* path of the expert-parallel forward below; kept for callers of the          */
+/* reference ABI and as its cross-check.                                       */
+/* ------------------------------------------------------------------------ */
+glmrt_status_t glmrt_nccl_unique_id_bytes(size_t* out_bytes);
+glmrt_status_t glmrt_nccl_get_unique_id(void* out, size_t out_bytes);
+glmrt_status_t glmrt_nccl_comm_init_rank(const void* unique_id, size_t unique_id_bytes, int world_size,
+                                         int rank, void** out_handle);
+glmrt_status_t glmrt_nccl_gather_u8_async(void* handle, glmrt_device_buffer_t send,
+                                          glmrt_device_buffer_t recv, size_t bytes, int root,
+                                          void* cuda_stream);
+/* rows are split into world contiguous slices (the first rows % world one row longer); rank r
+ * receives every peer's copy of slice r, back to back in peer order. */
+glmrt_status_t glmrt_nccl_row_all_to_all_u8_async(void* handle, glmrt_device_buffer_t send,
+                                                  glmrt_device_buffer_t recv, size_t rows,
+                                                  size_t row_stride_bytes, void* cuda_stream);
+glmrt_status_t glmrt_nccl_all_reduce_bf16_async(void* handle, glmrt_device_buffer_t send,
+                                                glmrt_device_buffer_t recv, size_t values,
+                                                void* cuda_stream);
+glmrt_status_t glmrt_nccl_reduce_bf16_async(void* handle, glmrt_device_buffer_t send,
+                                            glmrt_device_buffer_t recv, size_t values, int root,
+                                            void* cuda_stream);
+glmrt_status_t glmrt_nccl_comm_destroy(void* handle);
+
+/* ------------------------------------------------------------------------ */
 /* Expert-parallel forward over NVLink peer memory (additions).               */
 /* Replaces the ExpertProtocolV2 TCP/RDMA transport between coordinator and    */
 /* expert hosts (rust/crates/glmrt-transport/src/protocol_v2.rs:236-310) and   */

@@ -275,3 +275,31 @@ def test_infra_alloc_copy_events(lib, pkg):
     info = N.DeviceInfo()
     lib.call("glmrt_cuda_device_info", C.c_int(0), C.byref(info))
     assert info.cuda_available == 1 and info.compute_capability_major == 10
+
+
+def test_nccl_wrappers_single_rank_communicator(lib, pkg):
+    """Reference NCCL ABI on a one-rank communicator: unique id, init, bf16 all-reduce and
+    reduce-to-root (identity for one rank), destroy."""
+    from glmrt_b200 import native as N
+    n = C.c_size_t(0)
+    st = lib.call_status("glmrt_nccl_unique_id_bytes", C.byref(n))
+    if st == 8:
+        pytest.skip("libnccl.so.2 not loadable in this process")
+    assert st == 0 and n.value == 128
+    uid = C.create_string_buffer(128)
+    lib.call("glmrt_nccl_get_unique_id", uid, C.c_size_t(128))
+    comm = C.c_void_p()
+    lib.call("glmrt_nccl_comm_init_rank", uid, C.c_size_t(128), C.c_int(1), C.c_int(0), C.byref(comm))
+    x = torch.randn(1000, device="cuda").to(torch.bfloat16)
+    y = torch.zeros_like(x)
+    z = torch.zeros_like(x)
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    sp = C.c_void_p(s.cuda_stream)
+    lib.call("glmrt_nccl_all_reduce_bf16_async", comm, dbuf(x), dbuf(y), C.c_size_t(1000), sp)
+    lib.call("glmrt_nccl_reduce_bf16_async", comm, dbuf(x), dbuf(z), C.c_size_t(1000), C.c_int(0), sp)
+    s.synchronize()
+    assert torch.equal(x, y) and torch.equal(x, z)
+    assert lib.call_status("glmrt_nccl_all_reduce_bf16_async", comm, dbuf(x), dbuf(y), C.c_size_t(1000), None) == 1
+    assert lib.call_status("glmrt_nccl_reduce_bf16_async", comm, dbuf(x), dbuf(z), C.c_size_t(1000), C.c_int(3), sp) == 1
+    lib.call("glmrt_nccl_comm_destroy", comm)
