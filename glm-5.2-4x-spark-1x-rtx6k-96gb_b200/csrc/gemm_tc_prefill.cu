@@ -17,8 +17,7 @@
 // compared with N = 128 (measured: FC1 1.63 -> 1.33 ms at T = 8192); the single accumulator buffer
 // it leaves room for means the epilogue does not overlap the MMAs, which sixteen (FC1) / eight
 // (FC2) epilogue warps keep short.  Producer, issuer and epilogue roles, bounded waits and the
-// work-item cache are as in gemm_tc.cu.  TMA loads read local memory only and use no cluster
-// multicast.
+// work-item cache are as in gemm_tc.cu.  Every TMA load reads this GPU's own memory into one CTA.
 #include <cuda.h>
 
 #include "common.cuh"
