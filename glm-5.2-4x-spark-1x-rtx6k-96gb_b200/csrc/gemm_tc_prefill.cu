@@ -10,14 +10,18 @@
 //        token and finds gate and up of 16 consecutive features in its own registers: SwiGLU, block
 //        amax, E4M3 scale, FP4 codes and packing need no cross-lane traffic, and the result leaves
 //        as one 8-byte store of codes and one scale byte per block.
-//   FC2  B = 256 down rows; the epilogue thread scales, rounds to bf16 and writes 256 contiguous
-//        bytes of its token's result row.
+//   FC2  B = 128 down rows, accumulators double-buffered in tensor memory: its K loop is only eight
+//        stages long, so an epilogue that held the single buffer of a 256-column tile drained the
+//        pipeline at every tile (measured at T = 8192: 1.08 ms with N = 256, 0.86 ms with N = 128).
+//        The epilogue thread scales, rounds to bf16, parks 128 bytes of its token's row in shared
+//        memory and sends them with one asynchronous bulk store: full 128-byte lines to local or
+//        peer memory instead of 32 lanes scattering 16-byte pieces over 32 rows.
 //
-// N = 256 halves the scale copies and the bytes brought into shared memory per unit of math
-// compared with N = 128 (measured: FC1 1.63 -> 1.33 ms at T = 8192); the single accumulator buffer
-// it leaves room for means the epilogue does not overlap the MMAs, which sixteen (FC1) / eight
-// (FC2) epilogue warps keep short.  Producer, issuer and epilogue roles, bounded waits and the
-// work-item cache are as in gemm_tc.cu.  Every TMA load reads this GPU's own memory into one CTA.
+// FC1 uses N = 256: half the scale copies and fewer bytes brought into shared memory per unit of
+// math than N = 128 (measured: FC1 1.63 -> 1.33 ms at T = 8192); its 48-stage K loop hides the one
+// non-overlapped epilogue per tile, which sixteen epilogue warps keep short.  Producer, issuer and
+// epilogue roles, bounded waits and the work-item cache are as in gemm_tc.cu.  Every TMA load reads
+// this GPU's own memory into one CTA.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -30,17 +34,16 @@ namespace {
 
 using namespace tc;
 
-// Tile geometry.  kWN = weight rows (UMMA N) per tile: 128 (64 gate + 64 up for FC1) with the
-// accumulators double-buffered, or 256 (128 gate + 128 up) with a single accumulator buffer: twice
-// the math per scale copy and per byte brought into shared memory, at the price of an epilogue
-// that no longer overlaps the MMAs.
+// Tile geometry.  kWN = weight rows (UMMA N) per tile: 128 with the accumulators double-buffered
+// (FC2), or 256 = 128 gate + 128 up with a single accumulator buffer (FC1).
 template <bool kFC1, int kWN>
 struct PfCfg {
   static constexpr int kBTiles = kWN / 128;                          // 128-row boxes / scale tiles of B
   static constexpr int kABytes = 128 * kStageBytesK;                 // 128 token rows
   static constexpr int kBBytes = kWN * kStageBytesK;
   static constexpr int kStageBytes = kABytes + kBBytes + (1 + kBTiles) * kSfStageBytes;
-  static constexpr int kStages = 221184 / kStageBytes;               // 6 (N=128) or 4 (N=256)
+  // FC2 gives one pipeline stage up for the staging rows of its epilogue
+  static constexpr int kStages = 221184 / kStageBytes - (kFC1 ? 0 : 1);   // 4 (FC1, N=256) / 5 (FC2, N=128)
   static constexpr int kAccBufs = kWN == 128 ? 2 : 1;
   static constexpr int kSfSetCols = 16 + 16 * kBTiles;               // scale columns of one stage
   static constexpr int kSfCol = kAccBufs * kWN;                      // two alternating sets follow the accumulators
@@ -53,7 +56,12 @@ struct PfCfg {
   static constexpr int kParts = kEpiWarps / 4;
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kChunkCache = 256;
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk);
+  // FC2 epilogue: each thread owns 128 staging bytes (64 bf16 of its row); the 144-byte pitch keeps
+  // the 16-byte shared stores of a quarter warp on distinct banks
+  static constexpr int kOutPitch = 144;
+  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * 32 * kOutPitch;
+  static constexpr size_t kSmemBytes =
+      static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
 
 __device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -80,6 +88,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   Chunk* chunk_cache = reinterpret_cast<Chunk*>(reinterpret_cast<uint8_t*>(bars) + 256);
+  uint8_t* out_stage = reinterpret_cast<uint8_t*>(chunk_cache + C::kChunkCache);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -251,22 +260,34 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           }
         }
       } else {
+        // The thread's 128 columns leave in two halves: scale, round to bf16, park 128 bytes in
+        // the thread's own staging row, then hand them to one asynchronous bulk store.  Each store
+        // writes a full 128-byte line of the destination row (local memory or a peer's), instead of
+        // 32 lanes scattering 16-byte pieces over 32 rows.
         constexpr int kColsPerPart = kWN / C::kParts;   // 128
+        uint8_t* mine = out_stage + (static_cast<size_t>(warp - 2) * 32 + lane) * C::kOutPitch;
 #pragma unroll
-        for (int c0 = part * kColsPerPart; c0 < (part + 1) * kColsPerPart; c0 += 16) {
-          uint32_t y[16];
-          tc_load16(t_acc + c0, y);
+        for (int half = 0; half < kColsPerPart / 64; ++half) {
+          const int c0 = part * kColsPerPart + half * 64;
+          uint32_t y[4][16];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tc_load16(t_acc + c0 + q * 16, y[q]);
           tc_wait_ld();
-          if (valid) {
+          bulk_store_wait_read();   // the previous store has finished reading the staging row
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
             uint32_t w[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[2 * i]), s2a))) |
-                     (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[2 * i + 1]), s2a))) << 16);
-            uint4* d4 = reinterpret_cast<uint4*>(dst + ft * C::kFeatPerTile + c0);
-            d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2a))) |
+                     (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2a))) << 16);
+            uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
+            s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
           }
+          fence_async_smem();
+          if (valid) bulk_store(dst + ft * C::kFeatPerTile + c0, smem_u32(mine), 128);
+          bulk_store_commit();
         }
       }
       tc_fence_before();
@@ -277,6 +298,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   }
 
   // ---- teardown ----
+  if (!kFC1 && warp >= 2) bulk_store_wait_all();
   __syncwarp();
   if (*abort_flag != 0u) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
@@ -310,7 +332,7 @@ glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& m, int 
   return launch_tokens<true, 256>(a, m.act1, m.gate, m.up, sm_count, stream);
 }
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  return launch_tokens<false, 256>(a, m.act2, m.down, m.down, sm_count, stream);
+  return launch_tokens<false, 128>(a, m.act2, m.down, m.down, sm_count, stream);
 }
 
 }  // namespace glmrt
