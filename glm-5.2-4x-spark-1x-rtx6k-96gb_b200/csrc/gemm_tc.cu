@@ -367,6 +367,22 @@ glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_
   return GLMRT_STATUS_OK;
 }
 
+glmrt_status_t make_scale_tensor_map(CUtensorMap* out, const void* base, uint64_t bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(GLMRT_STATUS_CUDA_UNAVAILABLE, "cuTensorMapEncodeTiled is not available");
+  if (bytes == 0 || bytes % 2048 != 0 || reinterpret_cast<uintptr_t>(base) % 128 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "scale tensor map: needs whole 2 KB groups on a 128-byte aligned base");
+  const cuuint64_t dims[2] = {128, bytes / 128};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128, 16};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GLMRT_STATUS_INTERNAL_ERROR, "cuTensorMapEncodeTiled (scales) failed with code " + std::to_string(static_cast<int>(r)));
+  return GLMRT_STATUS_OK;
+}
+
 glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
   if (a.chunk_tokens == 32) return launch_one<true, 32>(a, m.gate, m.up, m.act1, sm_count, stream);
   return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");

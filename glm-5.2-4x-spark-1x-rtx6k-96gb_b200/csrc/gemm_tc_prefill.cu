@@ -64,15 +64,6 @@ struct PfCfg {
       static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
 
-__device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-
 template <bool kFC1, int kWN>
 __global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
 expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act,
@@ -117,16 +108,24 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // A plan made of 256-slot chunks (for the CTA-pair FC1 kernel) is taken as two halves of 128
+  // slots; a half without tokens is skipped by every role alike.
+  const int halves = a.chunk_tokens > 128 ? a.chunk_tokens / 128 : 1;
   const int num_chunks = static_cast<int>(a.counters[kCntChunks]);
-  const int num_tiles = num_chunks * feat_tiles;
+  const int num_tiles = num_chunks * halves * feat_tiles;
+  auto load_chunk = [&](int tile) -> Chunk {
+    Chunk c = a.chunks[tile / (feat_tiles * halves)];
+    const int half = (tile / feat_tiles) % halves;
+    c.slot_base += 128 * half;
+    c.tokens = min(128, max(0, c.tokens - 128 * half));
+    return c;
+  };
   for (int i = threadIdx.x; i < C::kChunkCache; i += C::kThreads) {
     const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
-    if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
+    if (tile < num_tiles) chunk_cache[i] = load_chunk(static_cast<int>(tile));
   }
   __syncthreads();
-  auto chunk_of = [&](int it, int tile) -> Chunk {
-    return it < C::kChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
-  };
+  auto chunk_of = [&](int it, int tile) -> Chunk { return it < C::kChunkCache ? chunk_cache[it] : load_chunk(tile); };
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -138,6 +137,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
       const Chunk ch = chunk_of(it, tile);
+      if (ch.tokens == 0) continue;
       const int ft = tile % feat_tiles;
       const int w_row = ch.expert * out_rows + ft * C::kFeatPerTile;   // first weight row (per projection)
       const size_t sfa_tile0 = static_cast<size_t>(ch.slot_base / 128) * k_tiles64;
@@ -183,7 +183,9 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     bool alive = true;
     const uint32_t idesc = idesc_nvf4(kWN);
     uint32_t sf_flip = 0;   // scale columns alternate between two sets: copies of one stage run under the MMAs of the previous
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
+      if (halves > 1 && chunk_of(it, tile).tokens == 0) continue;
       if (!mbar_wait_warp(&acc_empty[abuf], aphase ^ 1u, abort_flag)) { alive = false; break; }
       tc_fence_after();
       const uint32_t d0 = tmem_base + abuf * kWN;
@@ -231,6 +233,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
       const Chunk ch = chunk_of(it, tile);
+      if (ch.tokens == 0) continue;
       const int ft = tile % feat_tiles;
       const bool valid = row < ch.tokens;
       const size_t slot = static_cast<size_t>(ch.slot_base) + row;

@@ -65,7 +65,7 @@ struct PlanArgs {
   const uint32_t* topk_indices;  // [rows * top_k] global expert ids
   int rows, top_k, experts;      // experts = global count
   int ep_world, ep_rank;
-  int chunk_tokens;              // BN: tokens per chunk (32 or 128)
+  int chunk_tokens;              // BN: tokens per chunk (32, 128 or 256)
   int max_slots, max_chunks;
   int32_t* route_slot;           // [rows * top_k] -> slot or -1
   int32_t* slot_route;           // [max_slots] -> route or -1
@@ -150,14 +150,21 @@ glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);
 struct TensorMaps {
   CUtensorMap gate, up, down;   // weight codes, 128-row boxes
   CUtensorMap act1, act2;       // activation codes (box rows = chunk_tokens)
+  CUtensorMap act1_sf, gate_sf, up_sf;   // tiled scales seen as rows of 128 bytes, 2 KB boxes (CTA-pair FC1)
 };
 // Encodes a 2D uint8 tensor map [rows, row_bytes] with a {128 B, box_rows} box and 128-byte swizzle.
 glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
                                      uint32_t box_rows);
+// Encodes a byte range as [bytes / 128, 128] with a {128 B, 16 rows} box and no swizzle: one box = 2 KB of scale tiles.
+glmrt_status_t make_scale_tensor_map(CUtensorMap* out, const void* base, uint64_t bytes);
 glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 // gemm_tc_prefill.cu: 128-token chunks, tokens on the MMA rows
 glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
+// gemm_tc_pair.cu: 256-token chunks on CTA pairs (FC1 only; FC2 of such a plan runs the kernel
+// above, which takes each chunk as two halves of 128)
+bool fc1_pair_supported(const FfnArgs& a, int sm_count);
+glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 
 }  // namespace glmrt

@@ -22,6 +22,7 @@ struct Layer {
   int local_experts = 0;
   int max_slots = 0;
   int max_chunks = 0;
+  bool have_sf_maps = false;   // the scale arrays are whole 2 KB groups: the CTA-pair FC1 kernel may run
   std::vector<void*> allocations;
   // weights (local experts stacked)
   uint8_t *gate_codes = nullptr, *up_codes = nullptr, *down_codes = nullptr;
@@ -132,6 +133,14 @@ glmrt_status_t build_maps(Layer* l) {
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->down, l->down_codes, wrows_fc2, c.intermediate_dim / 2, 128));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act1, l->act1_codes, l->max_slots, c.hidden_dim / 2, box));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act2, l->act2_codes, l->max_slots, c.intermediate_dim / 2, box));
+    const uint64_t sf_fc1 = wrows_fc1 * (c.hidden_dim / 16);
+    const uint64_t sf_act1 = static_cast<uint64_t>(l->max_slots) * (c.hidden_dim / 16);
+    if (sf_fc1 % 2048 == 0 && sf_act1 % 2048 == 0) {
+      GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->gate_sf, l->gate_sf, sf_fc1));
+      GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->up_sf, l->up_sf, sf_fc1));
+      GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->act1_sf, l->act1_sf, sf_act1));
+      l->have_sf_maps = true;
+    }
   }
   l->have_maps = true;
   return GLMRT_STATUS_OK;
@@ -169,7 +178,16 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
 glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream) {
   const auto& c = l->cfg;
-  const int chunk_tokens = rows <= 256 ? 32 : 128;
+  // Work-item size: 32 slots for decode batches (weights on the MMA rows), 128 for prefill (tokens
+  // on the MMA rows), 256 (FC1 on CTA pairs) once the average expert of this shard receives more
+  // than 192 routes, i.e. when most 256-slot items are better than half full.
+  int chunk_tokens = rows <= 256 ? 32 : 128;
+  if (chunk_tokens == 128 && !(c.flags & (GLMRT_B200_LAYER_ENGINE_SIMT | GLMRT_B200_LAYER_NO_PAIR_TILES)) &&
+      l->sm_count % 2 == 0 && c.hidden_dim % 256 == 0 && c.intermediate_dim % 128 == 0 &&
+      rows * c.top_k > static_cast<size_t>(192) * c.experts) {
+    if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
+    if (l->have_sf_maps) chunk_tokens = 256;
+  }
   mark(l, GLMRT_B200_STAGE_QUANTIZE, stream);
   GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
                                                      GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
@@ -198,8 +216,9 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   } else {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
     const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
-    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, stream)
-                                             : launch_fc1_tc_prefill(f, maps, l->sm_count, stream));
+    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32    ? launch_fc1_tc(f, maps, l->sm_count, stream)
+                          : chunk_tokens == 256 ? launch_fc1_tc_pair(f, maps, l->sm_count, stream)
+                                                : launch_fc1_tc_prefill(f, maps, l->sm_count, stream));
     mark(l, GLMRT_B200_STAGE_FC2, stream);
     GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, stream)
                                              : launch_fc2_tc_prefill(f, maps, l->sm_count, stream));

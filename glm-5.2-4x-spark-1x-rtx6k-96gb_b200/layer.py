@@ -41,7 +41,7 @@ class MoeLayer:
                  ep_world: int = 1, ep_rank: int = 0, engine: str = "tc", scaling: float = 2.5,
                  lib: N.NativeLibrary | None = None):
         self.lib = lib or N.library()
-        flags = {"tc": 0, "simt": N.LAYER_ENGINE_SIMT}[engine]
+        flags = {"tc": 0, "tc1": N.LAYER_NO_PAIR_TILES, "simt": N.LAYER_ENGINE_SIMT}[engine]
         self.cfg = N.MoeConfig(hidden, inter, experts, top_k, max_tokens, ep_world, ep_rank, flags, scaling)
         self.hidden, self.inter, self.experts, self.top_k = hidden, inter, experts, top_k
         self.max_tokens, self.ep_world, self.ep_rank = max_tokens, ep_world, ep_rank

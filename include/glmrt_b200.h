@@ -223,6 +223,8 @@ typedef struct glmrt_b200_moe_config_t {
 
 enum {
   GLMRT_B200_LAYER_ENGINE_SIMT = 1u, /* run the expert FFN on the SIMT verification kernels */
+  GLMRT_B200_LAYER_NO_PAIR_TILES = 2u, /* large batches: keep FC1 on one-CTA tiles (128 token slots) instead
+                                          of 256-slot tiles on CTA pairs */
 };
 
 glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer);
