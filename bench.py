@@ -200,7 +200,7 @@ def run_gpu(args):
     T, steps, warmup = args.tokens, args.steps, max(3, args.warmup)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    layer = MoeLayer(H, I, E, K_TOP, max_tokens=T)
+    layer = MoeLayer(H, I, E, K_TOP, max_tokens=T, engine="tc2" if args.pair_tiles else "tc")
     layer.fill_synthetic(0, 0.02)
     g = torch.Generator(device="cpu").manual_seed(0)
     rw = (torch.randn(E, H, generator=g) * 0.02)
@@ -415,6 +415,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--pair-tiles", action="store_true",
+                    help="large batches: run FC1 on CTA pairs (cta_group::2) instead of one-CTA tiles (for comparison)")
     ap.add_argument("--experts", type=int, default=E,
                     help="routed experts in the layer (256 = GLM-5.2; smaller values give a profiler-sized case)")
     args = ap.parse_args()

@@ -7,8 +7,10 @@
 // 256 B rows - the leader the 128 gate rows, its peer the 128 up rows of the same features - and a
 // single M = 256 MMA per K block, issued by the leader, fills a 128 x 256 accumulator in each CTA's
 // tensor memory.  Per unit of math a CTA brings 38 KB instead of 54 KB into shared memory, which
-// buys a fifth pipeline stage and a third less traffic per SM; measured on the one-CTA kernel, the
-// time per stage was set by the latency and rate of that traffic, not by the MMAs.
+// buys a fifth pipeline stage.  Measured on the GLM-5.2 layer it is exactly as fast as the one-CTA
+// kernel (T = 8192: 1.19 vs 1.14 ms, T = 16384: 1.88 vs 1.89 ms) and bit-identical: what each SM no
+// longer loads from L2 it now reads from its peer's shared memory, and the 256-slot items are
+// emptier on average.  The layer therefore uses it only when asked (GLMRT_B200_LAYER_PAIR_TILES).
 //
 // Protocol (every wait bounded, as in gemm_tc.cu):
 //   * both producers wait on their own `empty` barrier and load into their own shared memory; all
@@ -211,15 +213,23 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
       if (!mbar_wait_warp(acc_full, aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + lane_base;
+      // Both 16-feature blocks of this warp are read out first and the accumulator is handed back
+      // before any arithmetic, so the next item's MMAs run under this item's SwiGLU and stores.
+      uint32_t g[2][16], u[2][16];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        tc_load16(t_acc + (part * 2 + j) * 16, g[j]);
+        tc_load16(t_acc + 128 + (part * 2 + j) * 16, u[j]);
+      }
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int b = part * 2 + j;                   // 16-feature block of the tile
-        uint32_t g[16], u[16];
-        tc_load16(t_acc + b * 16, g);
-        tc_load16(t_acc + 128 + b * 16, u);
-        tc_wait_ld();
         uint32_t lo, hi, sbyte;
-        swiglu_requant_block16(g, u, s2g, s2u, lo, hi, sbyte);
+        swiglu_requant_block16(g[j], u[j], s2g, s2u, lo, hi, sbyte);
         if (valid) {
           const int feature = ft * C::kFeatPerTile + b * 16;
           *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + feature / 2) =
@@ -227,9 +237,6 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
           a.act2_sf[sf_tile_offset(slot, feature / 16, a.inter / 16)] = static_cast<uint8_t>(sbyte);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
       aphase ^= 1u;
     }
   }

@@ -245,16 +245,24 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       const uint32_t t_acc = tmem_base + lane_base + abuf * kWN;
       if (kFC1) {
         // gate occupies columns [0, kWN/2), up [kWN/2, kWN); 16 warps share the 16-feature blocks
+        // All blocks of this warp are read out first and the accumulator is handed back before
+        // any arithmetic: the next tile's MMAs run under this tile's SwiGLU and stores.
         constexpr int kBlocksPerWarp = (kWN / 32) / C::kParts;   // 1 (N=128) or 2 (N=256)
+        uint32_t g[kBlocksPerWarp][16], u[kBlocksPerWarp][16];
+#pragma unroll
+        for (int j = 0; j < kBlocksPerWarp; ++j) {
+          tc_load16(t_acc + (part * kBlocksPerWarp + j) * 16, g[j]);
+          tc_load16(t_acc + kWN / 2 + (part * kBlocksPerWarp + j) * 16, u[j]);
+        }
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[abuf]);
 #pragma unroll
         for (int j = 0; j < kBlocksPerWarp; ++j) {
           const int b = part * kBlocksPerWarp + j;
-          uint32_t g[16], u[16];
-          tc_load16(t_acc + b * 16, g);
-          tc_load16(t_acc + kWN / 2 + b * 16, u);
-          tc_wait_ld();
           uint32_t lo, hi, sbyte;
-          swiglu_requant_block16(g, u, s2a, s2b, lo, hi, sbyte);
+          swiglu_requant_block16(g[j], u[j], s2a, s2b, lo, hi, sbyte);
           if (valid) {
             const int feature = ft * C::kFeatPerTile + b * 16;
             *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + feature / 2) =
@@ -276,6 +284,11 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
 #pragma unroll
           for (int q = 0; q < 4; ++q) tc_load16(t_acc + c0 + q * 16, y[q]);
           tc_wait_ld();
+          if (half == kColsPerPart / 64 - 1) {   // everything is in registers: hand the accumulator back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[abuf]);
+          }
           bulk_store_wait_read();   // the previous store has finished reading the staging row
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -293,9 +306,6 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           bulk_store_commit();
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[abuf]);
       if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }
   }

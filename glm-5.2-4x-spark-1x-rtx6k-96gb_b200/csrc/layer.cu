@@ -179,10 +179,10 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
 glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream) {
   const auto& c = l->cfg;
   // Work-item size: 32 slots for decode batches (weights on the MMA rows), 128 for prefill (tokens
-  // on the MMA rows), 256 (FC1 on CTA pairs) once the average expert of this shard receives more
-  // than 192 routes, i.e. when most 256-slot items are better than half full.
+  // on the MMA rows); on request 256 (FC1 on CTA pairs) once the average expert receives more than
+  // 192 routes, i.e. when most 256-slot items are better than half full.
   int chunk_tokens = rows <= 256 ? 32 : 128;
-  if (chunk_tokens == 128 && !(c.flags & (GLMRT_B200_LAYER_ENGINE_SIMT | GLMRT_B200_LAYER_NO_PAIR_TILES)) &&
+  if (chunk_tokens == 128 && (c.flags & GLMRT_B200_LAYER_PAIR_TILES) && !(c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) &&
       l->sm_count % 2 == 0 && c.hidden_dim % 256 == 0 && c.intermediate_dim % 128 == 0 &&
       rows * c.top_k > static_cast<size_t>(192) * c.experts) {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));

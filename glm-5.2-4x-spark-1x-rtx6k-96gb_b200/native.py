@@ -68,7 +68,7 @@ class LayerStats(C.Structure):
 
 
 LAYER_ENGINE_SIMT = 1
-LAYER_NO_PAIR_TILES = 2
+LAYER_PAIR_TILES = 2
 FP4_RULE_RNE_PAYLOAD = 0
 FP4_RULE_NEAREST_LOW = 1
 

@@ -243,29 +243,29 @@ def test_glm52_shape_tc_matches_simt_at_bench_sizes(pkg, T):
 
 @pytest.mark.parametrize("T", [900, 1536])
 def test_pair_tiles_match_oracle_and_one_cta_tiles(pkg, small_layer, T):
-    """Above 192 routes per expert FC1 runs on CTA pairs over 256-slot work items (and FC2 takes
-    each item as two halves).  The result must meet the oracle gate and agree with the one-CTA
-    kernels run on the same plan-independent inputs; T=900 leaves many second halves empty."""
+    """On request, above 192 routes per expert FC1 runs on CTA pairs over 256-slot work items (and
+    FC2 takes each item as two halves).  The result must meet the oracle gate and agree with the
+    one-CTA kernels on the same inputs; T=900 leaves many second halves empty."""
     K = 4
     hid = O.make_hidden(4200 + T, T, 512)
     oi, ow, oo = O.layer_forward(small_layer, hid, K, mode="O1")
     outs = {}
-    for engine in ("tc", "tc1"):
+    for engine in ("tc2", "tc"):
         layer = make(pkg, small_layer, K, 2048, engine)
         out, idx, w = layer.forward(to_dev(hid), want_routes=True)
         layer.check()
         chunks = layer.debug("CHUNKS", np.int32).reshape(-1, 4)
         n_chunks = int(layer.debug("COUNTERS", np.uint32)[0])
         width = int(chunks[:n_chunks, 2].max())
-        assert (width > 128) == (engine == "tc"), f"{engine}: widest work item {width}"
+        assert (width > 128) == (engine == "tc2"), f"{engine}: widest work item {width}"
         assert O.router_indices_equivalent(idx.cpu().numpy(), oi, sel64(small_layer, hid))
         err = O.rel_l2_per_token(to_bits(out), oo)
         assert err.max() <= TOL, f"{engine} T={T}: max per-token rel L2 {err.max():.3e}"
         outs[engine] = to_bits(out).copy()
         layer.close()
-    diff = O.rel_l2_per_token(outs["tc"], outs["tc1"])
+    diff = O.rel_l2_per_token(outs["tc2"], outs["tc"])
     print(f"pair vs one-CTA tiles T={T}: max per-token rel L2 {diff.max():.3e}, "
-          f"{(outs['tc'] != outs['tc1']).mean():.2e} of bf16 words differ")
+          f"{(outs['tc2'] != outs['tc']).mean():.2e} of bf16 words differ")
     assert diff.max() <= 1e-3
 
 
