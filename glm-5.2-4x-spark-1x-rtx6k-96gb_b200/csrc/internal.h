@@ -85,8 +85,13 @@ struct DispatchArgs {
   uint8_t* act_sf;               // tiled scales, H/16 blocks per slot
   uint16_t* route_rows;          // bf16 [rows * top_k, H]: destination rows of FC2
   uint16_t** slot_out;           // [max_slots] destination row pointer per slot
+  uint8_t* payload_out;          // fused quantise + dispatch only: where the payload rows are written
 };
 glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
+// quant.cu: quantises bf16 rows [rows, hidden] and dispatches them in one kernel (payload rows
+// go to payload_out; `payload` is not read).  Needs hidden % 128 == 0 and 16-byte aligned rows.
+bool quantize_dispatch_supported(const uint16_t* in, const DispatchArgs& a);
+glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& a, cudaStream_t stream);
 
 // ---- ep.cu (expert-parallel exchange over peer memory) ----
 constexpr int kEpMaxExperts = 1024;

@@ -188,9 +188,17 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
     if (l->have_sf_maps) chunk_tokens = 256;
   }
+  DispatchArgs d{};
+  d.payload = l->payload; d.payload_out = l->payload; d.route_slot = l->route_slot;
+  d.rows = static_cast<int>(rows); d.top_k = static_cast<int>(c.top_k); d.hidden = static_cast<int>(c.hidden_dim);
+  d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
+  // The plan needs only the routes, so it runs first and the rows are quantised and dispatched by
+  // one kernel (its time is reported as the dispatch stage, the quantise stage then reads 0).
+  const bool fused = quantize_dispatch_supported(hidden, d);
   mark(l, GLMRT_B200_STAGE_QUANTIZE, stream);
-  GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
-                                                     GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
+  if (!fused)
+    GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
+                                                       GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
   mark(l, GLMRT_B200_STAGE_PLAN, stream);
   PlanArgs p{};
   p.topk_indices = l->topk_idx;
@@ -202,11 +210,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   p.chunks = l->chunks; p.counters = l->counters;
   GLMRT_RETURN_IF_ERROR(launch_route_plan(p, stream));
   mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
-  DispatchArgs d{};
-  d.payload = l->payload; d.route_slot = l->route_slot;
-  d.rows = static_cast<int>(rows); d.top_k = static_cast<int>(c.top_k); d.hidden = static_cast<int>(c.hidden_dim);
-  d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
-  GLMRT_RETURN_IF_ERROR(launch_dispatch(d, stream));
+  GLMRT_RETURN_IF_ERROR(fused ? launch_quantize_dispatch(hidden, d, stream) : launch_dispatch(d, stream));
   FfnArgs f = ffn_args(l, chunk_tokens);
   mark(l, GLMRT_B200_STAGE_FC1, stream);
   if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {

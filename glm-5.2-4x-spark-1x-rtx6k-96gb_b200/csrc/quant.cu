@@ -18,6 +18,45 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// One 16-element block: E4M3 scale of amax/6, then E2M1 codes, low nibble first.
+//
+// kNearestLow is the rule of the Python reference (quant_ref.py:41-46): the code nearest to the
+// IEEE quotient x / scale, ties towards the smaller magnitude.  The quotient is never formed:
+// for a bf16 x (8 significant bits), an E4M3 scale (4 bits) and a code midpoint m (0.25 .. 5),
+// x / scale is either exactly m or differs from it by more than 2^-9 relative, far more than the
+// rounding of the division, so fl(x / scale) > m holds exactly when |x| > m * scale, and m * scale
+// is exact in float32.  Seven comparisons against exact products replace sixteen divisions.
+template <bool kNearestLow>
+__device__ __forceinline__ void quantize_block16(const float (&v)[16], uint32_t& lo, uint32_t& hi, uint32_t& sbyte) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  sbyte = f32_to_e4m3_satfinite(__fdiv_rn(amax, 6.0f));
+  const float scale = e4m3_to_f32(sbyte);
+  lo = 0; hi = 0;
+  if (kNearestLow) {
+    if (scale != 0.0f) {
+      const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale,
+                  t5 = 3.5f * scale, t6 = 5.0f * scale;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float m = fabsf(v[i]);
+        const uint32_t mag = (m > t0) + (m > t1) + (m > t2) + (m > t3) + (m > t4) + (m > t5) + (m > t6);
+        const uint32_t c = mag | ((v[i] < 0.0f && mag != 0u) ? 8u : 0u);
+        if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
+      }
+    }
+  } else {
+    const float inv = scale == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float q = fminf(fmaxf(__fmul_rn(v[i], inv), -6.0f), 6.0f);
+      const uint32_t c = fp4_code_rne_payload(q);
+      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
+    }
+  }
+}
+
 // ---- activation payload -------------------------------------------------------------
 template <bool kNearestLow, bool kVector>
 __global__ void __launch_bounds__(kThreads)
@@ -44,27 +83,8 @@ quantize_rows_payload_kernel(const uint16_t* __restrict__ in, uint8_t* __restric
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = bf16_bits_to_f32(src[i]);
   }
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const uint32_t sbyte = f32_to_e4m3_satfinite(__fdiv_rn(amax, 6.0f));
-  const float scale = e4m3_to_f32(sbyte);
-  uint32_t lo = 0, hi = 0;
-  if (kNearestLow) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const uint32_t c = scale == 0.0f ? 0u : fp4_code_nearest_low(__fdiv_rn(v[i], scale));
-      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-    }
-  } else {
-    const float inv = scale == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float q = fminf(fmaxf(__fmul_rn(v[i], inv), -6.0f), 6.0f);
-      const uint32_t c = fp4_code_rne_payload(q);
-      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-    }
-  }
+  uint32_t lo, hi, sbyte;
+  quantize_block16<kNearestLow>(v, lo, hi, sbyte);
   uint8_t* prow = payload + row * (static_cast<size_t>(cols) / 2 + blocks_per_row);
   if (kVector) {
     reinterpret_cast<uint2*>(prow)[blk] = make_uint2(lo, hi);
@@ -186,7 +206,66 @@ tile_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, si
 
 unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / kThreads); }
 
+
+// Quantise + dispatch in one pass, one CTA per token row: the row is quantised once into a payload
+// image in shared memory, written out as the payload row (the expert-parallel exchange and the
+// inspection interface read it) and copied to the slot of each of the row's routes: codes as 16-byte
+// vectors, scales as 4-byte words of the tiled layout.  Replaces a launch and the re-read of the
+// payload by one warp per route.
+constexpr int kFusedThreads = 256;   // measured faster than one thread per 16-element block (384 for hidden 6144)
+__global__ void __launch_bounds__(kFusedThreads)
+quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
+  extern __shared__ uint4 row_img[];
+  uint8_t* img = reinterpret_cast<uint8_t*>(row_img);
+  const int row = blockIdx.x;
+  const int code_bytes = a.hidden / 2;
+  const int kblocks = a.hidden / 16;
+  const uint16_t* src_row = in + static_cast<size_t>(row) * a.hidden;
+  for (int blk = threadIdx.x; blk < kblocks; blk += kFusedThreads) {
+    const uint4 x0 = reinterpret_cast<const uint4*>(src_row + blk * 16)[0];
+    const uint4 x1 = reinterpret_cast<const uint4*>(src_row + blk * 16)[1];
+    const uint32_t w[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    uint32_t lo, hi, sbyte;
+    quantize_block16<true>(v, lo, hi, sbyte);
+    reinterpret_cast<uint2*>(img)[blk] = make_uint2(lo, hi);
+    img[code_bytes + blk] = static_cast<uint8_t>(sbyte);
+  }
+  __syncthreads();
+  const int row_vecs = (code_bytes + kblocks) / 16;
+  uint4* prow = reinterpret_cast<uint4*>(a.payload_out + static_cast<size_t>(row) * (code_bytes + kblocks));
+  for (int i = threadIdx.x; i < row_vecs; i += kFusedThreads) prow[i] = row_img[i];
+  const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(img + code_bytes);
+  for (int k = 0; k < a.top_k; ++k) {
+    const int route = row * a.top_k + k;
+    const int slot = a.route_slot[route];
+    if (slot < 0) continue;   // route of an expert that lives on another shard
+    uint4* dst4 = reinterpret_cast<uint4*>(a.act_codes + static_cast<size_t>(slot) * code_bytes);
+    for (int i = threadIdx.x; i < code_bytes / 16; i += kFusedThreads) dst4[i] = row_img[i];
+    for (int j = threadIdx.x; j < kblocks / 4; j += kFusedThreads)
+      *reinterpret_cast<uint32_t*>(a.act_sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
+    if (threadIdx.x == 0) a.slot_out[slot] = a.route_rows + static_cast<size_t>(route) * a.hidden;
+  }
+}
+
 }  // namespace
+
+bool quantize_dispatch_supported(const uint16_t* in, const DispatchArgs& a) {
+  return a.hidden % 128 == 0 && a.hidden <= 16384 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(a.payload_out) % 16 == 0;
+}
+
+glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& a, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(a.hidden) / 2 + a.hidden / 16;
+  quantize_dispatch_kernel<<<a.rows, kFusedThreads, smem, stream>>>(in, a);
+  GLMRT_LAUNCH_CHECK("quantize_dispatch_kernel");
+  return GLMRT_STATUS_OK;
+}
 
 glmrt_status_t launch_quantize_rows_payload(const uint16_t* in, uint8_t* payload, size_t rows, size_t cols,
                                             uint32_t rule, cudaStream_t stream) {

@@ -380,9 +380,9 @@ glmrt_status_t glmrt_b200_moe_layer_forward_ep_host(void* layer, const void* hid
  * GLMRT_REAL_FULL_NVFP4_ROUTE_CUDA_EVENT_TIMING, sparse_mlp/route.rs:1010-1062). */
 typedef enum glmrt_b200_stage_t {
   GLMRT_B200_STAGE_ROUTER = 0,
-  GLMRT_B200_STAGE_QUANTIZE = 1,
+  GLMRT_B200_STAGE_QUANTIZE = 1,     /* 0 when quantise and dispatch run as one kernel (the usual case) */
   GLMRT_B200_STAGE_PLAN = 2,
-  GLMRT_B200_STAGE_DISPATCH = 3,
+  GLMRT_B200_STAGE_DISPATCH = 3,     /* dispatch, or the fused quantise + dispatch kernel */
   GLMRT_B200_STAGE_FC1 = 4,
   GLMRT_B200_STAGE_FC2 = 5,
   GLMRT_B200_STAGE_COMBINE = 6,
