@@ -15,10 +15,14 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// kResidual: the summed routed row is not stored as such but folded into the layer output the way
+// the reference's residual kernel does it (native/cuda/kernels/residual.cu:36-62, truncating bf16
+// stores): mlp = bf16(shared + routed) when a shared-expert row is given, out = bf16(residual + mlp).
+template <bool kResidual>
 __global__ void __launch_bounds__(kThreads)
 combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __restrict__ topk_weights,
                       const int32_t* __restrict__ route_slot, uint16_t* __restrict__ out, int rows, int top_k,
-                      int hidden) {
+                      int hidden, const uint16_t* __restrict__ residual, const uint16_t* __restrict__ shared) {
   const int vec_per_row = hidden / 8;
   const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
   if (gid >= static_cast<size_t>(rows) * vec_per_row) return;
@@ -54,6 +58,29 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
         const float p1 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w[j], y1)));
         acc[2 * i] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i], p0)));
         acc[2 * i + 1] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i + 1], p1)));
+      }
+    }
+  }
+  if (kResidual) {
+    const size_t off = static_cast<size_t>(row) * hidden;
+    const uint4 r4 = reinterpret_cast<const uint4*>(residual + off)[v];
+    const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+    uint32_t sw[4] = {0u, 0u, 0u, 0u};
+    if (shared != nullptr) {
+      const uint4 s4 = reinterpret_cast<const uint4*>(shared + off)[v];
+      sw[0] = s4.x; sw[1] = s4.y; sw[2] = s4.z; sw[3] = s4.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float res = __uint_as_float(h == 0 ? rw[i] << 16 : rw[i] & 0xffff0000u);
+        float mlp = acc[2 * i + h];
+        if (shared != nullptr) {
+          const float sh = __uint_as_float(h == 0 ? sw[i] << 16 : sw[i] & 0xffff0000u);
+          mlp = __uint_as_float(__float_as_uint(__fadd_rn(sh, mlp)) & 0xffff0000u);
+        }
+        acc[2 * i + h] = __uint_as_float(__float_as_uint(__fadd_rn(res, mlp)) & 0xffff0000u);
       }
     }
   }
@@ -109,9 +136,14 @@ unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / 
 
 glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
-                                     cudaStream_t stream) {
-  combine_routes_kernel<<<grid_for(static_cast<size_t>(rows) * (hidden / 8)), kThreads, 0, stream>>>(
-      route_rows, topk_weights, route_slot, out, rows, top_k, hidden);
+                                     cudaStream_t stream, const uint16_t* residual, const uint16_t* shared) {
+  const unsigned grid = grid_for(static_cast<size_t>(rows) * (hidden / 8));
+  if (residual != nullptr)
+    combine_routes_kernel<true><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
+                                                               hidden, residual, shared);
+  else
+    combine_routes_kernel<false><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
+                                                                hidden, nullptr, nullptr);
   GLMRT_LAUNCH_CHECK("combine_routes_kernel");
   return GLMRT_STATUS_OK;
 }

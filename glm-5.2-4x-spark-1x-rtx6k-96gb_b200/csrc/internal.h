@@ -131,9 +131,12 @@ glmrt_status_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, 
 glmrt_status_t launch_ep_signal(const EpArgs& a, int which, cudaStream_t stream);
 
 // ---- combine.cu ----
+// residual / shared (optional, [rows, hidden] bf16): fold the routed sum into the layer output,
+// out = bf16(residual + bf16(shared + routed)), instead of storing it.
 glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, const uint16_t* residual = nullptr,
+                                     const uint16_t* shared = nullptr);
 
 // ---- ffn_simt.cu (verification engine) ----
 struct FfnArgs {

@@ -176,7 +176,8 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
 }
 
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
-glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream) {
+glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream,
+                          const uint16_t* residual = nullptr, const uint16_t* shared = nullptr) {
   const auto& c = l->cfg;
   // Work-item size: 32 slots for decode batches (weights on the MMA rows), 128 for prefill (tokens
   // on the MMA rows); on request 256 (FC1 on CTA pairs) once the average expert receives more than
@@ -231,7 +232,8 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   // with one shard every route is local; a shard of an expert-parallel layer only sums its own
   const int32_t* mask = c.ep_world > 1 ? l->route_slot : nullptr;
   GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
-                                              static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream));
+                                              static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream,
+                                              residual, shared));
   mark(l, GLMRT_B200_STAGE_COUNT, stream);
   l->stage_valid = l->profiling;
   l->last_rows = static_cast<uint32_t>(rows);
@@ -435,6 +437,34 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_async(void* layer, glmrt_
   if (err == cudaSuccess && topk_weights.ptr != nullptr)
     err = cudaMemcpyAsync(topk_weights.ptr, l->topk_w, routes * 4, cudaMemcpyDeviceToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward route copy", err);
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_residual_async(
+    void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t residual_bf16,
+    glmrt_device_buffer_t shared_delta_bf16, glmrt_device_buffer_t output_bf16, void* cuda_stream) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
+  if (l->cfg.ep_world != 1)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_residual: this entry point needs ep_world == 1");
+  const size_t row_bytes = static_cast<size_t>(l->cfg.hidden_dim) * 2;
+  GLMRT_RETURN_IF_ERROR(check_buf(hidden_bf16, rows * row_bytes, "forward_residual hidden"));
+  GLMRT_RETURN_IF_ERROR(check_buf(residual_bf16, rows * row_bytes, "forward_residual residual"));
+  GLMRT_RETURN_IF_ERROR(check_buf(output_bf16, rows * row_bytes, "forward_residual output"));
+  if (shared_delta_bf16.ptr != nullptr && shared_delta_bf16.bytes < rows * row_bytes)
+    return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "forward_residual shared_delta: buffer too small");
+  for (const void* p : {hidden_bf16.ptr, residual_bf16.ptr, shared_delta_bf16.ptr, output_bf16.ptr})
+    if (reinterpret_cast<uintptr_t>(p) % 16 != 0)
+      return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_residual: buffers must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  const uint64_t before = launches_total();
+  mark(l, GLMRT_B200_STAGE_ROUTER, s);
+  GLMRT_RETURN_IF_ERROR(run_router(l, hidden_bf16.ptr, rows, s));
+  GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                   static_cast<uint16_t*>(output_bf16.ptr), s,
+                                   static_cast<const uint16_t*>(residual_bf16.ptr),
+                                   static_cast<const uint16_t*>(shared_delta_bf16.ptr)));
+  l->launches_last = static_cast<uint32_t>(launches_total() - before);
   return ok();
 }
 

@@ -127,6 +127,19 @@ class MoeLayer:
                       C.c_size_t(rows), _buf(idx), _buf(w), _buf(out), _stream())
         return out
 
+    def forward_residual(self, hidden_bf16: torch.Tensor, residual_bf16: torch.Tensor,
+                         shared_delta_bf16: torch.Tensor | None = None,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+        """Forward with the layer's residual step folded into the combine:
+        out = bf16(residual + bf16(shared_delta + routed)) (truncating stores)."""
+        rows = hidden_bf16.shape[0]
+        if out is None:
+            out = torch.empty_like(hidden_bf16)
+        shared = N.DeviceBuffer.null() if shared_delta_bf16 is None else _buf(shared_delta_bf16)
+        self.lib.call("glmrt_b200_moe_layer_forward_residual_async", self.handle, _buf(hidden_bf16),
+                      C.c_size_t(rows), _buf(residual_bf16), shared, _buf(out), _stream())
+        return out
+
     def forward_host(self, hidden_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """Host buffers in, host buffers out (pinned memory recommended); synchronises."""
         assert not hidden_host.is_cuda and not out_host.is_cuda

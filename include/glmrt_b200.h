@@ -195,6 +195,25 @@ glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32_async(
 glmrt_status_t glmrt_cuda_gather_rows_bf16_async(const uint16_t* src, const uint32_t* row_indices,
                                                  uint16_t* dst, size_t rows, size_t row_width,
                                                  void* cuda_stream);
+/* Residual adds after the routed/shared MLP (native/include/glmrt_native.h:715-730, kernels
+ * native/cuda/kernels/residual.cu:18-62): float32 adds, bf16 results stored by truncation, a
+ * float32 delta truncated to bf16 first.  count == 0 is accepted and does nothing. */
+glmrt_status_t glmrt_cuda_residual_add_bf16(const uint16_t* residual, const uint16_t* delta,
+                                            uint16_t* out, size_t count);
+glmrt_status_t glmrt_cuda_residual_add_bf16_async(const uint16_t* residual, const uint16_t* delta,
+                                                  uint16_t* out, size_t count, void* cuda_stream);
+glmrt_status_t glmrt_cuda_residual_add_f32_delta_bf16(const uint16_t* residual, const float* delta_f32,
+                                                      uint16_t* out, size_t count);
+glmrt_status_t glmrt_cuda_residual_add_f32_delta_bf16_async(const uint16_t* residual,
+                                                            const float* delta_f32, uint16_t* out,
+                                                            size_t count, void* cuda_stream);
+/* out = bf16(residual + bf16(shared_delta + bf16(routed_delta_f32))) */
+glmrt_status_t glmrt_cuda_residual_add_shared_f32_delta_bf16(
+    const uint16_t* residual, const uint16_t* shared_delta, const float* routed_delta_f32,
+    uint16_t* out, size_t count);
+glmrt_status_t glmrt_cuda_residual_add_shared_f32_delta_bf16_async(
+    const uint16_t* residual, const uint16_t* shared_delta, const float* routed_delta_f32,
+    uint16_t* out, size_t count, void* cuda_stream);
 
 /* ------------------------------------------------------------------------ */
 /* Layer-level entry points (additions).                                      */
@@ -253,6 +272,15 @@ glmrt_status_t glmrt_b200_moe_layer_fill_synthetic(void* layer, uint64_t seed, f
 glmrt_status_t glmrt_b200_moe_layer_forward_async(
     void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t output_bf16,
     glmrt_device_buffer_t topk_indices, glmrt_device_buffer_t topk_weights, void* cuda_stream);
+/* The same forward with the residual step of the sparse layer folded into the combine kernel
+ * (python/reference/glmrt_reference/glm_moe_dsa_layer_ref.py:196-198 hidden + routed + shared, in
+ * the arithmetic of native/cuda/kernels/residual.cu:47-58): output = bf16(residual +
+ * bf16(shared_delta + routed)), truncating stores; shared_delta_bf16.ptr may be NULL (no shared
+ * expert: output = bf16(residual + routed)).  hidden_bf16 is the normalised input of the router
+ * and the experts, residual_bf16 the un-normalised layer input.  ep_world must be 1. */
+glmrt_status_t glmrt_b200_moe_layer_forward_residual_async(
+    void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t residual_bf16,
+    glmrt_device_buffer_t shared_delta_bf16, glmrt_device_buffer_t output_bf16, void* cuda_stream);
 /* Same with host buffers: copies the rows in from `hidden_host`, runs the layer, copies the
  * result out to `output_host` and synchronises the stream.  Host memory may be pageable;
  * pinned memory makes the copies asynchronous. */

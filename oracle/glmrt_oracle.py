@@ -534,6 +534,30 @@ def sum_topk_bf16(y_routes_bits) -> np.ndarray:
     return bf16_truncate(acc)
 
 
+def residual_add_bf16(residual_bits, delta_bits) -> np.ndarray:
+    """out = bf16(residual + delta), float32 add, truncating store
+    (native/cuda/kernels/residual.cu:18-26; f32_to_bf16 truncates, common.h:64-66)."""
+    r = bf16_to_f32(np.asarray(residual_bits, np.uint16))
+    d = bf16_to_f32(np.asarray(delta_bits, np.uint16))
+    return bf16_truncate((r + d).astype(np.float32))
+
+
+def residual_add_f32_delta_bf16(residual_bits, delta_f32) -> np.ndarray:
+    """out = bf16(residual + bf16(delta)) (native/cuda/kernels/residual.cu:28-38)."""
+    d = bf16_truncate(np.asarray(delta_f32, np.float32))
+    return residual_add_bf16(residual_bits, d)
+
+
+def residual_add_shared_f32_delta_bf16(residual_bits, shared_bits, routed_f32) -> np.ndarray:
+    """out = bf16(residual + bf16(shared + bf16(routed))) (native/cuda/kernels/residual.cu:40-52):
+    the layer output hidden + routed + shared of glm_moe_dsa_layer_ref.py:196-198 in the
+    native kernel's association and rounding."""
+    routed = bf16_to_f32(bf16_truncate(np.asarray(routed_f32, np.float32)))
+    shared = bf16_to_f32(np.asarray(shared_bits, np.uint16))
+    mlp = bf16_truncate((shared + routed).astype(np.float32))
+    return residual_add_bf16(residual_bits, mlp)
+
+
 def scatter_add_rows_bf16_weighted_to_f32(src_bits, row_indices, row_weights, dst_f32) -> np.ndarray:
     """dst[row_indices[r]] += w[r] * src[r] (native/cuda/kernels/residual.cu:666-678)."""
     dst = np.array(dst_f32, np.float32, copy=True)

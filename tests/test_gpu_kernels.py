@@ -251,6 +251,36 @@ def test_sum_topk8_and_weighted_scatter_and_gather(lib):
     np.testing.assert_array_equal(g.cpu().view(torch.int16).numpy().view(np.uint16), src[ri.astype(np.int64)])
 
 
+def test_residual_adds_match_oracle_bit_exactly(lib):
+    """native/tests/cuda_selftest.cc:1053-1110 (same inputs, same host formula), then random data
+    with values whose sums are not representable in bf16 so that truncation matters."""
+    res = O.bf16_truncate(np.array([0.25, -0.5, 1.5, 2.0, -3.0, 4.5, 0.0, -0.125], np.float32))
+    shared = O.bf16_truncate(np.array([-0.25, 0.75, 0.125, -1.5, 2.0, -0.5, 0.25, 0.5], np.float32))
+    routed = np.array([-0.51, 0.26, 0.501, -1.001, 3.51, -2.01, 0.126, 0.251], np.float32)
+    rng = np.random.default_rng(12)
+    n = 100003                                                        # not a multiple of the block size
+    cases = [(res, shared, routed),
+             (O.bf16_round(rng.standard_normal(n, np.float32) * 3), O.bf16_round(rng.standard_normal(n, np.float32)),
+              rng.standard_normal(n, np.float32))]
+    for r, sh, rt in cases:
+        k = r.size
+        rt_t, sh_t = bf16_tensor(r), bf16_tensor(sh)
+        d32 = torch.from_numpy(rt).cuda()
+        out = torch.zeros(k, dtype=torch.bfloat16, device="cuda")
+        bits = lambda t: t.cpu().view(torch.int16).numpy().view(np.uint16)
+        lib.call("glmrt_cuda_residual_add_shared_f32_delta_bf16_async", ptr(rt_t), ptr(sh_t), ptr(d32), ptr(out),
+                 C.c_size_t(k), stream())
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(bits(out), O.residual_add_shared_f32_delta_bf16(r, sh, rt))
+        lib.call("glmrt_cuda_residual_add_f32_delta_bf16", ptr(rt_t), ptr(d32), ptr(out), C.c_size_t(k))
+        np.testing.assert_array_equal(bits(out), O.residual_add_f32_delta_bf16(r, rt))
+        lib.call("glmrt_cuda_residual_add_bf16", ptr(rt_t), ptr(sh_t), ptr(out), C.c_size_t(k))
+        np.testing.assert_array_equal(bits(out), O.residual_add_bf16(r, sh))
+    # empty range is accepted; null pointers are not
+    assert lib.call_status("glmrt_cuda_residual_add_bf16_async", None, None, None, C.c_size_t(0), stream()) == 0
+    assert lib.call_status("glmrt_cuda_residual_add_bf16_async", None, None, None, C.c_size_t(4), stream()) == 1
+
+
 def test_infra_alloc_copy_events(lib, pkg):
     from glmrt_b200 import native as N
     b = N.DeviceBuffer()

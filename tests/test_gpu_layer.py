@@ -136,6 +136,80 @@ def test_forward_routed_and_host_entry_points(pkg, small_layer):
     layer.close()
 
 
+@pytest.mark.parametrize("T", [5, 300])
+def test_forward_residual_folds_the_layer_output_into_the_combine(pkg, small_layer, T):
+    """out = bf16(residual + bf16(shared + routed)) computed inside the combine kernel equals the
+    plain forward followed by the oracle's residual step, bit for bit; without a shared-expert
+    row it is bf16(residual + routed)."""
+    K = 4
+    layer = make(pkg, small_layer, K, 512, "tc")
+    hid = O.make_hidden(2300 + T, T, 512)
+    rng = np.random.default_rng(T)
+    res = O.bf16_round(rng.standard_normal((T, 512), np.float32) * 2)
+    shared = O.bf16_round(rng.standard_normal((T, 512), np.float32))
+    routed = to_bits(layer.forward(to_dev(hid)))
+    layer.check()
+    got = to_bits(layer.forward_residual(to_dev(hid), to_dev(res), to_dev(shared)))
+    layer.check()
+    want = O.residual_add_shared_f32_delta_bf16(res, shared, O.bf16_to_f32(routed))
+    np.testing.assert_array_equal(got, want)
+    got2 = to_bits(layer.forward_residual(to_dev(hid), to_dev(res)))
+    np.testing.assert_array_equal(got2, O.residual_add_bf16(res, routed))
+    layer.close()
+
+
+def test_decode_step_replays_from_a_cuda_graph(pkg, small_layer):
+    """The forward only enqueues work on the caller's stream (no allocation, no synchronisation
+    after the first call), so a decode step can be captured once and replayed on new inputs, the
+    way the reference replays its routed step (native/cuda/kernels/b12x_direct.cu:1101-1256)."""
+    K, T = 4, 8
+    layer = make(pkg, small_layer, K, 64, "tc")
+    x = to_dev(O.make_hidden(1, T, 512)).clone()
+    out = torch.empty_like(x)
+    layer.forward(x, out=out)                      # first call sets kernel attributes and tensor maps
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer.forward(x, out=out)
+    for seed in (2, 3):
+        hid = O.make_hidden(seed, T, 512)
+        x.copy_(to_dev(hid))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = to_bits(out).copy()
+        eager = to_bits(layer.forward(to_dev(hid)))
+        np.testing.assert_array_equal(replayed, eager)
+    layer.check()
+    layer.close()
+
+
+def test_full_size_prefill_is_row_permutation_equivariant(pkg):
+    """At the full prefill size (GLM-5.2 layer, T = 8192) no CPU oracle is in reach; the property
+    checked instead needs no reference values: a token's result depends on its own row only, so
+    permuting the rows of the batch permutes the rows of the output bit for bit, and 64 of the
+    rows run alone (decode kernels) agree with their rows in the large batch within the gate."""
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K, T = 6144, 2048, 256, 8, 8192
+    layer = MoeLayer(H, I, E, K, max_tokens=T)
+    layer.fill_synthetic(11, 0.02)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    layer.set_router((torch.randn(E, H, generator=g) * 0.02), torch.zeros(E))
+    x = (torch.randn(T, H, generator=g)).to(torch.bfloat16).cuda()
+    perm = torch.randperm(T, generator=g).cuda()
+    out = layer.forward(x).clone()
+    out_p = layer.forward(x[perm].contiguous())
+    layer.check()
+    assert torch.equal(out_p.view(torch.int16), out[perm].view(torch.int16))
+    assert torch.isfinite(out.float()).all() and out.float().abs().max() > 0
+    rows = torch.arange(0, T, T // 64, device="cuda")[:64]
+    small = layer.forward(x[rows].contiguous())
+    layer.check()
+    err = O.rel_l2_per_token(to_bits(small), to_bits(out[rows]))
+    print(f"T=8192 rows vs the same rows alone: max per-token rel L2 {err.max():.3e}")
+    assert err.max() <= 1e-2
+    layer.close()
+
+
 def test_bad_routes_are_reported_not_faulted(pkg, small_layer):
     from glmrt_b200.native import GlmrtError
     K, T = 4, 4

@@ -188,3 +188,22 @@ def test_combine_and_sum_topk():
     assert np.abs(O.bf16_to_f32(out) - ref).max() < 0.1
     s = O.sum_topk_bf16(y)
     assert np.abs(O.bf16_to_f32(s) - O.bf16_to_f32(y).sum(axis=1)).max() < 0.05
+
+
+def test_residual_adds_truncate_like_the_native_kernels():
+    """native/tests/cuda_selftest.cc:1079-1093 inputs; expected values worked out by hand from
+    the kernel's formula: float32 adds, results and the float32 delta truncated to bf16."""
+    res = O.bf16_truncate(np.array([0.25, -0.5, 1.5, 2.0], np.float32))
+    shared = O.bf16_truncate(np.array([-0.25, 0.75, 0.125, -1.5], np.float32))
+    routed = np.array([-0.51, 0.26, 0.501, -1.001], np.float32)
+    out = O.bf16_to_f32(O.residual_add_shared_f32_delta_bf16(res, shared, routed))
+    # bf16(-0.51) = -0.5078125 (truncated), bf16(0.26) = 0.259765625, bf16(0.501) = 0.5, bf16(-1.001) = -1.0
+    # mlp = bf16(shared + routed) = -0.7578125 -> trunc 8 bits: -0.7578125 = -0.11000010b -> -0.75390625
+    want_mlp = O.bf16_to_f32(O.bf16_truncate(np.array([-0.25 - 0.5078125, 0.75 + 0.259765625, 0.125 + 0.5, -1.5 - 1.0], np.float32)))
+    want = O.bf16_to_f32(O.bf16_truncate((O.bf16_to_f32(res) + want_mlp).astype(np.float32)))
+    np.testing.assert_array_equal(out, want)
+    assert out[2] == 2.125 and out[3] == -0.5            # exact cases: 1.5 + 0.625, 2.0 - 2.5
+    # truncation, not rounding: 1 + 2^-8 + 2^-9 keeps only the 2^-8 bit... (7 explicit mantissa bits -> dropped entirely)
+    x = np.array([1.0 + 2.0 ** -8 + 2.0 ** -9], np.float32)
+    assert O.bf16_to_f32(O.bf16_truncate(x))[0] == 1.0
+    assert O.bf16_to_f32(O.residual_add_f32_delta_bf16(O.bf16_truncate(np.array([0.0], np.float32)), x))[0] == 1.0
