@@ -48,6 +48,15 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
+def measured_peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 def layer_algorithmic_bytes(tokens: int, distinct: int) -> int:
     """Bytes one forward must move: weights of the experts actually selected, activations in and
     out, the float32 router weight and the route table."""
@@ -168,7 +177,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
         "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "nvfp4", "data": "synthetic",
-        "config": {"workload": f"glm52_moe_layer_decode_T{args.tokens}", "tokens": args.tokens, "hidden": H,
+        "config": {"workload": f"glm52_moe_layer_{'prefill' if args.tokens > 256 else 'decode'}_T{args.tokens}", "tokens": args.tokens, "hidden": H,
                    "experts": E, "top_k": K_TOP, "intermediate": I},
         "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": "port",
                          "sample": r["sample"]},
@@ -271,11 +280,37 @@ def run_gpu(args):
         cpu = {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": "port",
                "sample": r["sample"]}
 
+    prefill = T > 256          # the layer switches to its tokens-on-the-MMA-rows kernels above 256 rows
+    if not prefill:
+        roofline = {"bound": "hbm", "kernel": "expert_gemm_kernel<FC1>", "achieved": fc1_gbs, "peak": peak,
+                    "unit": "GB/s", "frac": fc1_gbs / peak, "peak_source": peak_kind,
+                    "algorithmic_bytes_per_launch": fc1_bytes, "ms_per_launch": stage_ms["fc1"],
+                    "traffic": NCU_FC1_TRAFFIC_PER_EXPERT * distinct,
+                    "traffic_source": "ncu dram read+write of one FC1 launch on a 64-expert T=16 case "
+                                      "(profiles/expert_gemm_fc1_fc2_E64_T16_ncu_full.md), per expert touched, "
+                                      "times the experts touched here"}
+    else:
+        # prefill: the contraction is what one pays for; FP4 runs at four times the bf16 rate and no
+        # FP4 figure is measured on this pool, so the peak is 4 x the measured bf16 burst figure
+        fc1_flops = routes * 2.0 * (2 * I) * H
+        tf = fc1_flops / (stage_ms["fc1"] * 1e-3) / 1e12
+        bf16_peak, bf16_kind = measured_peak_tflops()
+        roofline = {"bound": "tensor", "kernel": "expert_gemm_tokens_kernel<FC1>", "achieved": tf,
+                    "peak": 4.0 * bf16_peak, "unit": "TFLOP/s", "frac": tf / (4.0 * bf16_peak),
+                    "peak_source": f"4 x bf16 burst ({bf16_kind}); nominal dense FP4 is 9000",
+                    "frac_of_nominal_fp4": tf / 9000.0,
+                    "algorithmic_flops_per_launch": fc1_flops, "ms_per_launch": stage_ms["fc1"],
+                    "hbm_gbs": fc1_gbs, "hbm_frac": fc1_gbs / peak,
+                    "traffic": NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT * distinct,
+                    "traffic_source": "ncu dram read+write of one FC1 launch on a 64-expert T=2048 case "
+                                      "(profiles/expert_gemm_tokens_fc1_fc2_E64_T2048_ncu_full.md), per expert "
+                                      "touched (weights dominate), times the experts touched here"}
+
     line = {
         "metric": "moe_layer_tokens_per_s", "value": T / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
-        "config": {"workload": f"glm52_moe_layer_decode_T{T}", "tokens": T, "hidden": H, "experts": E,
+        "config": {"workload": f"glm52_moe_layer_{'prefill' if prefill else 'decode'}_T{T}", "tokens": T, "hidden": H, "experts": E,
                    "top_k": K_TOP, "intermediate": I, "experts_per_gpu": E,
                    "l2": f"no flush: each step streams {layer_bytes / 1e9:.2f} GB of expert weights, far above the 126 MB L2",
                    "distinct_experts_per_step": distinct, "stage_ms": stage_ms,
@@ -285,13 +320,7 @@ def run_gpu(args):
         "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2,
                 "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_ms},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "kernel": "expert_gemm_kernel<FC1>", "achieved": fc1_gbs, "peak": peak,
-                     "unit": "GB/s", "frac": fc1_gbs / peak, "peak_source": peak_kind,
-                     "algorithmic_bytes_per_launch": fc1_bytes, "ms_per_launch": stage_ms["fc1"],
-                     "traffic": NCU_FC1_TRAFFIC_PER_EXPERT * distinct,
-                     "traffic_source": "ncu dram read+write of one FC1 launch on a 64-expert T=16 case "
-                                       "(profiles/expert_gemm_fc1_fc2_E64_T16_ncu_full.md), per expert touched, "
-                                       "times the experts touched here"},
+        "roofline": roofline,
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
@@ -373,7 +402,7 @@ def run_ep(args, dist, rank, world, local_rank):
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4",
             "data": "synthetic",
-            "config": {"workload": f"glm52_moe_layer_decode_T{T}", "tokens": T, "hidden": H, "experts": E,
+            "config": {"workload": f"glm52_moe_layer_{'prefill' if T > 256 else 'decode'}_T{T}", "tokens": T, "hidden": H, "experts": E,
                        "top_k": K_TOP, "intermediate": I, "experts_per_gpu": E // world,
                        "parallelism": f"ep{world}: expert e on rank e % {world}, rows block-partitioned, "
                                       "dispatch/combine = in-kernel NVLink peer stores",
@@ -401,9 +430,11 @@ def run_ep(args, dist, rank, world, local_rank):
     dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch (818.80 MB, 57 experts touched)
-# from the ncu capture summarised under profiles/: DRAM traffic per expert touched.
-NCU_FC1_TRAFFIC_PER_EXPERT = 818.80e6 / 57
+# dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch from the ncu captures summarised
+# under profiles/, per expert touched: decode kernel (820.55 MB, 57 experts touched) and prefill
+# kernel (1014.57 MB, 64 experts).
+NCU_FC1_TRAFFIC_PER_EXPERT = 820.55e6 / 57
+NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT = 1014.57e6 / 64
 
 
 def main():
