@@ -61,6 +61,9 @@ glmrt_status_t launch_quantize_weight_f32(const float* in, uint8_t* packed, uint
                                           uint32_t* amax_scratch, size_t rows, size_t cols, cudaStream_t stream);
 
 // ---- plan.cu ----
+// A route entry with this expert id is "no route": it gets no slot and is not an error (the
+// expert worker's view of a request may name fewer than top_k experts for a row).
+constexpr uint32_t kNoRoute = 0xffffffffu;
 struct PlanArgs {
   const uint32_t* topk_indices;  // [rows * top_k] global expert ids
   int rows, top_k, experts;      // experts = global count
@@ -137,6 +140,17 @@ glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* to
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
                                      cudaStream_t stream, const uint16_t* residual = nullptr,
                                      const uint16_t* shared = nullptr);
+
+// ---- layer.cu: entry used by the ExpertProtocolV2 executor (protocol_v2.cu) ----
+struct LayerDims { uint32_t hidden, experts, top_k, max_tokens, ep_world, ep_rank; };
+glmrt_status_t layer_dims(void* layer, LayerDims* out);
+// Runs `rows` host rows (bf16, or NVFP4 payload rows when hidden_is_payload) with host route tables
+// [rows, top_k] (expert kNoRoute = none) through the layer and writes bf16 rows, or NVFP4 payload
+// rows in the native rounding rule when out_is_payload, to host memory.  Synchronises the stream
+// and reports the device error word.
+glmrt_status_t layer_execute_host_rows(void* layer, const void* hidden_host, bool hidden_is_payload, size_t hidden_stride,
+                                       size_t rows, const uint32_t* idx_host, const float* w_host, bool out_is_payload,
+                                       void* out_host, size_t out_stride, cudaStream_t stream);
 
 // ---- ffn_simt.cu (verification engine) ----
 struct FfnArgs {

@@ -176,6 +176,7 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
 }
 
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
+// `hidden` == nullptr: the payload rows are already in l->payload (a request that carried NVFP4 rows).
 glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream,
                           const uint16_t* residual = nullptr, const uint16_t* shared = nullptr) {
   const auto& c = l->cfg;
@@ -195,9 +196,9 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
   // The plan needs only the routes, so it runs first and the rows are quantised and dispatched by
   // one kernel (its time is reported as the dispatch stage, the quantise stage then reads 0).
-  const bool fused = quantize_dispatch_supported(hidden, d);
+  const bool fused = hidden != nullptr && quantize_dispatch_supported(hidden, d);
   mark(l, GLMRT_B200_STAGE_QUANTIZE, stream);
-  if (!fused)
+  if (!fused && hidden != nullptr)
     GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
                                                        GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
   mark(l, GLMRT_B200_STAGE_PLAN, stream);
@@ -229,8 +230,8 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
                                              : launch_fc2_tc_prefill(f, maps, l->sm_count, stream));
   }
   mark(l, GLMRT_B200_STAGE_COMBINE, stream);
-  // with one shard every route is local; a shard of an expert-parallel layer only sums its own
-  const int32_t* mask = c.ep_world > 1 ? l->route_slot : nullptr;
+  // routes without a slot (another shard's expert, a "no route" entry, a refused plan) are skipped
+  const int32_t* mask = l->route_slot;
   GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
                                               static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream,
                                               residual, shared));
@@ -511,6 +512,49 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_host(void* layer, const v
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "forward_host synchronize", err);
   return ok();
 }
+
+namespace glmrt {
+
+glmrt_status_t layer_dims(void* layer, LayerDims* out) {
+  Layer* l = static_cast<Layer*>(layer);
+  if (l == nullptr || out == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
+  const auto& c = l->cfg;
+  *out = LayerDims{c.hidden_dim, c.experts, c.top_k, c.max_tokens, c.ep_world, c.ep_rank};
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t layer_execute_host_rows(void* layer, const void* hidden_host, bool hidden_is_payload, size_t hidden_stride,
+                                       size_t rows, const uint32_t* idx_host, const float* w_host, bool out_is_payload,
+                                       void* out_host, size_t out_stride, cudaStream_t s) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
+  const auto& c = l->cfg;
+  const size_t H = c.hidden_dim, routes = rows * c.top_k;
+  const size_t payload_row = H / 2 + H / 16, bf16_row = H * 2;
+  cudaError_t err = cudaMemcpyAsync(l->topk_idx, idx_host, routes * 4, cudaMemcpyHostToDevice, s);
+  if (err == cudaSuccess) err = cudaMemcpyAsync(l->topk_w, w_host, routes * 4, cudaMemcpyHostToDevice, s);
+  if (err == cudaSuccess)
+    err = hidden_is_payload ? cudaMemcpy2DAsync(l->payload, payload_row, hidden_host, hidden_stride, payload_row, rows,
+                                                cudaMemcpyHostToDevice, s)
+                            : cudaMemcpy2DAsync(l->hidden_stage, bf16_row, hidden_host, hidden_stride, bf16_row, rows,
+                                                cudaMemcpyHostToDevice, s);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "executor input copy", err);
+  const uint64_t before = launches_total();
+  mark(l, GLMRT_B200_STAGE_ROUTER, s);
+  GLMRT_RETURN_IF_ERROR(run_routed(l, hidden_is_payload ? nullptr : l->hidden_stage, rows, l->out_stage, s));
+  if (out_is_payload) {
+    // response rows in the wire format, with the native kernel's rounding rule (nvfp4_payload.cu:11-33)
+    GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(l->out_stage, l->payload, rows, H, GLMRT_B200_FP4_RULE_RNE_PAYLOAD, s));
+    err = cudaMemcpy2DAsync(out_host, out_stride, l->payload, payload_row, payload_row, rows, cudaMemcpyDeviceToHost, s);
+  } else {
+    err = cudaMemcpy2DAsync(out_host, out_stride, l->out_stage, bf16_row, bf16_row, rows, cudaMemcpyDeviceToHost, s);
+  }
+  l->launches_last = static_cast<uint32_t>(launches_total() - before);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "executor output copy", err);
+  return glmrt_b200_moe_layer_check(layer, s);
+}
+
+}  // namespace glmrt
 
 extern "C" glmrt_status_t glmrt_b200_moe_layer_check(void* layer, void* cuda_stream) {
   Layer* l = static_cast<Layer*>(layer);

@@ -31,7 +31,9 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
   for (int r = threadIdx.x; r < n; r += kPlanThreads) {
     const uint32_t e = a.topk_indices[r];
     int pos = -1;
-    if (e >= static_cast<uint32_t>(a.experts)) {
+    if (e == kNoRoute) {
+      // nothing to do for this entry
+    } else if (e >= static_cast<uint32_t>(a.experts)) {
       atomicOr(&s_error, static_cast<int>(kErrBadExpert));
     } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
       pos = atomicAdd(&cnt[e / a.ep_world], 1);
@@ -128,7 +130,9 @@ __global__ void __launch_bounds__(kPlanBlock) plan_count_kernel(PlanArgs a, int 
   if (r < a.rows * a.top_k) {
     const uint32_t e = a.topk_indices[r];
     int pos = -1;
-    if (e >= static_cast<uint32_t>(a.experts)) {
+    if (e == kNoRoute) {
+      // nothing to do for this entry
+    } else if (e >= static_cast<uint32_t>(a.experts)) {
       atomicOr(&a.counters[kCntError], static_cast<uint32_t>(kErrBadExpert));
     } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
       pos = atomicAdd(&hist[e / a.ep_world], 1);

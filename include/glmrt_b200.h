@@ -403,6 +403,144 @@ glmrt_status_t glmrt_b200_moe_layer_forward_ep_phase_async(void* layer, uint32_t
 glmrt_status_t glmrt_b200_moe_layer_forward_ep_host(void* layer, const void* hidden_host, size_t rows,
                                                     void* output_host, void* cuda_stream);
 
+/* ------------------------------------------------------------------------ */
+/* ExpertProtocolV2 frames and the expert executor (host side).               */
+/* The wire format of rust/crates/glmrt-transport/src/protocol_v2.rs and its   */
+/* protocol_v2/{request,response,view}.rs: little-endian, 96-byte headers      */
+/* (128 with the debug checksum), 40-byte row descriptors, 10-byte route       */
+/* entries (row, expert, bf16 gate weight), then the row payload.  Regular     */
+/* request and response frames are encoded, parsed and validated with the      */
+/* reference's rules; stream-plan, stream-data and layer-block frames are      */
+/* recognised and refused by the executor.  All functions are host-only and    */
+/* need no GPU except glmrt_b200_pv2_execute.                                  */
+/* ------------------------------------------------------------------------ */
+enum {                                     /* protocol_v2.rs:10-34 */
+  GLMRT_B200_PV2_REQUEST_HEADER_LEN = 96,
+  GLMRT_B200_PV2_RESPONSE_HEADER_LEN = 96,
+  GLMRT_B200_PV2_DEBUG_HEADER_LEN = 128,
+  GLMRT_B200_PV2_ROW_DESCRIPTOR_LEN = 40,
+  GLMRT_B200_PV2_ROUTE_ENTRY_LEN = 10,
+  GLMRT_B200_PV2_FLAG_DEBUG_CHECKSUM = 1u << 0,
+  GLMRT_B200_PV2_FLAG_PRECOMPILE_WARMUP = 1u << 1,
+  GLMRT_B200_PV2_FLAG_RESPONSE_ROW_INDICES = 1u << 2,
+  GLMRT_B200_PV2_FLAG_RESPONSE_MORE_CHUNKS = 1u << 3,
+  GLMRT_B200_PV2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED = 1u << 4,
+  GLMRT_B200_PV2_FLAG_RESPONSE_NVFP4_E2M1_FP8_E4M3 = 1u << 5,
+  GLMRT_B200_PV2_FLAG_STREAM_PLAN = 1u << 6,
+  GLMRT_B200_PV2_FLAG_STREAM_DATA = 1u << 7,
+  GLMRT_B200_PV2_FLAG_STREAM_FINAL = 1u << 8,
+  GLMRT_B200_PV2_FLAG_SPARK_REDUCTION = 1u << 9,
+  GLMRT_B200_PV2_FLAG_LAYER_BLOCK = 1u << 10,
+  GLMRT_B200_PV2_FLAG_SPARK_ROW_SHARDED_REDUCTION = 1u << 11,
+  GLMRT_B200_PV2_SPARK_COLLECTIVE_PART_COUNT_SHIFT = 12,   /* four bits */
+};
+enum {                                     /* ExpertV2Dtype, protocol_v2.rs:44-51 */
+  GLMRT_B200_PV2_DTYPE_BF16 = 1,
+  GLMRT_B200_PV2_DTYPE_F16 = 2,
+  GLMRT_B200_PV2_DTYPE_FP8_DEBUG = 3,
+  GLMRT_B200_PV2_DTYPE_NVFP4_E2M1_FP8_E4M3 = 4,   /* elements/2 code bytes + elements/16 scale bytes per row */
+  GLMRT_B200_PV2_DTYPE_FP8_E4M3_ROW_SCALED = 5,   /* elements bytes + one float32 scale per row */
+};
+typedef struct glmrt_b200_pv2_request_header_t {   /* ExpertProtocolV2RequestHeader, protocol_v2.rs:236-250 */
+  uint64_t request_id;
+  uint64_t placement_version;
+  uint32_t layer_id;
+  uint32_t row_count;
+  uint32_t hidden_dim;
+  uint32_t hidden_dtype;
+  uint32_t hidden_row_stride_bytes;
+  uint32_t route_count;
+  uint32_t row_descriptor_bytes;
+  uint32_t route_bytes;
+  uint64_t hidden_payload_bytes;
+  uint32_t flags;
+  uint32_t header_len;            /* 96 or 128; filled by parse and encode */
+} glmrt_b200_pv2_request_header_t;
+typedef struct glmrt_b200_pv2_row_t {               /* ExpertProtocolV2RowDescriptor, protocol_v2.rs:252-260 */
+  uint64_t row_id;
+  uint64_t source_request_id;
+  uint64_t token_position;
+  uint32_t route_offset;
+  uint32_t route_count;
+  uint32_t source_kind;           /* 1 decode, 2 prefill, 3 MTP verify, 4 benchmark */
+  uint32_t reserved;
+} glmrt_b200_pv2_row_t;
+typedef struct glmrt_b200_pv2_route_t {             /* ExpertProtocolV2RouteEntry, protocol_v2.rs:262-267 */
+  uint32_t row_index;
+  uint32_t expert_id;
+  float gate_weight;              /* travels as bf16 (truncated), protocol_v2.rs:584-608 */
+} glmrt_b200_pv2_route_t;
+typedef struct glmrt_b200_pv2_response_header_t {   /* ExpertProtocolV2ResponseHeader, protocol_v2.rs:269-282 */
+  uint64_t request_id;
+  uint64_t placement_version;
+  uint32_t layer_id;
+  uint32_t row_count;
+  uint32_t output_dim;
+  uint32_t output_dtype;
+  uint32_t output_row_stride_bytes;
+  uint32_t status;                /* 0 ok, 1 error */
+  uint64_t output_payload_bytes;
+  uint32_t flags;
+  uint32_t header_len;
+  uint64_t executor_id;
+} glmrt_b200_pv2_response_header_t;
+/* Where the sections of a parsed frame start (byte offsets into the frame). */
+typedef struct glmrt_b200_pv2_sections_t {
+  uint64_t rows_offset;           /* request: row descriptors; response: row-index table (or payload_offset) */
+  uint64_t routes_offset;         /* request only */
+  uint64_t payload_offset;
+  uint64_t payload_bytes;
+} glmrt_b200_pv2_sections_t;
+
+/* ExpertV2Dtype::row_bytes (protocol_v2.rs:61-83). */
+glmrt_status_t glmrt_b200_pv2_row_bytes(uint32_t dtype, size_t elements, size_t* out_bytes);
+/* expert_protocol_v2_compact_id (protocol_v2.rs:229-232): first 8 bytes, little-endian, of SHA-256(name). */
+glmrt_status_t glmrt_b200_pv2_compact_id(const char* name, uint64_t* out_id);
+/* SHA-256 of a byte range (the digest behind the debug checksum and the compact id). */
+glmrt_status_t glmrt_b200_pv2_sha256(const void* bytes, size_t len, uint8_t out_digest[32]);
+/* ExpertProtocolV2Request::{validate, encode_into} (protocol_v2/request.rs:327-379, 516-633).  The
+ * counts and byte sizes of `header` are taken from the arguments; request_id, placement_version,
+ * layer_id, hidden_dim, hidden_dtype, hidden_row_stride_bytes (0 = the dtype's row size) and flags
+ * from `header`.  Gate weights are made canonical (bf16) first.  *out_len receives the frame size
+ * also when `out` is too small (BUFFER_TOO_SMALL). */
+glmrt_status_t glmrt_b200_pv2_encode_request(const glmrt_b200_pv2_request_header_t* header,
+                                             const glmrt_b200_pv2_row_t* rows, size_t row_count,
+                                             const glmrt_b200_pv2_route_t* routes, size_t route_count,
+                                             const void* hidden_payload, size_t hidden_payload_bytes,
+                                             void* out, size_t out_capacity, size_t* out_len);
+/* ExpertProtocolV2RequestView::parse (protocol_v2/view.rs:33-136): validates the frame and all
+ * rows and routes like Request::decode, without copying and without checking the checksum. */
+glmrt_status_t glmrt_b200_pv2_parse_request(const void* frame, size_t frame_bytes,
+                                            glmrt_b200_pv2_request_header_t* out_header,
+                                            glmrt_b200_pv2_sections_t* out_sections);
+glmrt_status_t glmrt_b200_pv2_request_row(const void* frame, size_t frame_bytes, size_t index,
+                                          glmrt_b200_pv2_row_t* out_row);
+glmrt_status_t glmrt_b200_pv2_request_route(const void* frame, size_t frame_bytes, size_t index,
+                                            glmrt_b200_pv2_route_t* out_route);
+/* verify_checksum (protocol_v2/view.rs:299-330, :581-600): OK when the frame carries no checksum. */
+glmrt_status_t glmrt_b200_pv2_verify_request_checksum(const void* frame, size_t frame_bytes);
+glmrt_status_t glmrt_b200_pv2_verify_response_checksum(const void* frame, size_t frame_bytes);
+/* ExpertProtocolV2Response::{validate, encode_into} (protocol_v2/response.rs:130-174, 577-642).
+ * row_indices may be NULL unless the header's flags ask for the row-index table. */
+glmrt_status_t glmrt_b200_pv2_encode_response(const glmrt_b200_pv2_response_header_t* header,
+                                              const uint32_t* row_indices, const void* payload,
+                                              size_t payload_bytes, void* out, size_t out_capacity,
+                                              size_t* out_len);
+glmrt_status_t glmrt_b200_pv2_parse_response(const void* frame, size_t frame_bytes,
+                                             glmrt_b200_pv2_response_header_t* out_header,
+                                             glmrt_b200_pv2_sections_t* out_sections);
+/* The executor (ProtocolV2ExpertExecutor::execute_with_identity, glmrt-transport/src/synthetic.rs:
+ * 51-66, in the role of RealNvfp4ProtocolV2Executor, protocol_v2_executor.rs:1882-2493): parses a
+ * regular request frame, runs its rows through the experts of `layer` that its routes name
+ * (hidden dtype bf16 or NVFP4 payload rows; at most top_k routes per row; routes of experts that
+ * do not live on this layer's shard are refused) and writes a response frame with one partial
+ * output row per request row: bf16, or NVFP4 payload rows when the request negotiates them
+ * (native rounding rule).  The row-scaled FP8 response is refused.  The executor id is the compact
+ * id of "b200-nvfp4-tcgen05-executor".  Synchronises `cuda_stream`. */
+glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* request_frame, size_t request_bytes,
+                                      void* response_out, size_t response_capacity,
+                                      size_t* response_len, void* cuda_stream);
+
 /* Per-stage device times of the last forward, measured with CUDA events recorded on the
  * caller's stream between the kernels (reference precedent: the CUDA-event timeline behind
  * GLMRT_REAL_FULL_NVFP4_ROUTE_CUDA_EVENT_TIMING, sparse_mlp/route.rs:1010-1062). */

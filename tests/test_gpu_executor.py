@@ -1,0 +1,158 @@
+"""The ExpertProtocolV2 executor on the GPU: request frame in, response frame out, through
+``glmrt_b200_pv2_execute`` (the expert worker's side of the reference's wire protocol,
+rust/crates/glmrt-transport/src/synthetic.rs:51-107 and real_full/expert_probe/
+protocol_v2_executor.rs:1882-2493).  Partial output rows must equal what the layer computes for
+the same rows and routes through its device-buffer entry point, bit for bit.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import glmrt_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def to_dev(bits):
+    return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).cuda()
+
+
+def to_bits(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def ref_layer():
+    return O.make_layer(21, 512, 256, 16)
+
+
+def build_request(P, hid_bits, idx, w, keep=lambda row, expert: True, dtype=None, payload=None, flags=0, request_id=77):
+    rows, routes = [], []
+    for r in range(idx.shape[0]):
+        first = len(routes)
+        for k in range(idx.shape[1]):
+            if keep(r, int(idx[r, k])):
+                routes.append(P.ExpertProtocolV2RouteEntry(r, int(idx[r, k]), float(w[r, k])))
+        rows.append(P.ExpertProtocolV2RowDescriptor(500 + r, P.ExpertV2SourceKind.Decode, 9, 100 + r, first, len(routes) - first))
+    dtype = dtype or P.ExpertV2Dtype.Bf16
+    body = payload if payload is not None else hid_bits.tobytes()
+    return P.ExpertProtocolV2Request(request_id, 3, 5, hid_bits.shape[1], dtype, rows, routes, body, 0, flags)
+
+
+def wire_weights(w):
+    """Gate weights as they arrive: truncated to bf16 (protocol_v2.rs:584-608)."""
+    return (w.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+
+
+def test_executor_matches_forward_routed_bit_for_bit(pkg, ref_layer):
+    from glmrt_b200 import protocol_v2 as P
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K, T = 512, 256, 16, 4, 24
+    layer = MoeLayer(H, I, E, K, max_tokens=64)
+    layer.load_quantized_layer(ref_layer)
+    hid = O.make_hidden(31, T, H)
+    _, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    idx, w = idx.cpu().numpy(), w.cpu().numpy()
+    want = to_bits(layer.forward_routed(to_dev(hid), torch.from_numpy(idx).cuda(), torch.from_numpy(wire_weights(w)).cuda()))
+    ex = P.B200MoeExecutor(layer)
+    req = build_request(P, hid, idx, w)
+    resp = ex.execute(P.ExpertProtocolV2RequestView.parse(req.encode()))
+    assert resp.status == P.ExpertProtocolV2Status.Ok and resp.request_id == 77 and resp.layer_id == 5
+    assert resp.row_count == T and resp.output_dim == H and resp.output_dtype == P.ExpertV2Dtype.Bf16
+    assert resp.executor_id == P.expert_protocol_v2_compact_id(ex.name())
+    got = np.frombuffer(resp.partial_output_payload, np.uint16).reshape(T, H)
+    np.testing.assert_array_equal(got, want)
+    st = layer.stats()
+    assert st.device_error == 0 and st.launches_last_forward >= 5
+
+    # the same rows sent as NVFP4 payload rows (3456-byte rows for 6144; here 288): identical result
+    from glmrt_b200 import native as N
+    pay = torch.zeros(T * (H // 2 + H // 16), dtype=torch.uint8, device="cuda")
+    x = to_dev(hid)
+    layer.lib.call("glmrt_b200_quantize_bf16_nvfp4_row_payload_async", N.DeviceBuffer.of(x.data_ptr(), x.numel() * 2),
+                   N.DeviceBuffer.of(pay.data_ptr(), pay.numel()), C.c_size_t(T), C.c_size_t(H), C.c_uint32(1),      # 1 = the layer's rule (nearest, ties low)
+                   C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    req4 = build_request(P, hid, idx, w, dtype=P.ExpertV2Dtype.Nvfp4E2m1Fp8E4m3, payload=pay.cpu().numpy().tobytes())
+    assert len(req4.encode()) == 96 + 40 * T + 10 * T * K + T * (H // 2 + H // 16)
+    resp4 = ex.execute(P.ExpertProtocolV2RequestView.parse(req4.encode()))
+    np.testing.assert_array_equal(np.frombuffer(resp4.partial_output_payload, np.uint16).reshape(T, H), want)
+
+    # a checksummed request gets a checksummed response; the NVFP4 response dtype is negotiated by flag
+    flags = P.EXPERT_PROTOCOL_V2_FLAG_DEBUG_CHECKSUM | P.EXPERT_PROTOCOL_V2_FLAG_RESPONSE_NVFP4_E2M1_FP8_E4M3
+    frame = ex.execute_frame(build_request(P, hid, idx, w, flags=flags).encode())
+    respq = P.ExpertProtocolV2Response.decode(frame)          # verifies the response checksum
+    assert respq.flags & P.EXPERT_PROTOCOL_V2_FLAG_DEBUG_CHECKSUM and respq.output_dtype == P.ExpertV2Dtype.Nvfp4E2m1Fp8E4m3
+    assert respq.output_row_stride_bytes == H // 2 + H // 16
+    outq = torch.zeros(T * (H // 2 + H // 16), dtype=torch.uint8, device="cuda")
+    y = to_dev(want)
+    layer.lib.call("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", N.DeviceBuffer.of(y.data_ptr(), y.numel() * 2),
+                   N.DeviceBuffer.of(outq.data_ptr(), outq.numel()), C.c_size_t(T), C.c_size_t(H),
+                   C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert respq.partial_output_payload == outq.cpu().numpy().tobytes()
+    layer.close()
+
+
+def test_executor_on_a_shard_takes_only_its_own_routes(pkg, ref_layer):
+    """The coordinator sends each expert host the routes of the experts it owns (placement.rs:25-42);
+    rows may then carry fewer than top_k routes, or none.  The two hosts' partial rows equal the
+    shard layers' own partial forward."""
+    from glmrt_b200 import protocol_v2 as P
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K, T = 512, 256, 16, 4, 40
+    full = MoeLayer(H, I, E, K, max_tokens=64)
+    full.load_quantized_layer(ref_layer)
+    hid = O.make_hidden(32, T, H)
+    _, idx, w = full.forward(to_dev(hid), want_routes=True)
+    idx, w = idx.cpu().numpy(), w.cpu().numpy()
+    full.close()
+    for rank in (0, 1):
+        shard = MoeLayer(H, I, E, K, max_tokens=64, ep_world=2, ep_rank=rank)
+        shard.load_quantized_layer(ref_layer)
+        want = to_bits(shard.forward_routed(to_dev(hid), torch.from_numpy(idx).cuda(), torch.from_numpy(wire_weights(w)).cuda()))
+        req = build_request(P, hid, idx, w, keep=lambda r, e: e % 2 == rank)
+        assert len(req.routes) < T * K
+        resp = P.B200MoeExecutor(shard).execute(P.ExpertProtocolV2RequestView.parse(req.encode()))
+        np.testing.assert_array_equal(np.frombuffer(resp.partial_output_payload, np.uint16).reshape(T, H), want)
+        shard.check()
+        shard.close()
+
+
+def test_executor_refuses_what_it_cannot_run(pkg, ref_layer):
+    from glmrt_b200 import native as N
+    from glmrt_b200 import protocol_v2 as P
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K, T = 512, 256, 16, 4, 4
+    layer = MoeLayer(H, I, E, K, max_tokens=8, ep_world=2, ep_rank=0)
+    layer.load_quantized_layer(ref_layer)
+    ex = P.B200MoeExecutor(layer)
+    hid = O.make_hidden(33, T, H)
+    idx = np.tile(np.array([[0, 2, 4, 6]], np.int32), (T, 1))
+    w = np.full((T, K), 0.625, np.float32)
+    good = build_request(P, hid, idx, w)
+    ex.execute_frame(good.encode())
+    cases = [
+        (build_request(P, hid, idx + 1, w), "does not live on this shard"),
+        (build_request(P, hid, np.tile(idx, (1, 2)), np.tile(w, (1, 2))), "top_k is 4"),
+        (build_request(P, O.make_hidden(1, T, 256), idx, w), "does not match the layer"),
+        (build_request(P, hid, idx, w, flags=P.EXPERT_PROTOCOL_V2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED), "row-scaled FP8"),
+        (build_request(P, hid, idx, w, flags=P.EXPERT_PROTOCOL_V2_FLAG_LAYER_BLOCK, keep=lambda r, e: False), "not supported"),
+        (build_request(P, O.make_hidden(2, 9, H), np.tile(idx[:1], (9, 1)), np.tile(w[:1], (9, 1))), "max_tokens"),
+    ]
+    for req, msg in cases:
+        with pytest.raises(N.GlmrtError, match=msg):
+            ex.execute_frame(req.encode())
+    # a response buffer that is too small is reported with the size needed; nothing ran
+    frame = good.encode()
+    n = C.c_size_t()
+    small = C.create_string_buffer(200)
+    st = layer.lib.call_status("glmrt_b200_pv2_execute", layer.handle, frame, C.c_size_t(len(frame)), small, C.c_size_t(200),
+                               C.byref(n), None)
+    assert st == 2 and n.value == 96 + T * H * 2
+    # the context is still usable
+    ex.execute_frame(good.encode())
+    layer.check()
+    layer.close()
