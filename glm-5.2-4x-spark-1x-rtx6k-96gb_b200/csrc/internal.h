@@ -141,15 +141,20 @@ glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* to
                                      cudaStream_t stream, const uint16_t* residual = nullptr,
                                      const uint16_t* shared = nullptr);
 
+// ---- residual.cu ----
+glmrt_status_t launch_bf16_rows_to_fp8_row_scaled(const uint16_t* src, uint8_t* dst, size_t rows, size_t row_width,
+                                                  size_t dst_row_stride_bytes, cudaStream_t stream);
+
 // ---- layer.cu: entry used by the ExpertProtocolV2 executor (protocol_v2.cu) ----
 struct LayerDims { uint32_t hidden, experts, top_k, max_tokens, ep_world, ep_rank; };
 glmrt_status_t layer_dims(void* layer, LayerDims* out);
 // Runs `rows` host rows (bf16, or NVFP4 payload rows when hidden_is_payload) with host route tables
 // [rows, top_k] (expert kNoRoute = none) through the layer and writes bf16 rows, or NVFP4 payload
-// rows in the native rounding rule when out_is_payload, to host memory.  Synchronises the stream
-// and reports the device error word.
+// rows in the native rounding rule (out_kind 1) or row-scaled FP8 rows (out_kind 2), to host memory.
+// Synchronises the stream and reports the device error word.
+enum { kOutBf16 = 0, kOutNvfp4Payload = 1, kOutFp8RowScaled = 2 };
 glmrt_status_t layer_execute_host_rows(void* layer, const void* hidden_host, bool hidden_is_payload, size_t hidden_stride,
-                                       size_t rows, const uint32_t* idx_host, const float* w_host, bool out_is_payload,
+                                       size_t rows, const uint32_t* idx_host, const float* w_host, int out_kind,
                                        void* out_host, size_t out_stride, cudaStream_t stream);
 
 // ---- ffn_simt.cu (verification engine) ----

@@ -524,7 +524,7 @@ glmrt_status_t layer_dims(void* layer, LayerDims* out) {
 }
 
 glmrt_status_t layer_execute_host_rows(void* layer, const void* hidden_host, bool hidden_is_payload, size_t hidden_stride,
-                                       size_t rows, const uint32_t* idx_host, const float* w_host, bool out_is_payload,
+                                       size_t rows, const uint32_t* idx_host, const float* w_host, int out_kind,
                                        void* out_host, size_t out_stride, cudaStream_t s) {
   Layer* l = static_cast<Layer*>(layer);
   GLMRT_RETURN_IF_ERROR(validate_forward(l, rows));
@@ -542,10 +542,15 @@ glmrt_status_t layer_execute_host_rows(void* layer, const void* hidden_host, boo
   const uint64_t before = launches_total();
   mark(l, GLMRT_B200_STAGE_ROUTER, s);
   GLMRT_RETURN_IF_ERROR(run_routed(l, hidden_is_payload ? nullptr : l->hidden_stage, rows, l->out_stage, s));
-  if (out_is_payload) {
+  if (out_kind == kOutNvfp4Payload) {
     // response rows in the wire format, with the native kernel's rounding rule (nvfp4_payload.cu:11-33)
     GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(l->out_stage, l->payload, rows, H, GLMRT_B200_FP4_RULE_RNE_PAYLOAD, s));
     err = cudaMemcpy2DAsync(out_host, out_stride, l->payload, payload_row, payload_row, rows, cudaMemcpyDeviceToHost, s);
+  } else if (out_kind == kOutFp8RowScaled) {
+    // H + 4 bytes per row; the input stage is free again and large enough (2H per row)
+    uint8_t* fp8 = reinterpret_cast<uint8_t*>(l->hidden_stage);
+    GLMRT_RETURN_IF_ERROR(launch_bf16_rows_to_fp8_row_scaled(l->out_stage, fp8, rows, H, H + 4, s));
+    err = cudaMemcpy2DAsync(out_host, out_stride, fp8, H + 4, H + 4, rows, cudaMemcpyDeviceToHost, s);
   } else {
     err = cudaMemcpy2DAsync(out_host, out_stride, l->out_stage, bf16_row, bf16_row, rows, cudaMemcpyDeviceToHost, s);
   }

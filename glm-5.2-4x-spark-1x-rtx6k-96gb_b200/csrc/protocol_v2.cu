@@ -584,8 +584,6 @@ extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* reques
   GLMRT_RETURN_IF_ERROR(parse_request(b, request_bytes, &h, &sec));
   if (h.flags & (GLMRT_B200_PV2_FLAG_STREAM_PLAN | GLMRT_B200_PV2_FLAG_STREAM_DATA | GLMRT_B200_PV2_FLAG_LAYER_BLOCK))
     return bad("executor: streamed-ingress and layer-block frames are not supported, only regular requests");
-  if (h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED)
-    return bad("executor: the row-scaled FP8 response dtype is not supported (bf16 and NVFP4 are)");
   // the reference's executors check the checksum of a frame that carries one (synthetic.rs:124)
   GLMRT_RETURN_IF_ERROR(glmrt_b200_pv2_verify_request_checksum(request_frame, request_bytes));
   LayerDims d;
@@ -624,8 +622,13 @@ extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* reques
   glmrt_b200_pv2_response_header_t rh{};
   rh.request_id = h.request_id; rh.placement_version = h.placement_version; rh.layer_id = h.layer_id;
   rh.row_count = h.row_count; rh.output_dim = h.hidden_dim;
-  const bool out_payload = h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_NVFP4_E2M1_FP8_E4M3;
-  rh.output_dtype = out_payload ? GLMRT_B200_PV2_DTYPE_NVFP4_E2M1_FP8_E4M3 : GLMRT_B200_PV2_DTYPE_BF16;
+  // response dtype negotiated by the request's flags (view.rs:258-264)
+  const int out_kind = (h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_NVFP4_E2M1_FP8_E4M3)   ? kOutNvfp4Payload
+                       : (h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED) ? kOutFp8RowScaled
+                                                                                       : kOutBf16;
+  rh.output_dtype = out_kind == kOutNvfp4Payload   ? GLMRT_B200_PV2_DTYPE_NVFP4_E2M1_FP8_E4M3
+                    : out_kind == kOutFp8RowScaled ? GLMRT_B200_PV2_DTYPE_FP8_E4M3_ROW_SCALED
+                                                   : GLMRT_B200_PV2_DTYPE_BF16;
   size_t out_row = 0;
   GLMRT_RETURN_IF_ERROR(row_bytes(rh.output_dtype, rh.output_dim, &out_row));
   rh.output_row_stride_bytes = static_cast<uint32_t>(out_row);
@@ -640,7 +643,7 @@ extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* reques
   uint8_t* out = static_cast<uint8_t*>(response_out);
   // the partial output rows land directly behind the header
   GLMRT_RETURN_IF_ERROR(layer_execute_host_rows(layer, b + sec.payload_offset, in_payload, h.hidden_row_stride_bytes, rows,
-                                                idx.data(), w.data(), out_payload, out + header_len, out_row,
+                                                idx.data(), w.data(), out_kind, out + header_len, out_row,
                                                 static_cast<cudaStream_t>(cuda_stream)));
   return glmrt_b200_pv2_encode_response(&rh, nullptr, out + header_len, payload_bytes, out, response_capacity, response_len);
 }

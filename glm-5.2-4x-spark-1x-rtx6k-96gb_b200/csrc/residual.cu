@@ -50,15 +50,74 @@ glmrt_status_t run(const uint16_t* residual, const uint16_t* delta_bf16, const f
   return ok();
 }
 
+// bf16 rows -> E4M3 bytes followed by one float32 scale per row (the reference's response dtype
+// Fp8E4m3RowScaled, native/cuda/kernels/residual.cu:245-277): scale = max |finite value| / 448 (1 when
+// the row is all zero), byte = e4m3(value / scale) with saturation, non-finite values encode 0.
+__global__ void __launch_bounds__(kThreads)
+bf16_rows_to_fp8_row_scaled_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ dst, size_t row_width,
+                                   size_t dst_row_stride_bytes) {
+  __shared__ float warp_max[kThreads / 32];
+  __shared__ float row_scale;
+  const uint16_t* source = src + blockIdx.x * row_width;
+  uint8_t* output = dst + blockIdx.x * dst_row_stride_bytes;
+  float m = 0.0f;
+  for (size_t col = threadIdx.x; col < row_width; col += kThreads) {
+    const float v = bf16_bits_to_f32(source[col]);
+    m = fmaxf(m, isfinite(v) ? fabsf(v) : 0.0f);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float all = 0.0f;
+    for (int i = 0; i < kThreads / 32; ++i) all = fmaxf(all, warp_max[i]);
+    row_scale = all > 0.0f ? __fdiv_rn(all, 448.0f) : 1.0f;
+    *reinterpret_cast<float*>(output + row_width) = row_scale;
+  }
+  __syncthreads();
+  const float scale = row_scale;
+  for (size_t col = threadIdx.x; col < row_width; col += kThreads) {
+    const float v = bf16_bits_to_f32(source[col]);
+    output[col] = static_cast<uint8_t>(f32_to_e4m3_satfinite(isfinite(v) ? __fdiv_rn(v, scale) : 0.0f));
+  }
+}
+
 glmrt_status_t sync_null(glmrt_status_t st) {
   if (st != GLMRT_STATUS_OK) return st;
   return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
 }
 
 }  // namespace
+
+glmrt_status_t launch_bf16_rows_to_fp8_row_scaled(const uint16_t* src, uint8_t* dst, size_t rows, size_t row_width,
+                                                  size_t dst_row_stride_bytes, cudaStream_t stream) {
+  bf16_rows_to_fp8_row_scaled_kernel<<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(src, dst, row_width,
+                                                                                          dst_row_stride_bytes);
+  GLMRT_LAUNCH_CHECK("bf16_rows_to_fp8_row_scaled_kernel");
+  return GLMRT_STATUS_OK;
+}
+
 }  // namespace glmrt
 
 using namespace glmrt;
+
+extern "C" glmrt_status_t glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async(const uint16_t* src, uint8_t* dst, size_t rows,
+                                                                            size_t row_width, size_t dst_row_stride_bytes,
+                                                                            void* cuda_stream) {
+  // validate_bf16_rows_to_fp8_row_scaled_args (residual.cu:724-737)
+  if (src == nullptr || dst == nullptr || rows == 0 || row_width == 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "bf16_rows_to_fp8_row_scaled: null pointer or empty shape");
+  if (row_width > SIZE_MAX - sizeof(float) || dst_row_stride_bytes < row_width + sizeof(float) ||
+      dst_row_stride_bytes % alignof(float) != 0 || row_width % alignof(float) != 0 || rows > SIZE_MAX / row_width ||
+      rows > 0x7fffffffull)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT,
+                "bf16_rows_to_fp8_row_scaled: the row stride must hold the row and a float32 scale, 4-byte aligned");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  GLMRT_RETURN_IF_ERROR(launch_bf16_rows_to_fp8_row_scaled(src, dst, rows, row_width, dst_row_stride_bytes,
+                                                           static_cast<cudaStream_t>(cuda_stream)));
+  return ok();
+}
 
 extern "C" glmrt_status_t glmrt_cuda_residual_add_bf16_async(const uint16_t* residual, const uint16_t* delta,
                                                              uint16_t* out, size_t count, void* cuda_stream) {

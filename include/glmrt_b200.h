@@ -207,6 +207,13 @@ glmrt_status_t glmrt_cuda_residual_add_f32_delta_bf16(const uint16_t* residual, 
 glmrt_status_t glmrt_cuda_residual_add_f32_delta_bf16_async(const uint16_t* residual,
                                                             const float* delta_f32, uint16_t* out,
                                                             size_t count, void* cuda_stream);
+/* bf16 rows -> E4M3 bytes + one float32 scale per row (glmrt_native.h:776-778, kernel residual.cu:
+ * 245-277): scale = max |finite value| / 448 (1 for an all-zero row), byte = e4m3(value / scale),
+ * saturating; dst_row_stride_bytes >= row_width + 4 and a multiple of 4. */
+glmrt_status_t glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async(const uint16_t* src, uint8_t* dst,
+                                                                 size_t rows, size_t row_width,
+                                                                 size_t dst_row_stride_bytes,
+                                                                 void* cuda_stream);
 /* out = bf16(residual + bf16(shared_delta + bf16(routed_delta_f32))) */
 glmrt_status_t glmrt_cuda_residual_add_shared_f32_delta_bf16(
     const uint16_t* residual, const uint16_t* shared_delta, const float* routed_delta_f32,
@@ -534,8 +541,8 @@ glmrt_status_t glmrt_b200_pv2_parse_response(const void* frame, size_t frame_byt
  * regular request frame, runs its rows through the experts of `layer` that its routes name
  * (hidden dtype bf16 or NVFP4 payload rows; at most top_k routes per row; routes of experts that
  * do not live on this layer's shard are refused) and writes a response frame with one partial
- * output row per request row: bf16, or NVFP4 payload rows when the request negotiates them
- * (native rounding rule).  The row-scaled FP8 response is refused.  The executor id is the compact
+ * output row per request row: bf16, or NVFP4 payload rows (native rounding rule) or row-scaled
+ * FP8 rows when the request's flags negotiate them.  The executor id is the compact
  * id of "b200-nvfp4-tcgen05-executor".  Synchronises `cuda_stream`. */
 glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* request_frame, size_t request_bytes,
                                       void* response_out, size_t response_capacity,

@@ -558,6 +558,21 @@ def residual_add_shared_f32_delta_bf16(residual_bits, shared_bits, routed_f32) -
     return residual_add_bf16(residual_bits, mlp)
 
 
+def bf16_rows_to_fp8_e4m3_row_scaled(rows_bits) -> np.ndarray:
+    """[R, W] bf16 -> [R, W + 4] bytes: E4M3 values then one little-endian float32 scale per row
+    (native/cuda/kernels/residual.cu:245-277): scale = max |finite| / 448, 1 for an all-zero row;
+    byte = e4m3(value / scale) round-to-nearest, saturating; non-finite values encode 0."""
+    x = bf16_to_f32(np.asarray(rows_bits, np.uint16))
+    finite = np.isfinite(x)
+    amax = np.where(finite, np.abs(x), np.float32(0)).max(axis=1).astype(np.float32)
+    scale = np.where(amax > 0, (amax / np.float32(448.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    q = np.where(finite, (x / scale[:, None]).astype(np.float32), np.float32(0)).astype(np.float32)
+    out = np.zeros((x.shape[0], x.shape[1] + 4), np.uint8)
+    out[:, :x.shape[1]] = e4m3_encode_satfinite(q)
+    out[:, x.shape[1]:] = scale.view(np.uint8).reshape(-1, 4)
+    return out
+
+
 def scatter_add_rows_bf16_weighted_to_f32(src_bits, row_indices, row_weights, dst_f32) -> np.ndarray:
     """dst[row_indices[r]] += w[r] * src[r] (native/cuda/kernels/residual.cu:666-678)."""
     dst = np.array(dst_f32, np.float32, copy=True)

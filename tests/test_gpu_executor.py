@@ -93,6 +93,13 @@ def test_executor_matches_forward_routed_bit_for_bit(pkg, ref_layer):
                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert respq.partial_output_payload == outq.cpu().numpy().tobytes()
+
+    # row-scaled FP8 response rows: H E4M3 bytes + one float32 scale (protocol_v2.rs:49-50, residual.cu:245-277)
+    resp8 = ex.execute(P.ExpertProtocolV2RequestView.parse(
+        build_request(P, hid, idx, w, flags=P.EXPERT_PROTOCOL_V2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED).encode()))
+    assert resp8.output_dtype == P.ExpertV2Dtype.Fp8E4m3RowScaled and resp8.output_row_stride_bytes == H + 4
+    got8 = np.frombuffer(resp8.partial_output_payload, np.uint8).reshape(T, H + 4)
+    np.testing.assert_array_equal(got8, O.bf16_rows_to_fp8_e4m3_row_scaled(want))
     layer.close()
 
 
@@ -138,7 +145,6 @@ def test_executor_refuses_what_it_cannot_run(pkg, ref_layer):
         (build_request(P, hid, idx + 1, w), "does not live on this shard"),
         (build_request(P, hid, np.tile(idx, (1, 2)), np.tile(w, (1, 2))), "top_k is 4"),
         (build_request(P, O.make_hidden(1, T, 256), idx, w), "does not match the layer"),
-        (build_request(P, hid, idx, w, flags=P.EXPERT_PROTOCOL_V2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED), "row-scaled FP8"),
         (build_request(P, hid, idx, w, flags=P.EXPERT_PROTOCOL_V2_FLAG_LAYER_BLOCK, keep=lambda r, e: False), "not supported"),
         (build_request(P, O.make_hidden(2, 9, H), np.tile(idx[:1], (9, 1)), np.tile(w[:1], (9, 1))), "max_tokens"),
     ]

@@ -281,6 +281,32 @@ def test_residual_adds_match_oracle_bit_exactly(lib):
     assert lib.call_status("glmrt_cuda_residual_add_bf16_async", None, None, None, C.c_size_t(4), stream()) == 1
 
 
+def test_bf16_rows_to_fp8_row_scaled_matches_oracle(lib):
+    """native/cuda/kernels/residual.cu:245-277: E4M3 bytes + one float32 scale per row; an all-zero
+    row keeps scale 1, non-finite values encode 0 and do not enter the row maximum."""
+    rng = np.random.default_rng(14)
+    R, W = 7, 6144
+    x = rng.standard_normal((R, W), np.float32) * np.float32(3.0)
+    x[1] = 0.0
+    x[2, 5], x[2, 9], x[2, 100] = np.inf, -np.inf, np.nan
+    x[3] *= np.float32(1e-6)
+    x[4] *= np.float32(1e4)
+    bits = O.bf16_round(x)
+    src = bf16_tensor(bits)
+    stride = W + 8                                        # wider than the row: the tail stays untouched
+    dst = torch.full((R, stride), 0xAB, dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async", ptr(src), ptr(dst), C.c_size_t(R), C.c_size_t(W),
+             C.c_size_t(stride), stream())
+    torch.cuda.synchronize()
+    got = dst.cpu().numpy()
+    want = O.bf16_rows_to_fp8_e4m3_row_scaled(bits)
+    np.testing.assert_array_equal(got[:, :W + 4], want)
+    assert (got[:, W + 4:] == 0xAB).all()
+    assert want[1, W:].view(np.float32)[0] == 1.0
+    assert lib.call_status("glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async", ptr(src), ptr(dst), C.c_size_t(R),
+                           C.c_size_t(W), C.c_size_t(W + 2), stream()) == 1
+
+
 def test_infra_alloc_copy_events(lib, pkg):
     from glmrt_b200 import native as N
     b = N.DeviceBuffer()
