@@ -1,6 +1,7 @@
 // Shared host/device helpers for libglmrt_b200: status + last-error plumbing and the
 // numeric formats of the routed-MoE path (E2M1 codes, E4M3 scales, bf16).
 #pragma once
+#include <atomic>
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -44,6 +45,22 @@ inline bool checked_mul(size_t a, size_t b, size_t* out) {
     if (_e != cudaSuccess) return ::glmrt::status_from_cuda(_e, what);            \
     ::glmrt::count_launch();                                                      \
   } while (0)
+
+// Raises a kernel's dynamic shared-memory limit once per device.  `done` is a static of the call
+// site (one bit per device ordinal); the attribute belongs to the device, so a process that drives
+// several GPUs sets it on each.  Racing first calls both set it, which is harmless.
+template <typename Kernel>
+inline glmrt_status_t ensure_smem_limit(std::atomic<uint64_t>& done, Kernel kernel, size_t bytes, const char* what) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return status_from_cuda(err, "cudaGetDevice");
+  const uint64_t bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return GLMRT_STATUS_OK;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (err != cudaSuccess) return status_from_cuda(err, what);
+  done.fetch_or(bit, std::memory_order_release);
+  return GLMRT_STATUS_OK;
+}
 
 // ---- device-side formats ----
 #ifdef __CUDACC__

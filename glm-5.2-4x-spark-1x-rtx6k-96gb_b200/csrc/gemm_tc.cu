@@ -336,13 +336,8 @@ template <bool kFC1, int kBN>
 glmrt_status_t launch_one(const FfnArgs& a, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b,
                           int sm_count, cudaStream_t stream) {
   using C = Cfg<kFC1, kBN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<kFC1, kBN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(C::kSmemBytes));
-    if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaFuncSetAttribute(expert_gemm_kernel)", err);
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_kernel<kFC1, kBN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_kernel)"));
   expert_gemm_kernel<kFC1, kBN><<<sm_count, kThreadsTC, C::kSmemBytes, stream>>>(a, a0, a1, b);
   GLMRT_LAUNCH_CHECK("expert_gemm_kernel");
   return GLMRT_STATUS_OK;

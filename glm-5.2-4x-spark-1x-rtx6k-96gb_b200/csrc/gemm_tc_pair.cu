@@ -261,14 +261,8 @@ bool fc1_pair_supported(const FfnArgs& a, int sm_count) {
 
 glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
   using C = PairCfg;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(expert_fc1_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(C::kSmemBytes));
-    if (err != cudaSuccess)
-      return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaFuncSetAttribute(expert_fc1_pair_kernel)", err);
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_fc1_pair_kernel, C::kSmemBytes, "cudaFuncSetAttribute(expert_fc1_pair_kernel)"));
   PairMaps maps;
   maps.act = m.act1; maps.gate = m.gate; maps.up = m.up;
   maps.act_sf = m.act1_sf; maps.gate_sf = m.gate_sf; maps.up_sf = m.up_sf;

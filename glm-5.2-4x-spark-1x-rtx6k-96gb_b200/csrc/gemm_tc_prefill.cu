@@ -326,14 +326,8 @@ template <bool kFC1, int kWN>
 glmrt_status_t launch_tokens(const FfnArgs& a, const CUtensorMap& act, const CUtensorMap& w0, const CUtensorMap& w1,
                              int sm_count, cudaStream_t stream) {
   using C = PfCfg<kFC1, kWN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(expert_gemm_tokens_kernel<kFC1, kWN>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(C::kSmemBytes));
-    if (err != cudaSuccess)
-      return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)", err);
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_tokens_kernel<kFC1, kWN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)"));
   expert_gemm_tokens_kernel<kFC1, kWN><<<sm_count, C::kThreads, C::kSmemBytes, stream>>>(a, act, w0, w1);
   GLMRT_LAUNCH_CHECK("expert_gemm_tokens_kernel");
   return GLMRT_STATUS_OK;

@@ -225,13 +225,8 @@ glmrt_status_t launch_router_logits_tc(const uint16_t* x, const CUtensorMap& map
                                        cudaStream_t stream) {
   CUtensorMap map_x;
   GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&map_x, x, rows, hidden * 2, 128));
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(router_logits_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(kRtSmemBytes));
-    if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaFuncSetAttribute(router_logits_tc_kernel)", err);
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, router_logits_tc_kernel, kRtSmemBytes, "cudaFuncSetAttribute(router_logits_tc_kernel)"));
   const int tiles = static_cast<int>(((rows + 127) / 128) * (experts / 128));
   router_logits_tc_kernel<<<std::min(sm_count, tiles), kThreadsTC, kRtSmemBytes, stream>>>(
       map_x, map_w3, logits, static_cast<int>(rows), static_cast<int>(hidden), static_cast<int>(experts), error_word);
