@@ -294,7 +294,11 @@ glmrt_status_t glmrt_b200_moe_layer_forward_residual_async(
 glmrt_status_t glmrt_b200_moe_layer_forward_host(void* layer, const void* hidden_host, size_t rows,
                                                  void* output_host, void* cuda_stream);
 /* Routed forward with caller-supplied routes (the expert worker's view of a request:
- * rows + (expert, weight) routes; protocol_v2.rs:236-310).  Skips the router. */
+ * rows + (expert, weight) routes; protocol_v2.rs:236-310).  Skips the router.  An index entry
+ * 0xFFFFFFFF means "no route" (a row with fewer than top_k experts on this worker) and is
+ * skipped; any other id outside the layer is reported by glmrt_b200_moe_layer_check.  Routes of
+ * experts that live on another shard (ep_world > 1) are skipped as well: the result is this
+ * shard's partial. */
 glmrt_status_t glmrt_b200_moe_layer_forward_routed_async(
     void* layer, glmrt_device_buffer_t hidden_bf16, size_t rows, glmrt_device_buffer_t topk_indices,
     glmrt_device_buffer_t topk_weights, glmrt_device_buffer_t output_bf16, void* cuda_stream);

@@ -210,6 +210,40 @@ def test_full_size_prefill_is_row_permutation_equivariant(pkg):
     layer.close()
 
 
+def test_sparse_layer_output_with_shared_expert(pkg, small_layer):
+    """hidden + routed + shared (python/reference/glmrt_reference/glm_moe_dsa_layer_ref.py:190-198):
+    the shared expert is one more NVFP4 expert that every row selects with weight 1; it runs through
+    a second layer object (one expert, top-1, caller-supplied routes) and its rows enter the routed
+    layer's combine as the shared delta.  Checked against the oracle's composition of the same
+    pieces, within the gate of the layer (the residual step itself is exact, tested separately)."""
+    from glmrt_b200.layer import MoeLayer
+    K, T, H, I = 4, 40, 512, 256
+    shared_ref = O.make_layer(77, H, I, 1)
+    routed = make(pkg, small_layer, K, 64, "tc")
+    shared = MoeLayer(H, I, 1, 1, max_tokens=64)
+    shared.load_quantized_layer(shared_ref)
+    hid = O.make_hidden(900, T, H)                # the normalised rows (input of router and experts)
+    resid = O.bf16_round(np.random.default_rng(3).standard_normal((T, H), np.float32))   # the layer input
+    x = to_dev(hid)
+    ones = torch.ones((T, 1), dtype=torch.float32, device="cuda")
+    zeros = torch.zeros((T, 1), dtype=torch.int32, device="cuda")
+    shared_rows = shared.forward_routed(x, zeros, ones)
+    shared.check()
+    got = to_bits(routed.forward_residual(x, to_dev(resid), shared_rows))
+    routed.check()
+    # oracle: routed (O1) and shared (O1, weight 1) outputs, then the native residual formula
+    _, _, routed_o = O.layer_forward(small_layer, hid, K, mode="O1")
+    shared_o = O.moe_forward(hid, lambda e: shared_ref.expert(e), np.zeros((T, 1), np.int64), np.ones((T, 1), np.float32), mode="O1")
+    want = O.residual_add_shared_f32_delta_bf16(resid, shared_o, O.bf16_to_f32(routed_o))
+    delta_got = O.bf16_to_f32(got) - O.bf16_to_f32(resid)
+    delta_want = O.bf16_to_f32(want) - O.bf16_to_f32(resid)
+    err = np.linalg.norm(delta_got - delta_want, axis=1) / np.maximum(np.linalg.norm(delta_want, axis=1), 1e-30)
+    print(f"layer output with shared expert: max per-token rel L2 of the MLP delta {err.max():.3e}")
+    assert err.max() <= 3e-2       # two bf16 truncations of a value of order 1 on top of the 2e-2 gate
+    routed.close()
+    shared.close()
+
+
 def test_bad_routes_are_reported_not_faulted(pkg, small_layer):
     from glmrt_b200.native import GlmrtError
     K, T = 4, 4
