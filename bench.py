@@ -239,6 +239,26 @@ def run_gpu(args):
     launches = int(st1.launches_total - st0.launches_total)
     ms_per_step = total_ms / steps
 
+    # ---- the same steps replayed from CUDA graphs (reported beside the stream-ordered figure) ----
+    graph_ms = None
+    if args.graph:
+        graphs = []
+        for b in dev_batches:
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph):
+                layer.forward(b, out)
+            graphs.append(gph)
+        for i in range(warmup):
+            graphs[i % n_batches].replay()
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(steps):
+            graphs[i % n_batches].replay()
+        ev1.record()
+        torch.cuda.synchronize()
+        graph_ms = ev0.elapsed_time(ev1) / steps
+        layer.check()
+
     # ---- per-kernel timing (events around each kernel on the launching stream) ----
     layer.set_profiling(True)
     stage_sum = {}
@@ -314,6 +334,7 @@ def run_gpu(args):
                    "top_k": K_TOP, "intermediate": I, "experts_per_gpu": E,
                    "l2": f"no flush: each step streams {layer_bytes / 1e9:.2f} GB of expert weights, far above the 126 MB L2",
                    "distinct_experts_per_step": distinct, "stage_ms": stage_ms,
+                   "graph_replay_ms_per_step": graph_ms,
                    "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
                    "layer_frac_of_peak": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
         "clocks": sampler.summary(),
@@ -446,6 +467,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time the steps replayed from CUDA graphs (config.graph_replay_ms_per_step)")
     ap.add_argument("--pair-tiles", action="store_true",
                     help="large batches: run FC1 on CTA pairs (cta_group::2) instead of one-CTA tiles (for comparison)")
     ap.add_argument("--experts", type=int, default=E,

@@ -114,3 +114,30 @@ def test_nccl_wrappers_validate_or_report_unavailable(lib, pkg):
         from glmrt_b200 import native as N
         nb = N.DeviceBuffer.null()
         assert lib.call_status("glmrt_nccl_all_reduce_bf16_async", None, nb, nb, C.c_size_t(4), None) == 1
+
+
+def test_protocol_codec_validates_its_arguments(lib, pkg):
+    """The ExpertProtocolV2 codec is host code: it must answer without a GPU, reject null pointers
+    and report the size it needs when the output buffer is too small."""
+    from glmrt_b200 import protocol_v2 as P
+    n = C.c_size_t()
+    assert lib.call_status("glmrt_b200_pv2_row_bytes", C.c_uint32(1), C.c_size_t(8), None) == 1
+    assert lib.call_status("glmrt_b200_pv2_row_bytes", C.c_uint32(9), C.c_size_t(8), C.byref(n)) == 1
+    assert "unknown dtype" in lib.last_error()
+    assert lib.call_status("glmrt_b200_pv2_parse_request", None, C.c_size_t(0), None, None) == 1
+    assert lib.call_status("glmrt_b200_pv2_compact_id", None, None) == 1
+    req = P.ExpertProtocolV2Request(1, 1, 0, 32, P.ExpertV2Dtype.Bf16,
+                                    [P.ExpertProtocolV2RowDescriptor(0, P.ExpertV2SourceKind.Decode, 0, 0, 0, 0)], [],
+                                    b"\0" * 64)
+    frame = req.encode(lib)
+    assert len(frame) == 96 + 40 + 64
+    h = P._RequestHeader()
+    h.request_id, h.hidden_dim, h.hidden_dtype = 1, 32, 1
+    row = P._Row(0, 0, 0, 0, 0, 1, 0)
+    small = C.create_string_buffer(16)
+    st = lib.call_status("glmrt_b200_pv2_encode_request", C.byref(h), C.byref(row), C.c_size_t(1), None, C.c_size_t(0),
+                         b"\0" * 64, C.c_size_t(64), small, C.c_size_t(16), C.byref(n))
+    assert st == 2 and n.value == len(frame)
+    # the executor refuses a null layer before it looks at the frame
+    assert lib.call_status("glmrt_b200_pv2_execute", None, frame, C.c_size_t(len(frame)), small, C.c_size_t(16),
+                           C.byref(n), None) == 1
