@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_plan_kernel(EpArgs a, PlanArgs 
           if (chunks < p.max_chunks) {
             Chunk ch;
             ch.expert = e / a.world;
-            ch.slot_base = running + off;
+            ch.slot_base = running + slot_of_position(off, p.chunk_tokens);
             ch.tokens = min(p.chunk_tokens, tot - off);
             ch.reserved = 0;
             p.chunks[chunks] = ch;
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_plan_kernel(EpArgs a, PlanArgs 
           ++chunks;
         }
       }
-      running += (tot + 127) & ~127;
+      running += expert_slot_span(tot, p.chunk_tokens);
     }
     if (running > p.max_slots) overflow = true;
     if (overflow) atomicOr(&c->plan_error, 1);
@@ -158,7 +158,7 @@ ep_dispatch_kernel(EpArgs a, const uint8_t* payload, const uint32_t* topk_indice
       if (lane == 0) pos = atomicAdd(&a.ctrl->cursor[e], 1);
       pos = __shfl_sync(0xffffffffu, pos, 0);
       const int owner = static_cast<int>(e % a.world);
-      const int slot = a.ctrl->base_slot[e] + a.ctrl->my_offset[e] + pos;
+      const int slot = a.ctrl->base_slot[e] + slot_of_position(a.ctrl->my_offset[e] + pos, a.chunk_tokens);
       const int row = warp / top_k;
       const int code_bytes = hidden / 2, kblocks = hidden / 16;
       const uint8_t* src = payload + static_cast<size_t>(row) * (code_bytes + kblocks);

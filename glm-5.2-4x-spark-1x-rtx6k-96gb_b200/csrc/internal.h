@@ -61,6 +61,24 @@ glmrt_status_t launch_quantize_weight_f32(const float* in, uint8_t* packed, uint
                                           uint32_t* amax_scratch, size_t rows, size_t cols, cudaStream_t stream);
 
 // ---- plan.cu ----
+// Slot layout of one expert.  Work items of 128 or 256 slots tile the expert's range densely (the
+// range is rounded up to the 128-row granularity of the tiled scales).  Work items of 32 slots
+// (decode kernels) each get a 128-slot group of their own, so that the scales of a work item always
+// start at column 0 of a scale tile in tensor memory: the block-scaled MMA was only ever run, and
+// is only known to work, with its B-scale address on such a boundary.
+#if defined(__CUDACC__)
+#define GLMRT_HD __host__ __device__
+#else
+#define GLMRT_HD
+#endif
+GLMRT_HD inline int expert_slot_span(int count, int chunk_tokens) {
+  return chunk_tokens < 128 ? ((count + chunk_tokens - 1) / chunk_tokens) * 128 : (count + 127) & ~127;
+}
+// slot (relative to the expert's first slot) of the expert's route number `pos`
+GLMRT_HD inline int slot_of_position(int pos, int chunk_tokens) {
+  return chunk_tokens < 128 ? (pos / chunk_tokens) * 128 + pos % chunk_tokens : pos;
+}
+
 // A route entry with this expert id is "no route": it gets no slot and is not an error (the
 // expert worker's view of a request may name fewer than top_k experts for a row).
 constexpr uint32_t kNoRoute = 0xffffffffu;
@@ -115,6 +133,7 @@ struct EpControl {
 };
 struct EpArgs {
   int world, rank, experts;
+  int chunk_tokens;              // work-item size of this step (decides the slot layout, see expert_slot_span)
   uint32_t epoch;
   EpControl* ctrl;
   uint32_t* counters;

@@ -275,7 +275,11 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   l->local_experts = static_cast<int>((c.experts - c.ep_rank + c.ep_world - 1) / c.ep_world);
   const size_t H = c.hidden_dim, I = c.intermediate_dim, E = l->local_experts, T = c.max_tokens, K = c.top_k;
   const size_t routes = T * K;
-  l->max_slots = static_cast<int>(round_up(routes + E * 127, 128));
+  // Dense work items (128 / 256 slots): every expert's range is rounded up to 128 slots.  Batches of
+  // at most 256 rows use 32-slot work items, each in a 128-slot group of its own (expert_slot_span).
+  const size_t decode_routes = std::min<size_t>(T, 256) * K;
+  const size_t decode_slots = 128 * (std::min(E, decode_routes) + decode_routes / 32 + 1);
+  l->max_slots = static_cast<int>(std::max(round_up(routes + E * 127, 128), decode_slots));
   l->max_chunks = static_cast<int>(E + (routes + 31) / 32);
   glmrt_status_t st = GLMRT_STATUS_OK;
   auto A = [&](glmrt_status_t s) { if (st == GLMRT_STATUS_OK) st = s; };
@@ -686,6 +690,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
   const int routes = static_cast<int>(rows * c.top_k);
   EpArgs a = l->ep;
   a.epoch = l->ep_epoch;
+  a.chunk_tokens = chunk_tokens;
   switch (phase) {
     case 0: {
       mark(l, GLMRT_B200_STAGE_ROUTER, s);

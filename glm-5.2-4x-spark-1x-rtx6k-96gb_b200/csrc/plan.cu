@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
     int slots = 0, chunks = 0, distinct = 0, routes = 0;
     for (int le = le0; le < le1; ++le) {
       const int c = cnt[le];
-      slots += (c + 127) & ~127;
+      slots += expert_slot_span(c, a.chunk_tokens);
       chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
       distinct += c != 0;
       routes += c;
@@ -81,13 +81,13 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
         for (int off = 0; off < c; off += a.chunk_tokens) {
           Chunk ch;
           ch.expert = le;
-          ch.slot_base = slot_off + off;
+          ch.slot_base = slot_off + slot_of_position(off, a.chunk_tokens);
           ch.tokens = min(a.chunk_tokens, c - off);
           ch.reserved = 0;
           a.chunks[chunk_off++] = ch;
         }
       }
-      slot_off += (c + 127) & ~127;
+      slot_off += expert_slot_span(c, a.chunk_tokens);
     }
     if (lane == 0) {
       s_error = err;
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
     const int pos = a.route_slot[r];
     if (pos < 0) continue;
     const uint32_t e = a.topk_indices[r];
-    const int slot = base[e / a.ep_world] + pos;
+    const int slot = base[e / a.ep_world] + slot_of_position(pos, a.chunk_tokens);
     if (bad || slot >= a.max_slots) {
       a.route_slot[r] = -1;
     } else {
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(PlanArgs a, int local_e
   int slots = 0, chunks = 0, distinct = 0, routes = 0;
   for (int le = le0; le < le1; ++le) {
     const int c = a.expert_counts[le];
-    slots += (c + 127) & ~127;
+    slots += expert_slot_span(c, a.chunk_tokens);
     chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
     distinct += c != 0;
     routes += c;
@@ -196,13 +196,13 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(PlanArgs a, int local_e
       for (int off = 0; off < c; off += a.chunk_tokens) {
         Chunk ch;
         ch.expert = le;
-        ch.slot_base = slot_off + off;
+        ch.slot_base = slot_off + slot_of_position(off, a.chunk_tokens);
         ch.tokens = min(a.chunk_tokens, c - off);
         ch.reserved = 0;
         a.chunks[chunk_off++] = ch;
       }
     }
-    slot_off += (c + 127) & ~127;
+    slot_off += expert_slot_span(c, a.chunk_tokens);
   }
   if (lane == 0) {
     a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(total_chunks);
@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(kPlanBlock) plan_place_kernel(PlanArgs a, int 
   if (pos < 0) return;
   const bool bad = a.counters[kCntError] != 0;
   const int le = static_cast<int>(a.topk_indices[r] / a.ep_world);
-  const int slot = a.expert_base[le] + a.block_hist[static_cast<size_t>(blockIdx.x) * local_experts + le] + pos;
+  const int slot = a.expert_base[le] +
+                   slot_of_position(a.block_hist[static_cast<size_t>(blockIdx.x) * local_experts + le] + pos, a.chunk_tokens);
   if (bad || slot >= a.max_slots) {
     a.route_slot[r] = -1;
   } else {

@@ -244,6 +244,38 @@ def test_sparse_layer_output_with_shared_expert(pkg, small_layer):
     shared.close()
 
 
+@pytest.mark.parametrize("T", [200, 256])
+def test_decode_kernels_with_many_rows_per_expert(pkg, small_layer, T):
+    """Batches of at most 256 rows run the decode kernels (32-slot work items).  With 16 experts
+    every expert receives well over 32 rows here, so each has several work items; and with
+    caller-supplied routes one expert receives every row of the batch (8 work items at T=256)."""
+    K = 4
+    layer = make(pkg, small_layer, K, 256, "tc")
+    hid = O.make_hidden(6100 + T, T, 512)
+    out, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    layer.check()
+    oi, ow, oo = O.layer_forward(small_layer, hid, K, mode="O1")
+    gi = idx.cpu().numpy()
+    assert O.router_indices_equivalent(gi, oi, sel64(small_layer, hid))
+    counts = np.bincount(gi.reshape(-1), minlength=16)
+    assert counts.max() > 32
+    chunks = layer.debug("CHUNKS", np.int32).reshape(-1, 4)
+    n_chunks = int(layer.debug("COUNTERS", np.uint32)[0])
+    assert n_chunks > 16 and chunks[:n_chunks, 2].max() <= 32 and (chunks[:n_chunks, 1] % 128 == 0).all()
+    same = np.all(gi == oi.astype(np.int32), axis=1)
+    err = O.rel_l2_per_token(to_bits(out)[same], oo[same])
+    assert err.max() <= TOL, f"T={T}: max per-token rel L2 {err.max():.3e}"
+    # every row to expert 3 (and three other fixed experts), weights from the router
+    fixed = np.tile(np.array([[3, 0, 9, 14]], np.int32), (T, 1))
+    wts = w.cpu().numpy()
+    got = to_bits(layer.forward_routed(to_dev(hid), torch.from_numpy(fixed).cuda(), torch.from_numpy(wts).cuda()))
+    layer.check()
+    want = O.moe_forward(hid, lambda e: small_layer.expert(e), fixed.astype(np.int64), wts, mode="O1")
+    err2 = O.rel_l2_per_token(got, want)
+    assert err2.max() <= TOL, f"T={T} fixed routes: max per-token rel L2 {err2.max():.3e}"
+    layer.close()
+
+
 def test_bad_routes_are_reported_not_faulted(pkg, small_layer):
     from glmrt_b200.native import GlmrtError
     K, T = 4, 4
