@@ -29,8 +29,11 @@ def small_layer():
     return O.make_layer(21, 512, 256, 16)
 
 
-@pytest.mark.parametrize("world,T", [(2, 24), (4, 30), (2, 1), (4, 300)])
-def test_ep_shards_in_one_process_match_single_shard_and_oracle(pkg, small_layer, world, T):
+@pytest.mark.parametrize("world,T,max_tokens", [(2, 24, 512), (4, 30, 512), (2, 1, 512), (4, 300, 512),
+                                                (2, 24, 256), (4, 7, 64), (2, 200, 256)])
+def test_ep_shards_in_one_process_match_single_shard_and_oracle(pkg, small_layer, world, T, max_tokens):
+    """max_tokens above 256 selects the 128-slot work items (prefill kernels) for the exchange,
+    at most 256 the 32-slot ones (decode kernels); T=200 gives every expert several of those."""
     from glmrt_b200 import ep as EP
     from glmrt_b200.layer import MoeLayer
     K = 4
@@ -44,7 +47,7 @@ def test_ep_shards_in_one_process_match_single_shard_and_oracle(pkg, small_layer
 
     shards = []
     for r in range(world):
-        l = MoeLayer(512, 256, 16, K, max_tokens=512, ep_world=world, ep_rank=r)
+        l = MoeLayer(512, 256, 16, K, max_tokens=max_tokens, ep_world=world, ep_rank=r)
         l.load_quantized_layer(small_layer)
         shards.append(l)
     EP.attach_in_process(shards)
