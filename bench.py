@@ -209,7 +209,7 @@ def run_gpu(args):
     T, steps, warmup = args.tokens, args.steps, max(3, args.warmup)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    layer = MoeLayer(H, I, E, K_TOP, max_tokens=T, engine="tc2" if args.pair_tiles else "tc")
+    layer = MoeLayer(H, I, E, K_TOP, max_tokens=T, engine=args.pair_tiles or "tc")
     layer.fill_synthetic(0, 0.02)
     g = torch.Generator(device="cpu").manual_seed(0)
     rw = (torch.randn(E, H, generator=g) * 0.02)
@@ -469,8 +469,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", action="store_true",
                     help="also time the steps replayed from CUDA graphs (config.graph_replay_ms_per_step)")
-    ap.add_argument("--pair-tiles", action="store_true",
-                    help="large batches: run FC1 on CTA pairs (cta_group::2) instead of one-CTA tiles (for comparison)")
+    ap.add_argument("--pair-tiles", default=None, choices=["tc2", "tc2-fc1", "tc2-fc2"],
+                    help="large batches: run both / FC1 / FC2 on CTA pairs (cta_group::2) instead of one-CTA tiles")
     ap.add_argument("--experts", type=int, default=E,
                     help="routed experts in the layer (256 = GLM-5.2; smaller values give a profiler-sized case)")
     args = ap.parse_args()

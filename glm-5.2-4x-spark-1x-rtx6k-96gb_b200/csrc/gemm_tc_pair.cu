@@ -1,6 +1,9 @@
-// FC1 of large prefill batches on CTA pairs (tcgen05 cta_group::2).
+// Expert GEMMs of large prefill batches on CTA pairs (tcgen05 cta_group::2).
 //
-// Same computation as the FC1 instance of gemm_tc_prefill.cu (the reference's fused-MoE FC1 stage,
+// FC2 instance: the pair's B tile is 256 down rows (128 per CTA), each CTA's accumulator is 128
+// slots x 256 features and leaves as 128-byte bulk stores like the one-CTA FC2 kernel's.
+//
+// FC1: same computation as the FC1 instance of gemm_tc_prefill.cu (the reference's fused-MoE FC1 stage,
 // native/cuda/kernels/b12x_direct.cu:479-508, and SIMT gate/up MLP, mlp.cu:218-273), for experts
 // that received well over 128 tokens.  One work item is (expert, 256 token slots, 128 features):
 // the two CTAs of a cluster each hold 128 of the token slots as their A rows and one half of the
@@ -10,7 +13,8 @@
 // buys a fifth pipeline stage.  Measured on the GLM-5.2 layer it is exactly as fast as the one-CTA
 // kernel (T = 8192: 1.19 vs 1.14 ms, T = 16384: 1.88 vs 1.89 ms) and bit-identical: what each SM no
 // longer loads from L2 it now reads from its peer's shared memory, and the 256-slot items are
-// emptier on average.  The layer therefore uses it only when asked (GLMRT_B200_LAYER_PAIR_TILES).
+// emptier on average; FC2 on pairs measures 0.93 vs 0.86 ms and 1.60 vs 1.62 ms.  The layer
+// therefore uses these kernels only when asked (GLMRT_B200_LAYER_PAIR_FC1 / _FC2).
 //
 // Protocol (every wait bounded, as in gemm_tc.cu):
 //   * both producers wait on their own `empty` barrier and load into their own shared memory; all
@@ -35,31 +39,38 @@ namespace {
 
 using namespace tc;
 
+template <bool kFC1>
 struct PairCfg {
   static constexpr int kABytes = 128 * kStageBytesK;      // this CTA's 128 token slots
   static constexpr int kBBytes = 128 * kStageBytesK;      // this CTA's half of the 256 weight rows
   static constexpr int kSfaBytes = kSfStageBytes;         // scales of this CTA's slots
   static constexpr int kSfbBytes = 2 * kSfStageBytes;     // scales of all 256 weight rows (both CTAs need them)
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38912
-  static constexpr int kStages = 5;
+  static constexpr int kStages = kFC1 ? 5 : 4;            // FC2 leaves room for the staging rows of its epilogue
   static constexpr int kAccCols = 256;
   static constexpr int kSfSetCols = 16 + 32;
   static constexpr int kSfCol = kAccCols;
   static constexpr int kTmemCols = 512;
-  static constexpr int kFeatPerTile = 128;
-  static constexpr int kEpiWarps = 16;
+  static constexpr int kFeatPerTile = kFC1 ? 128 : 256;
+  static constexpr int kEpiWarps = kFC1 ? 16 : 8;
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kChunkCache = 256;
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk);
+  static constexpr int kOutPitch = 144;                   // FC2: 128 staging bytes per thread, conflict-free pitch
+  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * 32 * kOutPitch;
+  static constexpr size_t kSmemBytes =
+      static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
 
+// act / act_sf: this GEMM's activation codes and scales; w0 / w0_sf: the weight rows the leader
+// loads (FC1 gate, FC2 down) and their scales; w1 / w1_sf: the peer's (FC1 up, FC2 down again).
 struct PairMaps {
-  CUtensorMap act, gate, up, act_sf, gate_sf, up_sf;
+  CUtensorMap act, w0, w1, act_sf, w0_sf, w1_sf;
 };
 
-__global__ void __launch_bounds__(PairCfg::kThreads, 1)
-expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
-  using C = PairCfg;
+template <bool kFC1>
+__global__ void __launch_bounds__(PairCfg<kFC1>::kThreads, 1)
+expert_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
+  using C = PairCfg<kFC1>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
@@ -70,16 +81,18 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   Chunk* chunk_cache = reinterpret_cast<Chunk*>(reinterpret_cast<uint8_t*>(bars) + 256);
+  uint8_t* out_stage = reinterpret_cast<uint8_t*>(chunk_cache + C::kChunkCache);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   const uint32_t rank = cluster_ctarank();       // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int k_bytes = a.hidden / 2;
+  const int k_bytes = (kFC1 ? a.hidden : a.inter) / 2;
   const int k_stages = k_bytes / kStageBytesK;
   const int k_tiles64 = k_bytes / 32;
-  const int feat_tiles = a.inter / C::kFeatPerTile;
+  const int out_rows = kFC1 ? a.inter : a.hidden;
+  const int feat_tiles = out_rows / C::kFeatPerTile;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -112,7 +125,7 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
   if (warp == 0) {
     // ================= TMA producer (both CTAs) =================
     const uint64_t pol = policy_evict_last();
-    const CUtensorMap* map_w = rank == 0 ? &maps.gate : &maps.up;
+    const CUtensorMap* map_w = rank == 0 ? &maps.w0 : &maps.w1;
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -120,11 +133,14 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
     for (int tile = pair; tile < num_tiles && alive; tile += num_pairs, ++it) {
       const Chunk ch = chunk_of(it, tile);
       const int ft = tile % feat_tiles;
-      const int w_row = ch.expert * a.inter + ft * C::kFeatPerTile;
+      const int w_row = ch.expert * out_rows + ft * C::kFeatPerTile;
+      // FC1: both CTAs take rows w_row.. of their own projection; FC2: the peer takes the second 128 rows
+      const int my_w_row = w_row + (kFC1 ? 0 : 128 * static_cast<int>(rank));
       const int slot0 = ch.slot_base + 128 * static_cast<int>(rank);
       // rows of the scale maps are 128 bytes: one 512-byte scale tile = 4 rows
       const int sfa_row0 = (slot0 / 128) * k_tiles64 * 4;
       const int sfb_row0 = (w_row / 128) * k_tiles64 * 4;
+      const int sfb_row1 = kFC1 ? sfb_row0 : (w_row / 128 + 1) * k_tiles64 * 4;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
         if (elect_one()) {
@@ -136,10 +152,10 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
           const int kx = ks * kStageBytesK;
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * C::kStageBytes);
           tma_load_2d_pair(s_a, &maps.act, full, kx, slot0, pol);
-          tma_load_2d_pair(s_b, map_w, full, kx, w_row, pol);
+          tma_load_2d_pair(s_b, map_w, full, kx, my_w_row, pol);
           tma_load_2d_pair(s_sfa, &maps.act_sf, full, 0, sfa_row0 + ks * 16, pol);
-          tma_load_2d_pair(s_sfb, &maps.gate_sf, full, 0, sfb_row0 + ks * 16, pol);
-          tma_load_2d_pair(s_sfb + kSfStageBytes, &maps.up_sf, full, 0, sfb_row0 + ks * 16, pol);
+          tma_load_2d_pair(s_sfb, &maps.w0_sf, full, 0, sfb_row0 + ks * 16, pol);
+          tma_load_2d_pair(s_sfb + kSfStageBytes, &maps.w1_sf, full, 0, sfb_row1 + ks * 16, pol);
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -170,8 +186,8 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) {
               tc_copy_sf_pair(t_sfa + kb * 4, desc_sf(s_sfa + kb * 512));
-              tc_copy_sf_pair(t_sfb + kb * 8, desc_sf(s_sfb + kb * 512));                       // gate rows
-              tc_copy_sf_pair(t_sfb + kb * 8 + 4, desc_sf(s_sfb + kSfStageBytes + kb * 512));   // up rows
+              tc_copy_sf_pair(t_sfb + kb * 8, desc_sf(s_sfb + kb * 512));                       // B rows 0..127
+              tc_copy_sf_pair(t_sfb + kb * 8 + 4, desc_sf(s_sfb + kSfStageBytes + kb * 512));   // B rows 128..255
             }
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb)
@@ -195,7 +211,7 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
   } else {
     // ================= epilogue (both CTAs): one thread per (token slot, share of the features) =================
     const int quad = warp & 3;
-    const int part = (warp - 2) >> 2;                 // 0..3: 32 of the tile's 128 features each
+    const int part = (warp - 2) >> 2;                 // FC1 0..3: 32 of the tile's 128 features; FC2 0..1: 128 of its 256
     const int row = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t lead_acc_empty = cluster_addr(smem_u32(acc_empty), 0);
@@ -208,33 +224,68 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
       const int here = min(128, max(0, ch.tokens - 128 * static_cast<int>(rank)));
       const bool valid = row < here;
       const size_t slot = static_cast<size_t>(ch.slot_base) + 128 * rank + row;
-      const float s2g = a.scale2[ch.expert * 3 + 0];
-      const float s2u = a.scale2[ch.expert * 3 + 1];
+      const float s2g = a.scale2[ch.expert * 3 + (kFC1 ? 0 : 2)];
+      const float s2u = kFC1 ? a.scale2[ch.expert * 3 + 1] : 0.0f;
+      uint16_t* dst = (!kFC1 && valid) ? a.slot_out[slot] : nullptr;
       if (!mbar_wait_warp(acc_full, aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + lane_base;
-      // Both 16-feature blocks of this warp are read out first and the accumulator is handed back
-      // before any arithmetic, so the next item's MMAs run under this item's SwiGLU and stores.
-      uint32_t g[2][16], u[2][16];
+      if (kFC1) {
+        // Both 16-feature blocks of this warp are read out first and the accumulator is handed back
+        // before any arithmetic, so the next item's MMAs run under this item's SwiGLU and stores.
+        uint32_t g[2][16], u[2][16];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        tc_load16(t_acc + (part * 2 + j) * 16, g[j]);
-        tc_load16(t_acc + 128 + (part * 2 + j) * 16, u[j]);
-      }
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+        for (int j = 0; j < 2; ++j) {
+          tc_load16(t_acc + (part * 2 + j) * 16, g[j]);
+          tc_load16(t_acc + 128 + (part * 2 + j) * 16, u[j]);
+        }
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int b = part * 2 + j;                   // 16-feature block of the tile
-        uint32_t lo, hi, sbyte;
-        swiglu_requant_block16(g[j], u[j], s2g, s2u, lo, hi, sbyte);
-        if (valid) {
-          const int feature = ft * C::kFeatPerTile + b * 16;
-          *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + feature / 2) =
-              make_uint2(lo, hi);
-          a.act2_sf[sf_tile_offset(slot, feature / 16, a.inter / 16)] = static_cast<uint8_t>(sbyte);
+        for (int j = 0; j < 2; ++j) {
+          const int b = part * 2 + j;                   // 16-feature block of the tile
+          uint32_t lo, hi, sbyte;
+          swiglu_requant_block16(g[j], u[j], s2g, s2u, lo, hi, sbyte);
+          if (valid) {
+            const int feature = ft * C::kFeatPerTile + b * 16;
+            *reinterpret_cast<uint2*>(a.act2_codes + slot * static_cast<size_t>(a.inter / 2) + feature / 2) =
+                make_uint2(lo, hi);
+            a.act2_sf[sf_tile_offset(slot, feature / 16, a.inter / 16)] = static_cast<uint8_t>(sbyte);
+          }
+        }
+      } else {
+        // 128 columns per thread in two halves: scale, round to bf16, park 128 bytes in the thread's
+        // own staging row, send them with one bulk store (a full line of the destination row)
+        uint8_t* mine = out_stage + (static_cast<size_t>(warp - 2) * 32 + lane) * C::kOutPitch;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int c0 = part * 128 + half * 64;
+          uint32_t y[4][16];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tc_load16(t_acc + c0 + q * 16, y[q]);
+          tc_wait_ld();
+          if (half == 1) {   // everything is in registers: hand the accumulator back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+          }
+          bulk_store_wait_read();   // the previous store has finished reading the staging row
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2g))) |
+                     (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2g))) << 16);
+            uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
+            s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+          fence_async_smem();
+          if (valid) bulk_store(dst + ft * C::kFeatPerTile + c0, smem_u32(mine), 128);
+          bulk_store_commit();
         }
       }
       aphase ^= 1u;
@@ -242,6 +293,7 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
   }
 
   // ---- teardown ----
+  if (!kFC1 && warp >= 2) bulk_store_wait_all();
   __syncwarp();
   if (*abort_flag != 0u) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
@@ -255,17 +307,17 @@ expert_fc1_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
 
 }  // namespace
 
-bool fc1_pair_supported(const FfnArgs& a, int sm_count) {
-  return a.chunk_tokens == 256 && a.inter % 128 == 0 && (a.hidden / 2) % kStageBytesK == 0 && sm_count % 2 == 0;
+bool pair_tiles_supported(const FfnArgs& a, int sm_count) {
+  return a.chunk_tokens == 256 && a.inter % 256 == 0 && a.hidden % 256 == 0 && sm_count % 2 == 0;
 }
 
-glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  using C = PairCfg;
+namespace {
+template <bool kFC1>
+glmrt_status_t launch_pair(const FfnArgs& a, const PairMaps& maps, int sm_count, cudaStream_t stream) {
+  using C = PairCfg<kFC1>;
   static std::atomic<uint64_t> configured{0};
-  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_fc1_pair_kernel, C::kSmemBytes, "cudaFuncSetAttribute(expert_fc1_pair_kernel)"));
-  PairMaps maps;
-  maps.act = m.act1; maps.gate = m.gate; maps.up = m.up;
-  maps.act_sf = m.act1_sf; maps.gate_sf = m.gate_sf; maps.up_sf = m.up_sf;
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_pair_kernel<kFC1>, C::kSmemBytes,
+                                          "cudaFuncSetAttribute(expert_pair_kernel)"));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1));
   cfg.blockDim = dim3(C::kThreads);
@@ -275,10 +327,25 @@ glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& m, int sm_
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  cudaError_t err = cudaLaunchKernelEx(&cfg, expert_fc1_pair_kernel, a, maps);
-  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "launch expert_fc1_pair_kernel", err);
+  cudaError_t err = cudaLaunchKernelEx(&cfg, expert_pair_kernel<kFC1>, a, maps);
+  if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "launch expert_pair_kernel", err);
   count_launch();
   return GLMRT_STATUS_OK;
+}
+}  // namespace
+
+glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
+  PairMaps maps;
+  maps.act = m.act1; maps.w0 = m.gate; maps.w1 = m.up;
+  maps.act_sf = m.act1_sf; maps.w0_sf = m.gate_sf; maps.w1_sf = m.up_sf;
+  return launch_pair<true>(a, maps, sm_count, stream);
+}
+
+glmrt_status_t launch_fc2_tc_pair(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
+  PairMaps maps;
+  maps.act = m.act2; maps.w0 = m.down; maps.w1 = m.down;
+  maps.act_sf = m.act2_sf; maps.w0_sf = m.down_sf; maps.w1_sf = m.down_sf;
+  return launch_pair<false>(a, maps, sm_count, stream);
 }
 
 }  // namespace glmrt

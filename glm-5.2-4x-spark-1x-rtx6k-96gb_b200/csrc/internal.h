@@ -196,7 +196,7 @@ glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);
 struct TensorMaps {
   CUtensorMap gate, up, down;   // weight codes, 128-row boxes
   CUtensorMap act1, act2;       // activation codes (box rows = chunk_tokens)
-  CUtensorMap act1_sf, gate_sf, up_sf;   // tiled scales seen as rows of 128 bytes, 2 KB boxes (CTA-pair FC1)
+  CUtensorMap act1_sf, gate_sf, up_sf, act2_sf, down_sf;   // tiled scales seen as rows of 128 bytes, 2 KB boxes (CTA-pair kernels)
 };
 // Encodes a 2D uint8 tensor map [rows, row_bytes] with a {128 B, box_rows} box and 128-byte swizzle.
 glmrt_status_t make_codes_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t row_bytes,
@@ -208,9 +208,10 @@ glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& maps, int sm_co
 // gemm_tc_prefill.cu: 128-token chunks, tokens on the MMA rows
 glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
-// gemm_tc_pair.cu: 256-token chunks on CTA pairs (FC1 only; FC2 of such a plan runs the kernel
-// above, which takes each chunk as two halves of 128)
-bool fc1_pair_supported(const FfnArgs& a, int sm_count);
+// gemm_tc_pair.cu: 256-token chunks on CTA pairs (the one-CTA kernels above take such a chunk as
+// two halves of 128, so either GEMM of a 256-slot plan may run on either kind of kernel)
+bool pair_tiles_supported(const FfnArgs& a, int sm_count);
 glmrt_status_t launch_fc1_tc_pair(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
+glmrt_status_t launch_fc2_tc_pair(const FfnArgs& a, const TensorMaps& maps, int sm_count, cudaStream_t stream);
 
 }  // namespace glmrt

@@ -134,11 +134,15 @@ glmrt_status_t build_maps(Layer* l) {
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act1, l->act1_codes, l->max_slots, c.hidden_dim / 2, box));
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&m->act2, l->act2_codes, l->max_slots, c.intermediate_dim / 2, box));
     const uint64_t sf_fc1 = wrows_fc1 * (c.hidden_dim / 16);
+    const uint64_t sf_fc2 = wrows_fc2 * (c.intermediate_dim / 16);
     const uint64_t sf_act1 = static_cast<uint64_t>(l->max_slots) * (c.hidden_dim / 16);
-    if (sf_fc1 % 2048 == 0 && sf_act1 % 2048 == 0) {
+    const uint64_t sf_act2 = static_cast<uint64_t>(l->max_slots) * (c.intermediate_dim / 16);
+    if (sf_fc1 % 2048 == 0 && sf_act1 % 2048 == 0 && sf_fc2 % 2048 == 0 && sf_act2 % 2048 == 0) {
       GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->gate_sf, l->gate_sf, sf_fc1));
       GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->up_sf, l->up_sf, sf_fc1));
       GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->act1_sf, l->act1_sf, sf_act1));
+      GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->down_sf, l->down_sf, sf_fc2));
+      GLMRT_RETURN_IF_ERROR(make_scale_tensor_map(&m->act2_sf, l->act2_sf, sf_act2));
       l->have_sf_maps = true;
     }
   }
@@ -181,11 +185,11 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
                           const uint16_t* residual = nullptr, const uint16_t* shared = nullptr) {
   const auto& c = l->cfg;
   // Work-item size: 32 slots for decode batches (weights on the MMA rows), 128 for prefill (tokens
-  // on the MMA rows); on request 256 (FC1 on CTA pairs) once the average expert receives more than
+  // on the MMA rows); on request 256 (GEMMs on CTA pairs) once the average expert receives more than
   // 192 routes, i.e. when most 256-slot items are better than half full.
   int chunk_tokens = rows <= 256 ? 32 : 128;
   if (chunk_tokens == 128 && (c.flags & GLMRT_B200_LAYER_PAIR_TILES) && !(c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) &&
-      l->sm_count % 2 == 0 && c.hidden_dim % 256 == 0 && c.intermediate_dim % 128 == 0 &&
+      l->sm_count % 2 == 0 && c.hidden_dim % 256 == 0 && c.intermediate_dim % 256 == 0 &&
       rows * c.top_k > static_cast<size_t>(192) * c.experts) {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
     if (l->have_sf_maps) chunk_tokens = 256;
@@ -222,11 +226,14 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   } else {
     if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
     const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
-    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32    ? launch_fc1_tc(f, maps, l->sm_count, stream)
-                          : chunk_tokens == 256 ? launch_fc1_tc_pair(f, maps, l->sm_count, stream)
-                                                : launch_fc1_tc_prefill(f, maps, l->sm_count, stream));
+    const bool pair1 = chunk_tokens == 256 && (c.flags & GLMRT_B200_LAYER_PAIR_FC1);
+    const bool pair2 = chunk_tokens == 256 && (c.flags & GLMRT_B200_LAYER_PAIR_FC2);
+    GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, stream)
+                          : pair1            ? launch_fc1_tc_pair(f, maps, l->sm_count, stream)
+                                             : launch_fc1_tc_prefill(f, maps, l->sm_count, stream));
     mark(l, GLMRT_B200_STAGE_FC2, stream);
     GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, stream)
+                          : pair2            ? launch_fc2_tc_pair(f, maps, l->sm_count, stream)
                                              : launch_fc2_tc_prefill(f, maps, l->sm_count, stream));
   }
   mark(l, GLMRT_B200_STAGE_COMBINE, stream);

@@ -68,7 +68,9 @@ class LayerStats(C.Structure):
 
 
 LAYER_ENGINE_SIMT = 1
-LAYER_PAIR_TILES = 2
+LAYER_PAIR_FC1 = 2
+LAYER_PAIR_FC2 = 4
+LAYER_PAIR_TILES = 6
 FP4_RULE_RNE_PAYLOAD = 0
 FP4_RULE_NEAREST_LOW = 1
 

@@ -249,9 +249,10 @@ typedef struct glmrt_b200_moe_config_t {
 
 enum {
   GLMRT_B200_LAYER_ENGINE_SIMT = 1u, /* run the expert FFN on the SIMT verification kernels */
-  GLMRT_B200_LAYER_PAIR_TILES = 2u,  /* batches above 192 routes per expert: run FC1 on CTA pairs (256 token
-                                        slots per work item, tcgen05 cta_group::2) instead of one-CTA tiles;
-                                        bit-identical results, measured equally fast, off by default */
+  GLMRT_B200_LAYER_PAIR_FC1 = 2u,    /* batches above 192 routes per expert: plan 256-slot work items and run */
+  GLMRT_B200_LAYER_PAIR_FC2 = 4u,    /* FC1 and/or FC2 on CTA pairs (tcgen05 cta_group::2) instead of one-CTA
+                                        tiles; bit-identical results */
+  GLMRT_B200_LAYER_PAIR_TILES = 6u,  /* both */
 };
 
 glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer);

@@ -390,23 +390,24 @@ def test_pair_tiles_match_oracle_and_one_cta_tiles(pkg, small_layer, T):
     hid = O.make_hidden(4200 + T, T, 512)
     oi, ow, oo = O.layer_forward(small_layer, hid, K, mode="O1")
     outs = {}
-    for engine in ("tc2", "tc"):
+    for engine in ("tc2", "tc2-fc1", "tc2-fc2", "tc"):
         layer = make(pkg, small_layer, K, 2048, engine)
         out, idx, w = layer.forward(to_dev(hid), want_routes=True)
         layer.check()
         chunks = layer.debug("CHUNKS", np.int32).reshape(-1, 4)
         n_chunks = int(layer.debug("COUNTERS", np.uint32)[0])
         width = int(chunks[:n_chunks, 2].max())
-        assert (width > 128) == (engine == "tc2"), f"{engine}: widest work item {width}"
+        assert (width > 128) == engine.startswith("tc2"), f"{engine}: widest work item {width}"
         assert O.router_indices_equivalent(idx.cpu().numpy(), oi, sel64(small_layer, hid))
         err = O.rel_l2_per_token(to_bits(out), oo)
         assert err.max() <= TOL, f"{engine} T={T}: max per-token rel L2 {err.max():.3e}"
         outs[engine] = to_bits(out).copy()
         layer.close()
-    diff = O.rel_l2_per_token(outs["tc2"], outs["tc"])
-    print(f"pair vs one-CTA tiles T={T}: max per-token rel L2 {diff.max():.3e}, "
-          f"{(outs['tc2'] != outs['tc']).mean():.2e} of bf16 words differ")
-    assert diff.max() <= 1e-3
+    for engine in ("tc2", "tc2-fc1", "tc2-fc2"):
+        diff = O.rel_l2_per_token(outs[engine], outs["tc"])
+        print(f"{engine} vs one-CTA tiles T={T}: max per-token rel L2 {diff.max():.3e}, "
+              f"{(outs[engine] != outs['tc']).mean():.2e} of bf16 words differ")
+        assert diff.max() <= 1e-3
 
 
 @pytest.mark.parametrize("T", [16, 300, 1000])
