@@ -343,6 +343,40 @@ extern "C" glmrt_status_t glmrt_cuda_router_topk_bf16(const uint16_t* hidden, co
                                                           top_k, nullptr));
   return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
 }
+// The reference's variant with caller-owned scratch (no allocation, so it can be captured in a CUDA
+// graph; native/cuda/kernels/router.cu:582-644 sorts every row with a segmented radix sort).  Here
+// the same selection kernel as everywhere runs on logits kept in `corrected_scores`; the other
+// scratch arrays are validated like the reference does and left untouched.
+extern "C" glmrt_status_t glmrt_cuda_router_topk_bf16_cub_async(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias, float* corrected_scores,
+    float* sorted_corrected_scores, uint32_t* unsorted_indices, uint32_t* sorted_indices, int* segment_offsets,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, void* cub_temp_storage,
+    size_t cub_temp_storage_bytes, size_t rows, size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream) {
+  GLMRT_RETURN_IF_ERROR(validate(hidden, router_weight, correction_bias, topk_indices, topk_weights, rows, hidden_dim,
+                                 experts, top_k));
+  if (topk_scores == nullptr || corrected_scores == nullptr || sorted_corrected_scores == nullptr ||
+      unsorted_indices == nullptr || sorted_indices == nullptr || segment_offsets == nullptr ||
+      cub_temp_storage == nullptr || cub_temp_storage_bytes == 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router (caller scratch): null scratch pointer or empty temporary storage");
+  if (rows * experts > static_cast<size_t>(std::numeric_limits<int>::max()))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router (caller scratch): rows * experts out of range");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  GLMRT_RETURN_IF_ERROR(launch_router(hidden, true, router_weight, true, correction_bias, corrected_scores, topk_indices,
+                                      topk_scores, topk_weights, rows, hidden_dim, experts, top_k, 2.5f,
+                                      static_cast<cudaStream_t>(cuda_stream)));
+  return ok();
+}
+extern "C" glmrt_status_t glmrt_cuda_router_topk_bf16_cub(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias, float* corrected_scores,
+    float* sorted_corrected_scores, uint32_t* unsorted_indices, uint32_t* sorted_indices, int* segment_offsets,
+    uint32_t* topk_indices, float* topk_scores, float* topk_weights, void* cub_temp_storage,
+    size_t cub_temp_storage_bytes, size_t rows, size_t hidden_dim, size_t experts, size_t top_k) {
+  GLMRT_RETURN_IF_ERROR(glmrt_cuda_router_topk_bf16_cub_async(
+      hidden, router_weight, correction_bias, corrected_scores, sorted_corrected_scores, unsorted_indices,
+      sorted_indices, segment_offsets, topk_indices, topk_scores, topk_weights, cub_temp_storage,
+      cub_temp_storage_bytes, rows, hidden_dim, experts, top_k, nullptr));
+  return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+}
 extern "C" glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
     const uint16_t* hidden, const float* router_weight, const float* correction_bias, float* logits_scratch,
     uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows, size_t hidden_dim,

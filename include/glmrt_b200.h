@@ -117,6 +117,22 @@ glmrt_status_t glmrt_cuda_router_topk_bf16_async(
     const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias,
     uint32_t* topk_indices, float* topk_scores, float* topk_weights, size_t rows,
     size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
+/* glmrt_native.h:1019-1030: the variant whose scratch the caller owns (rows * experts floats in
+ * corrected_scores and sorted_corrected_scores, rows * experts indices twice, rows + 1 offsets,
+ * temporary storage), so that nothing is allocated.  Same results as the entry points above; the
+ * logits live in corrected_scores, the other scratch arrays are only validated. */
+glmrt_status_t glmrt_cuda_router_topk_bf16_cub(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias,
+    float* corrected_scores, float* sorted_corrected_scores, uint32_t* unsorted_indices,
+    uint32_t* sorted_indices, int* segment_offsets, uint32_t* topk_indices, float* topk_scores,
+    float* topk_weights, void* cub_temp_storage, size_t cub_temp_storage_bytes, size_t rows,
+    size_t hidden_dim, size_t experts, size_t top_k);
+glmrt_status_t glmrt_cuda_router_topk_bf16_cub_async(
+    const uint16_t* hidden, const uint16_t* router_weight, const float* correction_bias,
+    float* corrected_scores, float* sorted_corrected_scores, uint32_t* unsorted_indices,
+    uint32_t* sorted_indices, int* segment_offsets, uint32_t* topk_indices, float* topk_scores,
+    float* topk_weights, void* cub_temp_storage, size_t cub_temp_storage_bytes, size_t rows,
+    size_t hidden_dim, size_t experts, size_t top_k, void* cuda_stream);
 /* Addition: bf16 activations against float32 router weights, the operand types of
  * the Python oracle (python/reference/glmrt_reference/glm_moe_dsa_layer_ref.py:62-83).
  * `logits_scratch` holds rows * experts floats. */

@@ -100,6 +100,22 @@ def test_router_reference_named_entry_points_and_golden(lib, golden_dir):
     oi, ow, _, _ = O.router_topk(O.bf16_to_f32(hid), O.bf16_to_f32(rwb), bias, 4)
     np.testing.assert_array_equal(idx.cpu().numpy(), oi.astype(np.int32))
     np.testing.assert_allclose(wt.cpu().numpy(), ow, atol=2e-6)
+    # the variant with caller-owned scratch (native/include/glmrt_native.h:1019-1030): same answer, nothing allocated
+    n = 9 * 32
+    f1, f2 = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    u1 = torch.zeros(n, dtype=torch.int32, device="cuda")
+    u2 = torch.zeros(n, dtype=torch.int32, device="cuda")
+    seg = torch.zeros(10, dtype=torch.int32, device="cuda")
+    tmp = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    idx2, sc2, wt2 = torch.empty_like(idx), torch.empty_like(sc), torch.empty_like(wt)
+    lib.call("glmrt_cuda_router_topk_bf16_cub_async", ptr(xb), ptr(wb), ptr(bb), ptr(f1), ptr(f2), ptr(u1), ptr(u2),
+             ptr(seg), ptr(idx2), ptr(sc2), ptr(wt2), ptr(tmp), C.c_size_t(4096), C.c_size_t(9), C.c_size_t(512),
+             C.c_size_t(32), C.c_size_t(4), stream())
+    torch.cuda.synchronize()
+    assert torch.equal(idx2, idx) and torch.equal(wt2, wt) and torch.equal(sc2, sc)
+    assert lib.call_status("glmrt_cuda_router_topk_bf16_cub_async", ptr(xb), ptr(wb), ptr(bb), ptr(f1), ptr(f2), ptr(u1),
+                           ptr(u2), ptr(seg), ptr(idx2), ptr(sc2), ptr(wt2), None, C.c_size_t(0), C.c_size_t(9),
+                           C.c_size_t(512), C.c_size_t(32), C.c_size_t(4), stream()) == 1
 
 
 def test_router_ties_go_to_lower_expert_and_nonfinite_scores_are_skipped(lib):
