@@ -80,6 +80,15 @@ DEBUG = {name: i for i, name in enumerate(
      "SCALE2", "TOPK_IDX", "TOPK_W"])}
 
 
+class RouteBatchedMetadata(C.Structure):
+    """glmrt_nvfp4_route_batched_metadata_t (native/include/glmrt_native.h:114-127)."""
+    _fields_ = [("gate_weight", C.c_size_t), ("gate_scale", C.c_size_t), ("up_weight", C.c_size_t),
+                ("up_scale", C.c_size_t), ("down_weight", C.c_size_t), ("down_scale", C.c_size_t),
+                ("intermediate", C.c_size_t), ("down_weight_row_stride_bytes", C.c_size_t),
+                ("down_scale_row_stride_bytes", C.c_size_t), ("gate_scale_2", C.c_float), ("up_scale_2", C.c_float),
+                ("down_scale_2", C.c_float)]
+
+
 def declared_symbols(header_path: str = HEADER) -> list[str]:
     """Every function name declared in include/glmrt_b200.h."""
     text = open(header_path).read()

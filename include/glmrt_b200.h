@@ -195,6 +195,53 @@ glmrt_status_t glmrt_cuda_b12x_gather_nvfp4_rows_bf16_async(
 /* ------------------------------------------------------------------------ */
 /* Combine (native/include/glmrt_native.h:679-681,843-846)                    */
 /* ------------------------------------------------------------------------ */
+/* The reference's float32 route MLP on bf16 activations and NVFP4 weights (W4A16; glmrt_native.h:
+ * 114-127, 572-597; kernels native/cuda/kernels/mlp.cu:218-420).  For every route r with
+ * row_indices[r] < rows: activation_workspace[r, m] = silu(x . gate[m]) * (x . up[m]) and
+ * accumulator[row_indices[r], o] += route_weights[r] * (activation[r] . down[o]), all float32;
+ * routes whose row index is out of range are skipped.  `grouped`: every route uses the one expert
+ * given; `batched`: route r uses route_metadata[r] (device memory).  hidden_dim and the
+ * intermediate sizes must be multiples of 16; hidden_row_stride counts bf16 elements. */
+typedef struct glmrt_nvfp4_route_batched_metadata_t {
+  uintptr_t gate_weight;
+  uintptr_t gate_scale;
+  uintptr_t up_weight;
+  uintptr_t up_scale;
+  uintptr_t down_weight;
+  uintptr_t down_scale;
+  size_t intermediate;
+  size_t down_weight_row_stride_bytes;
+  size_t down_scale_row_stride_bytes;
+  float gate_scale_2;
+  float up_scale_2;
+  float down_scale_2;
+} glmrt_nvfp4_route_batched_metadata_t;
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_grouped_staged_accumulate_f32(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const uint8_t* gate_weight, const uint8_t* gate_scale, const uint8_t* up_weight,
+    const uint8_t* up_scale, const uint8_t* down_weight, const uint8_t* down_scale,
+    float* activation_workspace, float* accumulator, size_t rows, size_t routes,
+    size_t hidden_dim, size_t hidden_row_stride, size_t intermediate, size_t output_dim,
+    size_t down_weight_row_stride_bytes, size_t down_scale_row_stride_bytes,
+    float gate_scale_2, float up_scale_2, float down_scale_2);
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_grouped_staged_accumulate_f32_async(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const uint8_t* gate_weight, const uint8_t* gate_scale, const uint8_t* up_weight,
+    const uint8_t* up_scale, const uint8_t* down_weight, const uint8_t* down_scale,
+    float* activation_workspace, float* accumulator, size_t rows, size_t routes,
+    size_t hidden_dim, size_t hidden_row_stride, size_t intermediate, size_t output_dim,
+    size_t down_weight_row_stride_bytes, size_t down_scale_row_stride_bytes,
+    float gate_scale_2, float up_scale_2, float down_scale_2, void* cuda_stream);
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace,
+    float* accumulator, size_t rows, size_t routes, size_t hidden_dim,
+    size_t hidden_row_stride, size_t max_intermediate, size_t output_dim);
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32_async(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace,
+    float* accumulator, size_t rows, size_t routes, size_t hidden_dim,
+    size_t hidden_row_stride, size_t max_intermediate, size_t output_dim, void* cuda_stream);
 /* b12x_direct.cu:203-219: fixed-order float32 sum of the 8 per-route bf16 rows of width
  * 6144 per token, truncated to bf16.  routed_bf16 is [rows * 8, 6144]. */
 glmrt_status_t glmrt_cuda_b12x_spark_sum_topk8_bf16_async(

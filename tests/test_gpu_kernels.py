@@ -297,6 +297,77 @@ def test_residual_adds_match_oracle_bit_exactly(lib):
     assert lib.call_status("glmrt_cuda_residual_add_bf16_async", None, None, None, C.c_size_t(4), stream()) == 1
 
 
+def test_w4a16_route_mlp_entry_points_match_the_float32_reference(lib, pkg):
+    """The reference's float32 route MLP symbols (bf16 activations x NVFP4 weights, no activation
+    quantisation; native/cuda/kernels/mlp.cu:218-420): grouped (one expert for all routes) and batched
+    (an expert per route through the metadata table), against the float32 expert_forward of the
+    Python reference (moe_ref.py:17-21) restated in the oracle.  A route whose row index is out of
+    range is skipped."""
+    from glmrt_b200 import native as N
+    H, I, E = 512, 256, 3
+    ref = O.make_layer(5, H, I, E)
+    rows, routes = 6, 14
+    rng = np.random.default_rng(2)
+    hid = O.make_hidden(88, rows, H)
+    stride = H + 32                                           # rows wider than hidden_dim
+    xs = np.zeros((rows, stride), np.uint16)
+    xs[:, :H] = hid
+    row_idx = rng.integers(0, rows, routes).astype(np.uint32)
+    row_idx[5] = 1000                                         # out of range: skipped
+    rw = rng.random(routes, np.float32)
+    experts = rng.integers(0, E, routes)
+
+    def pack(c):
+        c = np.ascontiguousarray(c, np.uint8)
+        return (c[..., 0::2] | (c[..., 1::2] << 4)).astype(np.uint8)
+
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    W = [dict(g=dev(pack(ref.gate[e])), gs=dev(ref.gate_s[e]), u=dev(pack(ref.up[e])), us=dev(ref.up_s[e]),
+              d=dev(pack(ref.down[e])), ds=dev(ref.down_s[e])) for e in range(E)]
+    x = dev(xs.view(np.int16)).view(torch.bfloat16)
+    ri, rwt = dev(row_idx.view(np.int32)), dev(rw)
+    x32 = O.bf16_to_f32(hid)
+
+    def expected(expert_of_route):
+        acc = np.zeros((rows, H), np.float64)
+        for r in range(routes):
+            if row_idx[r] >= rows:
+                continue
+            y = O.expert_forward(x32[row_idx[r]][None, :], ref.expert(int(expert_of_route[r])))[0]
+            acc[row_idx[r]] += np.float64(rw[r]) * y.astype(np.float64)
+        return acc
+
+    work = torch.zeros(routes * I, device="cuda")
+    # grouped: expert 1 for every route
+    acc = torch.zeros(rows, H, device="cuda")
+    s2 = ref.scale2[1]
+    lib.call("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_grouped_staged_accumulate_f32_async", ptr(x), ptr(ri), ptr(rwt),
+             ptr(W[1]["g"]), ptr(W[1]["gs"]), ptr(W[1]["u"]), ptr(W[1]["us"]), ptr(W[1]["d"]), ptr(W[1]["ds"]), ptr(work),
+             ptr(acc), C.c_size_t(rows), C.c_size_t(routes), C.c_size_t(H), C.c_size_t(stride), C.c_size_t(I), C.c_size_t(H),
+             C.c_size_t(I // 2), C.c_size_t(I // 16), C.c_float(s2[0]), C.c_float(s2[1]), C.c_float(s2[2]), stream())
+    torch.cuda.synchronize()
+    want = expected(np.full(routes, 1))
+    scale = np.abs(want).max()
+    np.testing.assert_allclose(acc.cpu().numpy(), want, atol=2e-5 * scale, rtol=1e-4)
+    assert float(work[5 * I:(5 + 1) * I].abs().max()) == 0.0      # the skipped route staged zeros
+    # batched: an expert per route
+    meta = (N.RouteBatchedMetadata * routes)()
+    for r in range(routes):
+        w, s2 = W[int(experts[r])], ref.scale2[int(experts[r])]
+        meta[r] = N.RouteBatchedMetadata(w["g"].data_ptr(), w["gs"].data_ptr(), w["u"].data_ptr(), w["us"].data_ptr(),
+                                         w["d"].data_ptr(), w["ds"].data_ptr(), I, I // 2, I // 16, s2[0], s2[1], s2[2])
+    meta_dev = torch.from_numpy(np.frombuffer(bytes(meta), np.uint8).copy()).cuda()
+    acc2 = torch.zeros(rows, H, device="cuda")
+    lib.call("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32", ptr(x), ptr(ri), ptr(rwt),
+             ptr(meta_dev), ptr(work), ptr(acc2), C.c_size_t(rows), C.c_size_t(routes), C.c_size_t(H), C.c_size_t(stride),
+             C.c_size_t(I), C.c_size_t(H))
+    want2 = expected(experts)
+    np.testing.assert_allclose(acc2.cpu().numpy(), want2, atol=2e-5 * np.abs(want2).max(), rtol=1e-4)
+    assert lib.call_status("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32_async", ptr(x), ptr(ri),
+                           ptr(rwt), None, ptr(work), ptr(acc2), C.c_size_t(rows), C.c_size_t(routes), C.c_size_t(H),
+                           C.c_size_t(stride), C.c_size_t(I), C.c_size_t(H), stream()) == 1
+
+
 def test_bf16_rows_to_fp8_row_scaled_matches_oracle(lib):
     """native/cuda/kernels/residual.cu:245-277: E4M3 bytes + one float32 scale per row; an all-zero
     row keeps scale 1, non-finite values encode 0 and do not enter the row maximum."""
