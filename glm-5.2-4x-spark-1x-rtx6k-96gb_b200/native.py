@@ -89,6 +89,11 @@ class RouteBatchedMetadata(C.Structure):
                 ("down_scale_2", C.c_float)]
 
 
+class RouteShardReductionBuffers(C.Structure):
+    """glmrt_route_shard_reduction_buffers_t (native/include/glmrt_native.h:101-105)."""
+    _fields_ = [("local", DeviceBuffer), ("peers", DeviceBuffer * 3), ("output_f32", DeviceBuffer)]
+
+
 def declared_symbols(header_path: str = HEADER) -> list[str]:
     """Every function name declared in include/glmrt_b200.h."""
     text = open(header_path).read()

@@ -258,6 +258,66 @@ glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_weighted_to_f32_async(
 glmrt_status_t glmrt_cuda_gather_rows_bf16_async(const uint16_t* src, const uint32_t* row_indices,
                                                  uint16_t* dst, size_t rows, size_t row_width,
                                                  void* cuda_stream);
+/* The rest of the row gather / scatter-add family (glmrt_native.h:757-828; kernels residual.cu:
+ * 133-158,409-535).  Scatter-adds decode each compact source row (float32, bf16, row-scaled FP8 =
+ * row_width E4M3 bytes + a float32 scale, or NVFP4 = row_width/2 code bytes + row_width/16 E4M3
+ * scale bytes) and add it to dst[row_indices[r]]; with at most 64 source rows the contributions
+ * of an output value are added in source order (no atomics), above that with float32 atomics.
+ * Empty work (rows or row_width 0) is accepted. */
+glmrt_status_t glmrt_cuda_gather_rows_f32(const float* src, const uint32_t* row_indices, float* dst,
+                                          size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_gather_rows_f32_async(const float* src, const uint32_t* row_indices,
+                                                float* dst, size_t rows, size_t row_width,
+                                                void* cuda_stream);
+glmrt_status_t glmrt_cuda_gather_rows_bf16(const uint16_t* src, const uint32_t* row_indices,
+                                           uint16_t* dst, size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_f32(const float* src, const uint32_t* row_indices,
+                                               float* dst, size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_f32_async(const float* src, const uint32_t* row_indices,
+                                                     float* dst, size_t rows, size_t row_width,
+                                                     void* cuda_stream);
+glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_to_f32(const uint16_t* src,
+                                                       const uint32_t* row_indices, float* dst,
+                                                       size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_bf16_to_f32_async(const uint16_t* src,
+                                                             const uint32_t* row_indices, float* dst,
+                                                             size_t rows, size_t row_width,
+                                                             void* cuda_stream);
+glmrt_status_t glmrt_cuda_scatter_add_rows_fp8_e4m3_row_scaled_to_f32(
+    const uint8_t* src, size_t src_row_stride_bytes, const uint32_t* row_indices, float* dst,
+    size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_fp8_e4m3_row_scaled_to_f32_async(
+    const uint8_t* src, size_t src_row_stride_bytes, const uint32_t* row_indices, float* dst,
+    size_t rows, size_t row_width, void* cuda_stream);
+glmrt_status_t glmrt_cuda_scatter_add_rows_nvfp4_e2m1_fp8_e4m3_to_f32(
+    const uint8_t* src, size_t src_row_stride_bytes, const uint32_t* row_indices, float* dst,
+    size_t rows, size_t row_width);
+glmrt_status_t glmrt_cuda_scatter_add_rows_nvfp4_e2m1_fp8_e4m3_to_f32_async(
+    const uint8_t* src, size_t src_row_stride_bytes, const uint32_t* row_indices, float* dst,
+    size_t rows, size_t row_width, void* cuda_stream);
+/* Sum of a local partial (float32 or bf16 rows) and one to three peers' wire rows into float32,
+ * peers added in order (glmrt_native.h:90-105,829-836; kernel residual.cu:544-589). */
+typedef enum glmrt_route_shard_wire_dtype_t {
+  GLMRT_ROUTE_SHARD_WIRE_BF16 = 1,
+  GLMRT_ROUTE_SHARD_WIRE_FP8_E4M3_ROW_SCALED = 2,
+  GLMRT_ROUTE_SHARD_WIRE_NVFP4_E2M1_FP8_E4M3 = 3,
+} glmrt_route_shard_wire_dtype_t;
+typedef enum glmrt_route_shard_local_dtype_t {
+  GLMRT_ROUTE_SHARD_LOCAL_F32 = 1,
+  GLMRT_ROUTE_SHARD_LOCAL_BF16 = 2,
+} glmrt_route_shard_local_dtype_t;
+typedef struct glmrt_route_shard_reduction_buffers_t {
+  glmrt_device_buffer_t local;
+  glmrt_device_buffer_t peers[3];
+  glmrt_device_buffer_t output_f32;
+} glmrt_route_shard_reduction_buffers_t;
+glmrt_status_t glmrt_cuda_reduce_route_shards_to_f32(
+    const glmrt_route_shard_reduction_buffers_t* buffers, size_t rows, size_t row_width,
+    size_t peer_row_stride_bytes, uint32_t local_dtype, uint32_t peer_dtype, uint32_t peer_count);
+glmrt_status_t glmrt_cuda_reduce_route_shards_to_f32_async(
+    const glmrt_route_shard_reduction_buffers_t* buffers, size_t rows, size_t row_width,
+    size_t peer_row_stride_bytes, uint32_t local_dtype, uint32_t peer_dtype, uint32_t peer_count,
+    void* cuda_stream);
 /* Residual adds after the routed/shared MLP (native/include/glmrt_native.h:715-730, kernels
  * native/cuda/kernels/residual.cu:18-62): float32 adds, bf16 results stored by truncation, a
  * float32 delta truncated to bf16 first.  count == 0 is accepted and does nothing. */

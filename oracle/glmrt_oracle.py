@@ -558,6 +558,41 @@ def residual_add_shared_f32_delta_bf16(residual_bits, shared_bits, routed_f32) -
     return residual_add_bf16(residual_bits, mlp)
 
 
+def decode_wire_rows(rows_bytes, width: int, dtype: str) -> np.ndarray:
+    """[R, stride] bytes of wire rows -> [R, width] float32 (native/cuda/kernels/residual.cu:544-559):
+    "bf16"; "fp8" = width E4M3 bytes then a float32 scale; "nvfp4" = width/2 code bytes (low nibble
+    first) then width/16 E4M3 scale bytes."""
+    b = np.asarray(rows_bytes, np.uint8)
+    if dtype == "bf16":
+        return bf16_to_f32(np.ascontiguousarray(b[:, :2 * width]).view(np.uint16))
+    if dtype == "fp8":
+        scale = np.ascontiguousarray(b[:, width:width + 4]).view(np.float32)
+        return (e4m3_decode(b[:, :width]) * scale).astype(np.float32)
+    packed = b[:, :width // 2]
+    codes = np.empty((b.shape[0], width), np.uint8)
+    codes[:, 0::2] = packed & 0x0F
+    codes[:, 1::2] = packed >> 4
+    scales = e4m3_decode(b[:, width // 2:width // 2 + width // 16])
+    return (E2M1_VALUES[codes] * np.repeat(scales, 16, axis=1)).astype(np.float32)
+
+
+def scatter_add_rows_to_f32(values_f32, row_indices, dst_f32) -> np.ndarray:
+    """dst[row_indices[r]] += values[r], contributions added in source order, float32
+    (native/cuda/kernels/residual.cu:438-453, the ordered form used up to 64 rows)."""
+    out = np.array(dst_f32, np.float32, copy=True)
+    for r, d in enumerate(np.asarray(row_indices)):
+        out[int(d)] = (out[int(d)] + np.asarray(values_f32[r], np.float32)).astype(np.float32)
+    return out
+
+
+def reduce_route_shards_to_f32(local_f32, peers_f32) -> np.ndarray:
+    """local + peers[0] + peers[1] + ... in float32, in that order (residual.cu:561-589)."""
+    out = np.asarray(local_f32, np.float32).copy()
+    for p in peers_f32:
+        out = (out + np.asarray(p, np.float32)).astype(np.float32)
+    return out
+
+
 def bf16_rows_to_fp8_e4m3_row_scaled(rows_bits) -> np.ndarray:
     """[R, W] bf16 -> [R, W + 4] bytes: E4M3 values then one little-endian float32 scale per row
     (native/cuda/kernels/residual.cu:245-277): scale = max |finite| / 448, 1 for an all-zero row;

@@ -368,6 +368,73 @@ def test_w4a16_route_mlp_entry_points_match_the_float32_reference(lib, pkg):
                            C.c_size_t(stride), C.c_size_t(I), C.c_size_t(H), stream()) == 1
 
 
+@pytest.mark.parametrize("rows", [5, 200])
+def test_row_gather_scatter_add_and_shard_reduce_family(lib, pkg, rows):
+    """native/include/glmrt_native.h:757-836.  Up to 64 source rows the scatter-adds are ordered
+    (bit-exact against the oracle's source-order sum, duplicates in the index list included); above
+    that they use atomics (checked to float32 round-off)."""
+    from glmrt_b200 import native as N
+    rng = np.random.default_rng(rows)
+    W, D = 128, 9
+    idx = rng.integers(0, D, rows).astype(np.uint32)
+    ridx = torch.from_numpy(idx.view(np.int32)).cuda()
+    f32 = rng.standard_normal((rows, W), np.float32)
+    bits = O.bf16_round(f32)
+    fp8 = O.bf16_rows_to_fp8_e4m3_row_scaled(bits)
+    dst0 = rng.standard_normal((D, W), np.float32)
+    exact = rows <= 64
+
+    def check(symbol, src_tensor, values, *extra):
+        dst = torch.from_numpy(dst0.copy()).cuda()
+        lib.call(symbol, ptr(src_tensor), *extra, ptr(ridx), ptr(dst), C.c_size_t(rows), C.c_size_t(W), stream())
+        torch.cuda.synchronize()
+        want = O.scatter_add_rows_to_f32(values, idx, dst0)
+        if exact:
+            np.testing.assert_array_equal(dst.cpu().numpy(), want)
+        else:
+            np.testing.assert_allclose(dst.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+
+    check("glmrt_cuda_scatter_add_rows_f32_async", torch.from_numpy(f32).cuda(), f32)
+    check("glmrt_cuda_scatter_add_rows_bf16_to_f32_async", bf16_tensor(bits), O.bf16_to_f32(bits))
+    check("glmrt_cuda_scatter_add_rows_fp8_e4m3_row_scaled_to_f32_async", torch.from_numpy(fp8).cuda(),
+          O.decode_wire_rows(fp8, W, "fp8"), C.c_size_t(W + 4))
+    pay = torch.zeros(rows * (W // 2 + W // 16), dtype=torch.uint8, device="cuda")
+    xb = bf16_tensor(bits)
+    lib.call("glmrt_cuda_b12x_quantize_bf16_nvfp4_row_payload_async", N.DeviceBuffer.of(xb.data_ptr(), xb.numel() * 2),
+             N.DeviceBuffer.of(pay.data_ptr(), pay.numel()), C.c_size_t(rows), C.c_size_t(W), stream())
+    torch.cuda.synchronize()
+    nvrows = pay.cpu().numpy().reshape(rows, W // 2 + W // 16)
+    check("glmrt_cuda_scatter_add_rows_nvfp4_e2m1_fp8_e4m3_to_f32_async", pay, O.decode_wire_rows(nvrows, W, "nvfp4"),
+          C.c_size_t(W // 2 + W // 16))
+    # gathers
+    table = rng.standard_normal((D, W), np.float32)
+    t = torch.from_numpy(table).cuda()
+    g = torch.zeros(rows, W, device="cuda")
+    lib.call("glmrt_cuda_gather_rows_f32", ptr(t), ptr(ridx), ptr(g), C.c_size_t(rows), C.c_size_t(W))
+    np.testing.assert_array_equal(g.cpu().numpy(), table[idx.astype(np.int64)])
+    tb = bf16_tensor(O.bf16_round(table))
+    gb = torch.zeros(rows, W, dtype=torch.bfloat16, device="cuda")
+    lib.call("glmrt_cuda_gather_rows_bf16", ptr(tb), ptr(ridx), ptr(gb), C.c_size_t(rows), C.c_size_t(W))
+    np.testing.assert_array_equal(gb.cpu().view(torch.int16).numpy().view(np.uint16), O.bf16_round(table)[idx.astype(np.int64)])
+    # shard reduce: bf16 local + two row-scaled FP8 peers + one more, peers added in order
+    local = O.bf16_round(rng.standard_normal((rows, W), np.float32))
+    peers = [O.bf16_rows_to_fp8_e4m3_row_scaled(O.bf16_round(rng.standard_normal((rows, W), np.float32))) for _ in range(3)]
+    lt = bf16_tensor(local)
+    pts = [torch.from_numpy(p).cuda() for p in peers]
+    out = torch.zeros(rows, W, device="cuda")
+    bufs = N.RouteShardReductionBuffers()
+    bufs.local = N.DeviceBuffer.of(lt.data_ptr(), lt.numel() * 2)
+    for i, p in enumerate(pts):
+        bufs.peers[i] = N.DeviceBuffer.of(p.data_ptr(), p.numel())
+    bufs.output_f32 = N.DeviceBuffer.of(out.data_ptr(), out.numel() * 4)
+    lib.call("glmrt_cuda_reduce_route_shards_to_f32", C.byref(bufs), C.c_size_t(rows), C.c_size_t(W), C.c_size_t(W + 4),
+             C.c_uint32(2), C.c_uint32(2), C.c_uint32(3))
+    want = O.reduce_route_shards_to_f32(O.bf16_to_f32(local), [O.decode_wire_rows(p, W, "fp8") for p in peers])
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    assert lib.call_status("glmrt_cuda_reduce_route_shards_to_f32", C.byref(bufs), C.c_size_t(rows), C.c_size_t(W),
+                           C.c_size_t(W + 4), C.c_uint32(2), C.c_uint32(2), C.c_uint32(4)) == 1
+
+
 def test_bf16_rows_to_fp8_row_scaled_matches_oracle(lib):
     """native/cuda/kernels/residual.cu:245-277: E4M3 bytes + one float32 scale per row; an all-zero
     row keeps scale 1, non-finite values encode 0 and do not enter the row maximum."""
