@@ -53,16 +53,23 @@ glmrt_status_t run(const uint16_t* residual, const uint16_t* delta_bf16, const f
 // bf16 rows -> E4M3 bytes followed by one float32 scale per row (the reference's response dtype
 // Fp8E4m3RowScaled, native/cuda/kernels/residual.cu:245-277): scale = max |finite value| / 448 (1 when
 // the row is all zero), byte = e4m3(value / scale) with saturation, non-finite values encode 0.
+__device__ __forceinline__ float load_value(const uint16_t* p) { return bf16_bits_to_f32(*p); }
+__device__ __forceinline__ float load_value(const float* p) { return *p; }
+
+// T = uint16_t (bf16 rows, in place order) or float (float32 rows picked through row_indices:
+// the response pack of residual.cu:160-196)
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
-bf16_rows_to_fp8_row_scaled_kernel(const uint16_t* __restrict__ src, uint8_t* __restrict__ dst, size_t row_width,
-                                   size_t dst_row_stride_bytes) {
+rows_to_fp8_row_scaled_kernel(const T* __restrict__ src, const uint32_t* __restrict__ row_indices,
+                              uint8_t* __restrict__ dst, size_t row_width, size_t dst_row_stride_bytes) {
   __shared__ float warp_max[kThreads / 32];
   __shared__ float row_scale;
-  const uint16_t* source = src + blockIdx.x * row_width;
+  const size_t src_row = row_indices != nullptr ? static_cast<size_t>(row_indices[blockIdx.x]) : blockIdx.x;
+  const T* source = src + src_row * row_width;
   uint8_t* output = dst + blockIdx.x * dst_row_stride_bytes;
   float m = 0.0f;
   for (size_t col = threadIdx.x; col < row_width; col += kThreads) {
-    const float v = bf16_bits_to_f32(source[col]);
+    const float v = load_value(source + col);
     m = fmaxf(m, isfinite(v) ? fabsf(v) : 0.0f);
   }
 #pragma unroll
@@ -78,7 +85,7 @@ bf16_rows_to_fp8_row_scaled_kernel(const uint16_t* __restrict__ src, uint8_t* __
   __syncthreads();
   const float scale = row_scale;
   for (size_t col = threadIdx.x; col < row_width; col += kThreads) {
-    const float v = bf16_bits_to_f32(source[col]);
+    const float v = load_value(source + col);
     output[col] = static_cast<uint8_t>(f32_to_e4m3_satfinite(isfinite(v) ? __fdiv_rn(v, scale) : 0.0f));
   }
 }
@@ -92,9 +99,9 @@ glmrt_status_t sync_null(glmrt_status_t st) {
 
 glmrt_status_t launch_bf16_rows_to_fp8_row_scaled(const uint16_t* src, uint8_t* dst, size_t rows, size_t row_width,
                                                   size_t dst_row_stride_bytes, cudaStream_t stream) {
-  bf16_rows_to_fp8_row_scaled_kernel<<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(src, dst, row_width,
-                                                                                          dst_row_stride_bytes);
-  GLMRT_LAUNCH_CHECK("bf16_rows_to_fp8_row_scaled_kernel");
+  rows_to_fp8_row_scaled_kernel<uint16_t><<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(
+      src, nullptr, dst, row_width, dst_row_stride_bytes);
+  GLMRT_LAUNCH_CHECK("rows_to_fp8_row_scaled_kernel");
   return GLMRT_STATUS_OK;
 }
 
@@ -117,6 +124,28 @@ extern "C" glmrt_status_t glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async(cons
   GLMRT_RETURN_IF_ERROR(launch_bf16_rows_to_fp8_row_scaled(src, dst, rows, row_width, dst_row_stride_bytes,
                                                            static_cast<cudaStream_t>(cuda_stream)));
   return ok();
+}
+
+extern "C" glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_async(
+    const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
+    size_t dst_row_stride_bytes, void* cuda_stream) {
+  if (src == nullptr || row_indices == nullptr || dst == nullptr || rows == 0 || row_width == 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows_f32_to_fp8_row_scaled: null pointer or empty shape");
+  if (row_width > SIZE_MAX - sizeof(float) || dst_row_stride_bytes < row_width + sizeof(float) ||
+      dst_row_stride_bytes % alignof(float) != 0 || row_width % alignof(float) != 0 || rows > 0x7fffffffull)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT,
+                "gather_rows_f32_to_fp8_row_scaled: the row stride must hold the row and a float32 scale, 4-byte aligned");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  rows_to_fp8_row_scaled_kernel<float><<<static_cast<unsigned>(rows), kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, row_indices, dst, row_width, dst_row_stride_bytes);
+  GLMRT_LAUNCH_CHECK("rows_to_fp8_row_scaled_kernel");
+  return ok();
+}
+extern "C" glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled(const float* src, const uint32_t* row_indices,
+                                                                            uint8_t* dst, size_t rows, size_t row_width,
+                                                                            size_t dst_row_stride_bytes) {
+  return sync_null(glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_async(src, row_indices, dst, rows, row_width,
+                                                                           dst_row_stride_bytes, nullptr));
 }
 
 extern "C" glmrt_status_t glmrt_cuda_residual_add_bf16_async(const uint16_t* residual, const uint16_t* delta,

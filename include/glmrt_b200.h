@@ -337,6 +337,16 @@ glmrt_status_t glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async(const uint16_t*
                                                                  size_t rows, size_t row_width,
                                                                  size_t dst_row_stride_bytes,
                                                                  void* cuda_stream);
+/* The same encoding from float32 accumulator rows picked through row_indices (the response pack,
+ * glmrt_native.h:766-771, kernel residual.cu:160-196). */
+glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled(const float* src,
+                                                                 const uint32_t* row_indices,
+                                                                 uint8_t* dst, size_t rows,
+                                                                 size_t row_width,
+                                                                 size_t dst_row_stride_bytes);
+glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_async(
+    const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
+    size_t dst_row_stride_bytes, void* cuda_stream);
 /* out = bf16(residual + bf16(shared_delta + bf16(routed_delta_f32))) */
 glmrt_status_t glmrt_cuda_residual_add_shared_f32_delta_bf16(
     const uint16_t* residual, const uint16_t* shared_delta, const float* routed_delta_f32,

@@ -459,6 +459,13 @@ def test_bf16_rows_to_fp8_row_scaled_matches_oracle(lib):
     assert want[1, W:].view(np.float32)[0] == 1.0
     assert lib.call_status("glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async", ptr(src), ptr(dst), C.c_size_t(R),
                            C.c_size_t(W), C.c_size_t(W + 2), stream()) == 1
+    # the response pack: float32 rows picked through an index list (residual.cu:160-196)
+    table = torch.from_numpy(O.bf16_to_f32(bits)).cuda()
+    pick = np.array([6, 1, 1, 3], np.uint32)
+    dst2 = torch.zeros((4, W + 4), dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled", ptr(table), ptr(torch.from_numpy(pick.view(np.int32)).cuda()),
+             ptr(dst2), C.c_size_t(4), C.c_size_t(W), C.c_size_t(W + 4))
+    np.testing.assert_array_equal(dst2.cpu().numpy(), want[pick.astype(np.int64)])
 
 
 def test_infra_alloc_copy_events(lib, pkg):
