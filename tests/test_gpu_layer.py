@@ -276,6 +276,40 @@ def test_decode_kernels_with_many_rows_per_expert(pkg, small_layer, T):
     layer.close()
 
 
+def test_forward_argument_edges(pkg, small_layer):
+    """Empty and oversized batches, buffers that are too small or misaligned are refused before
+    any launch (the reference's ABI rule: validate, then launch; native/include/glmrt_native.h:
+    77-82); a batch of exactly max_tokens rows and a single row both run."""
+    import ctypes as C
+    from glmrt_b200 import native as N
+    K, H = 4, 512
+    layer = make(pkg, small_layer, K, 40, "tc")
+    full = to_dev(O.make_hidden(1, 40, H))
+    out = layer.forward(full)
+    layer.check()
+    assert torch.isfinite(out.float()).all()
+    one = layer.forward(full[:1].contiguous())
+    assert torch.equal(one[0].view(torch.int16), out[0].view(torch.int16))     # batch invariance at the edges
+    none = N.DeviceBuffer.null()
+    buf = lambda t, nbytes=None: N.DeviceBuffer.of(t.data_ptr(), t.numel() * t.element_size() if nbytes is None else nbytes)
+    big = to_dev(O.make_hidden(2, 41, H))
+    o41 = torch.empty_like(big)
+    st = lambda rows, x, o: layer.lib.call_status("glmrt_b200_moe_layer_forward_async", layer.handle, x, C.c_size_t(rows), o,
+                                                  none, none, None)
+    assert st(0, buf(full), buf(out)) == 1                                    # empty
+    assert st(41, buf(big), buf(o41)) == 1                                    # more than max_tokens
+    assert "max_tokens" in layer.lib.last_error()
+    assert st(40, buf(full, 40 * H * 2 - 2), buf(out)) == 2                   # hidden buffer too small
+    assert st(40, buf(full), buf(out, 16)) == 2                               # output buffer too small
+    odd = N.DeviceBuffer.of(full.data_ptr() + 2, 39 * H * 2)
+    assert st(39, odd, buf(out)) == 1                                         # not 16-byte aligned
+    assert st(40, none, buf(out)) in (1, 2)
+    layer.check()                                                             # nothing ran, nothing broke
+    again = layer.forward(full)
+    assert torch.equal(again.view(torch.int16), out.view(torch.int16))
+    layer.close()
+
+
 def test_bad_routes_are_reported_not_faulted(pkg, small_layer):
     from glmrt_b200.native import GlmrtError
     K, T = 4, 4
