@@ -41,16 +41,19 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
                              size_t rows, size_t hidden_dim, size_t experts, size_t top_k, float scaling,
                              cudaStream_t stream);
 
+// splits in 2..8: `logits` holds that many partial tables [splits][rows][experts], added in order
 glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
                                     float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
-                                    cudaStream_t stream);
+                                    cudaStream_t stream, int splits = 1);
 // ---- router_tc.cu (prefill-sized batches) ----
 glmrt_status_t launch_split_router_weight(const float* w, uint16_t* w3, size_t experts, size_t hidden,
                                           cudaStream_t stream);
 bool router_tc_supported(size_t rows, size_t hidden, size_t experts, const void* x);
+int router_tc_splits(size_t rows, size_t hidden, size_t experts, int sm_count);
+// splits > 1 writes partial tables [splits][rows][experts] for launch_router_select to add up
 glmrt_status_t launch_router_logits_tc(const uint16_t* x, const CUtensorMap& map_w3, float* logits, size_t rows,
                                        size_t hidden, size_t experts, uint32_t* error_word, int sm_count,
-                                       cudaStream_t stream);
+                                       cudaStream_t stream, int splits = 1);
 
 // ---- quant.cu ----
 glmrt_status_t launch_quantize_rows_payload(const uint16_t* in, uint8_t* payload, size_t rows, size_t cols,

@@ -32,6 +32,8 @@ struct Layer {
   uint16_t* router_w3 = nullptr;   // [experts, 3 * hidden] bf16 split of router_w for the tensor-core router
   CUtensorMap map_w3{};
   bool have_w3 = false;
+  float* logits_partial = nullptr;  // [splits][rows][experts] partial logits (tensor-core router, rows below one wave of tiles)
+  size_t logits_partial_floats = 0;
   // work buffers
   float *logits = nullptr, *topk_w = nullptr, *topk_scores = nullptr;
   uint32_t* topk_idx = nullptr;
@@ -169,11 +171,14 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
 glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_t s) {
   const auto& c = l->cfg;
   if (l->have_w3 && router_tc_supported(rows, c.hidden_dim, c.experts, hidden)) {
-    GLMRT_RETURN_IF_ERROR(launch_router_logits_tc(static_cast<const uint16_t*>(hidden), l->map_w3, l->logits, rows,
+    int splits = router_tc_splits(rows, c.hidden_dim, c.experts, l->sm_count);
+    if (static_cast<size_t>(splits) * rows * c.experts > l->logits_partial_floats) splits = 1;
+    float* table = splits > 1 ? l->logits_partial : l->logits;
+    GLMRT_RETURN_IF_ERROR(launch_router_logits_tc(static_cast<const uint16_t*>(hidden), l->map_w3, table, rows,
                                                   c.hidden_dim, c.experts, l->counters + kCntRouterError,
-                                                  l->sm_count, s));
-    return launch_router_select(l->logits, l->router_b, l->topk_idx, l->topk_scores, l->topk_w, rows, c.experts,
-                                c.top_k, c.routed_scaling, s);
+                                                  l->sm_count, s, splits));
+    return launch_router_select(table, l->router_b, l->topk_idx, l->topk_scores, l->topk_w, rows, c.experts,
+                                c.top_k, c.routed_scaling, s, splits);
   }
   return launch_router(hidden, true, l->router_w, false, l->router_b, l->logits, l->topk_idx, l->topk_scores,
                        l->topk_w, rows, c.hidden_dim, c.experts, c.top_k, c.routed_scaling, s);
@@ -356,6 +361,20 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_dev
     GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&l->map_w3, l->router_w3, l->cfg.experts,
                                                 static_cast<uint64_t>(l->cfg.hidden_dim) * 3 * 2, 128));
     l->have_w3 = true;
+    if (l->logits_partial == nullptr && l->cfg.max_tokens > 128) {
+      // largest splits * rows over the batch sizes this layer can see (splits * tiles <= SM count)
+      size_t need = 0;
+      for (size_t rows = 129; rows <= l->cfg.max_tokens; rows += 128) {
+        const size_t r = std::min<size_t>(rows + 127, l->cfg.max_tokens);
+        const int sp = router_tc_splits(r, l->cfg.hidden_dim, l->cfg.experts, l->sm_count);
+        if (sp > 1) need = std::max(need, static_cast<size_t>(sp) * r * l->cfg.experts);
+      }
+      if (need != 0) {
+        glmrt_status_t st = dev_alloc(l, &l->logits_partial, need);
+        if (st != GLMRT_STATUS_OK) return st;
+        l->logits_partial_floats = need;
+      }
+    }
   }
   return ok();
 }

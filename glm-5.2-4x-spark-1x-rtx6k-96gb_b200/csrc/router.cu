@@ -184,7 +184,7 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
                                      float* __restrict__ topk_weights, int rows, int experts, int top_k,
-                                     float scaling) {
+                                     float scaling, int splits) {
   extern __shared__ float smem[];
   const int warps = blockDim.x / 32;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -193,7 +193,19 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   float* sel = smem + static_cast<size_t>(warp) * 2 * experts;
   float* raw = sel + experts;
   for (int e = lane; e < experts; e += 32) {
-    const float s = sigmoid_f32(logits[static_cast<size_t>(row) * experts + e]);
+    // a logit may arrive as `splits` partial sums (tensor-core router below one wave of tiles): added in order
+    const float* part = logits + static_cast<size_t>(row) * experts + e;
+    float logit = part[0];
+    if (splits > 1) {
+      const size_t stride = static_cast<size_t>(rows) * experts;
+      float v[7];
+#pragma unroll
+      for (int j = 0; j < 7; ++j) v[j] = j + 1 < splits ? part[(j + 1) * stride] : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 7; ++j)
+        if (j + 1 < splits) logit = __fadd_rn(logit, v[j]);
+    }
+    const float s = sigmoid_f32(logit);
     const bool fin = isfinite(s);
     const float score = fin ? s : 0.0f;
     const float corrected = score + bias[e];
@@ -296,12 +308,12 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
 
 glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
                                     float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, int splits) {
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * 2 * experts * sizeof(float);
   router_select_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, smem, stream>>>(
       logits, bias, idx, scores, weights, static_cast<int>(rows), static_cast<int>(experts),
-      static_cast<int>(top_k), scaling);
+      static_cast<int>(top_k), scaling, splits);
   GLMRT_LAUNCH_CHECK("router_select_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -8,6 +8,10 @@
 // kind::f16 UMMA over the concatenated reduction dimension [hi | mid | lo] accumulates the same
 // exact products as the float32 reference, only in another order.
 //
+// Batches of a few hundred to a few thousand rows have fewer output tiles than the GPU has SMs, so
+// the reduction dimension is cut into 2, 4 or 8 equal ranges: one CTA per (tile, range) writes a
+// partial tile and the selection kernel adds the partials of a logit in range order.
+//
 // Tile = 128 rows x 128 experts, K stage = 64 elements (128-byte swizzled rows for both operands),
 // accumulators double-buffered in tensor memory, epilogue = one thread per row writing 512
 // contiguous bytes of logits.  Roles, bounded waits and teardown as in the expert GEMM kernels.
@@ -74,7 +78,8 @@ __global__ void __launch_bounds__(256) split_weight_kernel(const float* __restri
 
 __global__ void __launch_bounds__(kThreadsTC, 1)
 router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                        float* __restrict__ logits, int rows, int hidden, int experts, uint32_t* error_word) {
+                        float* __restrict__ logits, int rows, int hidden, int experts, int splits,
+                        uint32_t* error_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kRtStages) * kRtStageBytes);
@@ -88,10 +93,11 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   const int x_stages = hidden / 64;            // 64-element steps over one copy of X
-  const int k_stages = 3 * x_stages;           // [hi | mid | lo]
+  const int k_stages = 3 * x_stages / splits;  // [hi | mid | lo], this work item's share of it
   const int n_tiles = experts / 128;
   const int m_tiles = (rows + 127) / 128;
-  const int num_tiles = m_tiles * n_tiles;
+  const int num_tiles = m_tiles * n_tiles * splits;   // work item -> (row tile, expert tile, K range), K range fastest
+  const size_t split_stride = static_cast<size_t>(rows) * experts;
 
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0 && error_word != nullptr) *error_word = 0u;   // any expiry comes seconds later
@@ -119,14 +125,16 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-      const int mt = tile / n_tiles, nt = tile % n_tiles;
+      const int sp = tile % splits, mn = tile / splits;
+      const int mt = mn / n_tiles, nt = mn % n_tiles;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
         if (elect_one()) {
           const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * kRtStageBytes);
+          const int kg = sp * k_stages + ks;   // step in the concatenated reduction dimension
           mbar_expect_tx(&full_bar[stage], kRtStageBytes);
-          tma_load_2d(s_a, &map_x, &full_bar[stage], (ks % x_stages) * 128, mt * 128, pol);
-          tma_load_2d(s_a + kRtTile, &map_w, &full_bar[stage], ks * 128, nt * 128, pol);
+          tma_load_2d(s_a, &map_x, &full_bar[stage], (kg % x_stages) * 128, mt * 128, pol);
+          tma_load_2d(s_a + kRtTile, &map_w, &full_bar[stage], kg * 128, nt * 128, pol);
         }
         __syncwarp();
         if (++stage == kRtStages) { stage = 0; phase ^= 1u; }
@@ -170,7 +178,8 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
     uint32_t aphase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-      const int mt = tile / n_tiles, nt = tile % n_tiles;
+      const int sp = tile % splits, mn = tile / splits;
+      const int mt = mn / n_tiles, nt = mn % n_tiles;
       const int row = mt * 128 + quad * 32 + lane;
       if (!mbar_wait_warp(&acc_full[abuf], aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
@@ -181,7 +190,8 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
         tc_load32(t_acc + c0, v);
         tc_wait_ld();
         if (row < rows) {
-          uint4* dst = reinterpret_cast<uint4*>(logits + static_cast<size_t>(row) * experts + nt * 128 + c0);
+          uint4* dst = reinterpret_cast<uint4*>(logits + sp * split_stride + static_cast<size_t>(row) * experts +
+                                                nt * 128 + c0);
 #pragma unroll
           for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
@@ -220,16 +230,27 @@ bool router_tc_supported(size_t rows, size_t hidden, size_t experts, const void*
          reinterpret_cast<uintptr_t>(x) % 16 == 0;
 }
 
+// K ranges for a batch: the largest of 8, 4, 2, 1 that divides the reduction steps and keeps the
+// number of work items within the SM count.
+int router_tc_splits(size_t rows, size_t hidden, size_t experts, int sm_count) {
+  const size_t tiles = ((rows + 127) / 128) * (experts / 128);
+  const size_t steps = 3 * hidden / 64;
+  for (int s = 8; s > 1; s >>= 1)
+    if (steps % s == 0 && tiles * s <= static_cast<size_t>(sm_count)) return s;
+  return 1;
+}
+
 glmrt_status_t launch_router_logits_tc(const uint16_t* x, const CUtensorMap& map_w3, float* logits, size_t rows,
                                        size_t hidden, size_t experts, uint32_t* error_word, int sm_count,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, int splits) {
   CUtensorMap map_x;
   GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&map_x, x, rows, hidden * 2, 128));
   static std::atomic<uint64_t> configured{0};
   GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, router_logits_tc_kernel, kRtSmemBytes, "cudaFuncSetAttribute(router_logits_tc_kernel)"));
-  const int tiles = static_cast<int>(((rows + 127) / 128) * (experts / 128));
+  const int tiles = static_cast<int>(((rows + 127) / 128) * (experts / 128)) * splits;
   router_logits_tc_kernel<<<std::min(sm_count, tiles), kThreadsTC, kRtSmemBytes, stream>>>(
-      map_x, map_w3, logits, static_cast<int>(rows), static_cast<int>(hidden), static_cast<int>(experts), error_word);
+      map_x, map_w3, logits, static_cast<int>(rows), static_cast<int>(hidden), static_cast<int>(experts), splits,
+      error_word);
   GLMRT_LAUNCH_CHECK("router_logits_tc_kernel");
   return GLMRT_STATUS_OK;
 }
