@@ -723,11 +723,14 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       if (rows > 0)
         GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s));
       mark(l, GLMRT_B200_STAGE_QUANTIZE, s);
+      // the histogram only needs the routes: it goes out to the peers first and travels while the
+      // rows are quantised
+      GLMRT_RETURN_IF_ERROR(launch_ep_count(a, l->topk_idx, routes, s));
       if (rows > 0)
         GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
                                                            GLMRT_B200_FP4_RULE_NEAREST_LOW, s));
       mark(l, GLMRT_B200_STAGE_PLAN, s);
-      return launch_ep_count(a, l->topk_idx, routes, s);
+      return GLMRT_STATUS_OK;
     }
     case 1: {
       PlanArgs p{};
