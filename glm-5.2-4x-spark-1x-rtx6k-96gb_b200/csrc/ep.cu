@@ -165,8 +165,11 @@ ep_dispatch_kernel(EpArgs a, const uint8_t* payload, const uint32_t* topk_indice
       const uint4* src4 = reinterpret_cast<const uint4*>(src);
       uint4* dst4 = reinterpret_cast<uint4*>(a.peer_act_codes[owner] + static_cast<size_t>(slot) * code_bytes);
       for (int i = lane; i < code_bytes / 16; i += 32) dst4[i] = src4[i];
+      // scales leave as 4-byte words: four consecutive blocks of a slot are contiguous in the tiled layout
       uint8_t* sf = a.peer_act_sf[owner];
-      for (int j = lane; j < kblocks; j += 32) sf[sf_tile_offset(slot, j, kblocks)] = src[code_bytes + j];
+      const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(src + code_bytes);
+      for (int j = lane; j < kblocks / 4; j += 32)
+        *reinterpret_cast<uint32_t*>(sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
       if (lane == 0) {
         a.peer_slot_out[owner][slot] = a.my_rows_in_peer[owner] + static_cast<size_t>(warp) * hidden;
         route_slot[warp] = slot;
