@@ -98,6 +98,34 @@ quantize_rows_payload_kernel(const uint16_t* __restrict__ in, uint8_t* __restric
   prow[cols / 2 + blk] = static_cast<uint8_t>(sbyte);
 }
 
+// float32 accumulator rows picked through row_indices -> NVFP4 wire rows at a caller row stride
+// (the response pack; native/cuda/kernels/nvfp4_payload.cu:75-115 runs a 32-thread CTA per block
+// of 16, here a thread owns a block: 64 B read as four 16-byte loads, 8 B + 1 B written).
+__global__ void __launch_bounds__(kThreads)
+gather_f32_rows_payload_kernel(const float* __restrict__ in, const uint32_t* __restrict__ row_indices,
+                               uint8_t* __restrict__ payload, size_t rows, size_t cols, size_t stride_bytes) {
+  const size_t blocks_per_row = cols / 16;
+  const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
+  if (gid >= rows * blocks_per_row) return;
+  const size_t row = gid / blocks_per_row, blk = gid % blocks_per_row;
+  const float4* src = reinterpret_cast<const float4*>(in + static_cast<size_t>(row_indices[row]) * cols + blk * 16);
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 q = src[i];
+    v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+  }
+  uint32_t lo, hi, sbyte;
+  quantize_block16<false>(v, lo, hi, sbyte);
+  uint8_t* prow = payload + row * stride_bytes;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {   // the stride is only byte-granular
+    prow[blk * 8 + i] = static_cast<uint8_t>(lo >> (8 * i));
+    prow[blk * 8 + 4 + i] = static_cast<uint8_t>(hi >> (8 * i));
+  }
+  prow[cols / 2 + blk] = static_cast<uint8_t>(sbyte);
+}
+
 // ---- weight quantisers -----------------------------------------------------------------
 // mlp.cu:98-132: scale = e4m3(amax * g / 6); code = cvt.rn.satfinite.e2m1(v * g / scale).
 __global__ void __launch_bounds__(kThreads)
@@ -409,4 +437,33 @@ extern "C" glmrt_status_t glmrt_cuda_b12x_gather_nvfp4_rows_bf16_async(
       static_cast<int>(hidden_dim));
   GLMRT_LAUNCH_CHECK("gather_payload_rows_bf16_kernel");
   return ok();
+}
+
+extern "C" glmrt_status_t glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3_async(
+    const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
+    size_t dst_row_stride_bytes, void* cuda_stream) {
+  if (src == nullptr || row_indices == nullptr || dst == nullptr || rows == 0 || row_width == 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows_f32_to_nvfp4: null pointer or empty shape");
+  if (row_width % 16 != 0 || dst_row_stride_bytes < row_width / 2 + row_width / 16)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT,
+                "gather_rows_f32_to_nvfp4: the width must be a multiple of 16 and the row stride must hold codes and scales");
+  if (reinterpret_cast<uintptr_t>(src) % 16 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows_f32_to_nvfp4: the source must be 16-byte aligned");
+  size_t blocks = 0;
+  if (!checked_mul(rows, row_width / 16, &blocks) || blocks / kThreads + 1 > 0x7fffffffull)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows_f32_to_nvfp4: size overflow");
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  gather_f32_rows_payload_kernel<<<grid_for(blocks), kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      src, row_indices, dst, rows, row_width, dst_row_stride_bytes);
+  GLMRT_LAUNCH_CHECK("gather_f32_rows_payload_kernel");
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3(
+    const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
+    size_t dst_row_stride_bytes) {
+  const glmrt_status_t st = glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3_async(src, row_indices, dst, rows, row_width,
+                                                                                   dst_row_stride_bytes, nullptr);
+  if (st != GLMRT_STATUS_OK) return st;
+  return status_from_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
 }

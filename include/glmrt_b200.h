@@ -347,6 +347,18 @@ glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled(const float* sr
 glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_async(
     const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
     size_t dst_row_stride_bytes, void* cuda_stream);
+/* float32 accumulator rows picked through row_indices -> NVFP4 wire rows [row_width/2 packed E2M1 |
+ * row_width/16 E4M3 scales] at dst_row_stride_bytes (glmrt_native.h:787-792, kernel
+ * nvfp4_payload.cu:75-115): scale = e4m3(amax/6), codes of clamp(x * (1/scale), -6, 6) with the
+ * round-to-nearest-even thresholds.  src must be 16-byte aligned. */
+glmrt_status_t glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3(const float* src,
+                                                                 const uint32_t* row_indices,
+                                                                 uint8_t* dst, size_t rows,
+                                                                 size_t row_width,
+                                                                 size_t dst_row_stride_bytes);
+glmrt_status_t glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3_async(
+    const float* src, const uint32_t* row_indices, uint8_t* dst, size_t rows, size_t row_width,
+    size_t dst_row_stride_bytes, void* cuda_stream);
 /* out = bf16(residual + bf16(shared_delta + bf16(routed_delta_f32))) */
 glmrt_status_t glmrt_cuda_residual_add_shared_f32_delta_bf16(
     const uint16_t* residual, const uint16_t* shared_delta, const float* routed_delta_f32,

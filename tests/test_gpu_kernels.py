@@ -468,6 +468,40 @@ def test_bf16_rows_to_fp8_row_scaled_matches_oracle(lib):
     np.testing.assert_array_equal(dst2.cpu().numpy(), want[pick.astype(np.int64)])
 
 
+def test_gather_rows_f32_to_nvfp4_wire_rows(lib):
+    """The response pack to NVFP4 wire rows (nvfp4_payload.cu:75-115): float32 accumulator rows picked through
+    an index list, scale e4m3(amax/6), codes of clamp(x * (1/scale), -6, 6); bytes past the row are not touched."""
+    rng = np.random.default_rng(15)
+    R, W = 9, 6144
+    x = rng.standard_normal((R, W), np.float32) * np.float32(2.0)
+    x[1] = 0.0
+    x[2] *= np.float32(1e-7)                              # scales that round to zero
+    x[3] *= np.float32(1e4)                               # saturating scales
+    x[4, :16] = np.array([0.25, -0.25, 0.75, -0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -5.0, 6.0, -6.0, -0.0, 0.0, 3.0, -3.0],
+                         np.float32)                      # every tie of the code rule at scale 1
+    pick = np.array([8, 4, 4, 0, 1, 2, 3], np.uint32)
+    n = len(pick)
+    stride = W // 2 + W // 16 + 5
+    dst = torch.full((n, stride), 0xAB, dtype=torch.uint8, device="cuda")
+    table = torch.from_numpy(x).cuda()
+    idx = torch.from_numpy(pick.view(np.int32)).cuda()
+    lib.call("glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3_async", ptr(table), ptr(idx), ptr(dst), C.c_size_t(n),
+             C.c_size_t(W), C.c_size_t(stride), stream())
+    torch.cuda.synchronize()
+    codes, sb = O.quantize_rows_nvfp4(x[pick.astype(np.int64)], rule="rne_payload")
+    want = O.payload_rows(codes, sb)
+    got = dst.cpu().numpy()
+    np.testing.assert_array_equal(got[:, :W // 2 + W // 16], want)
+    assert (got[:, W // 2 + W // 16:] == 0xAB).all()
+    dst2 = torch.zeros((n, W // 2 + W // 16), dtype=torch.uint8, device="cuda")
+    lib.call("glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3", ptr(table), ptr(idx), ptr(dst2), C.c_size_t(n), C.c_size_t(W),
+             C.c_size_t(W // 2 + W // 16))
+    np.testing.assert_array_equal(dst2.cpu().numpy(), want)
+    for width, st in ((W + 8, stride), (W, W // 2), (0, stride)):
+        assert lib.call_status("glmrt_cuda_gather_rows_f32_to_nvfp4_e2m1_fp8_e4m3_async", ptr(table), ptr(idx), ptr(dst),
+                               C.c_size_t(n), C.c_size_t(width), C.c_size_t(st), stream()) == 1
+
+
 def test_infra_alloc_copy_events(lib, pkg):
     from glmrt_b200 import native as N
     b = N.DeviceBuffer()
