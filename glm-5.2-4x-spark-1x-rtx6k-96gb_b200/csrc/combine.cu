@@ -15,6 +15,17 @@ namespace {
 
 constexpr int kThreads = 256;
 
+__device__ __forceinline__ uint32_t bf16x2_mul_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_add_rn(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // kResidual: the summed routed row is not stored as such but folded into the layer output the way
 // the reference's residual kernel does it (native/cuda/kernels/residual.cu:36-62, truncating bf16
 // stores): mlp = bf16(shared + routed) when a shared-expert row is given, out = bf16(residual + mlp).
@@ -28,13 +39,16 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
   if (gid >= static_cast<size_t>(rows) * vec_per_row) return;
   const int row = static_cast<int>(gid / vec_per_row);
   const int v = static_cast<int>(gid % vec_per_row);
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  // Pairs of bf16 sums.  mul.rn.bf16x2 and add.rn.bf16x2 round the exact product / sum of bf16
+  // operands once to bf16, which is what the float32 operation followed by a round-to-nearest-even
+  // conversion yields: the product of two 8-bit significands is exact in float32, and a float32 sum
+  // of two bf16 values that is not exact differs from the larger operand by less than 2^-15 of it,
+  // nowhere near a bf16 rounding boundary.
+  uint32_t acc2[4] = {0u, 0u, 0u, 0u};
   // rows are fetched eight routes at a time before any arithmetic, so the loads overlap
   for (int k0 = 0; k0 < top_k; k0 += 8) {
     uint4 y4[8];
-    float w[8];
+    uint32_t w2[8];
     bool use[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -43,7 +57,8 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
       use[j] = k < top_k && (route_slot == nullptr || route_slot[r] >= 0);
       if (use[j]) {
         y4[j] = reinterpret_cast<const uint4*>(route_rows + static_cast<size_t>(r) * hidden)[v];
-        w[j] = bf16_bits_to_f32(f32_to_bf16_rne(topk_weights[r]));
+        const uint32_t wb = f32_to_bf16_rne(topk_weights[r]);
+        w2[j] = wb | (wb << 16);
       }
     }
 #pragma unroll
@@ -51,15 +66,14 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
       if (!use[j]) continue;
       const uint32_t yw[4] = {y4[j].x, y4[j].y, y4[j].z, y4[j].w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float y0 = __uint_as_float(yw[i] << 16);
-        const float y1 = __uint_as_float(yw[i] & 0xffff0000u);
-        const float p0 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w[j], y0)));
-        const float p1 = bf16_bits_to_f32(f32_to_bf16_rne(__fmul_rn(w[j], y1)));
-        acc[2 * i] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i], p0)));
-        acc[2 * i + 1] = bf16_bits_to_f32(f32_to_bf16_rne(__fadd_rn(acc[2 * i + 1], p1)));
-      }
+      for (int i = 0; i < 4; ++i) acc2[i] = bf16x2_add_rn(acc2[i], bf16x2_mul_rn(w2[j], yw[i]));
     }
+  }
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] = __uint_as_float(acc2[i] << 16);
+    acc[2 * i + 1] = __uint_as_float(acc2[i] & 0xffff0000u);
   }
   if (kResidual) {
     const size_t off = static_cast<size_t>(row) * hidden;

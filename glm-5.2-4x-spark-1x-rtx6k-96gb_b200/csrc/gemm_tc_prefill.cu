@@ -64,6 +64,43 @@ struct PfCfg {
       static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
 
+// FC2 epilogue of one thread: 128 accumulator columns of its token row leave in two halves: scale,
+// round to bf16, park 128 bytes in the thread's own staging row, then hand them to one asynchronous
+// bulk store.  Each store writes a full 128-byte line of the destination row (local memory or a
+// peer's), instead of 32 lanes scattering 16-byte pieces over 32 rows.  The accumulator is handed
+// back (one arrival per warp) as soon as the second half is in registers.  dst == nullptr: a slot
+// without a token, nothing is stored.
+__device__ __forceinline__ void fc2_emit_128_columns(uint32_t t_acc, float s2, uint16_t* dst, uint8_t* mine, int lane,
+                                                     uint64_t* acc_empty_bar) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t y[4][16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) tc_load16(t_acc + half * 64 + q * 16, y[q]);
+    tc_wait_ld();
+    if (half == 1) {   // everything is in registers: hand the accumulator back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar);
+    }
+    bulk_store_wait_read();   // the previous store has finished reading the staging row
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2))) |
+               (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2))) << 16);
+      uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
+      s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    fence_async_smem();
+    if (dst != nullptr) bulk_store(dst + half * 64, smem_u32(mine), 128);
+    bulk_store_commit();
+  }
+}
+
 template <bool kFC1, int kWN>
 __global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
 expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act,
@@ -271,40 +308,9 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           }
         }
       } else {
-        // The thread's 128 columns leave in two halves: scale, round to bf16, park 128 bytes in
-        // the thread's own staging row, then hand them to one asynchronous bulk store.  Each store
-        // writes a full 128-byte line of the destination row (local memory or a peer's), instead of
-        // 32 lanes scattering 16-byte pieces over 32 rows.
-        constexpr int kColsPerPart = kWN / C::kParts;   // 128
         uint8_t* mine = out_stage + (static_cast<size_t>(warp - 2) * 32 + lane) * C::kOutPitch;
-#pragma unroll
-        for (int half = 0; half < kColsPerPart / 64; ++half) {
-          const int c0 = part * kColsPerPart + half * 64;
-          uint32_t y[4][16];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) tc_load16(t_acc + c0 + q * 16, y[q]);
-          tc_wait_ld();
-          if (half == kColsPerPart / 64 - 1) {   // everything is in registers: hand the accumulator back
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[abuf]);
-          }
-          bulk_store_wait_read();   // the previous store has finished reading the staging row
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2a))) |
-                     (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2a))) << 16);
-            uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
-            s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          }
-          fence_async_smem();
-          if (valid) bulk_store(dst + ft * C::kFeatPerTile + c0, smem_u32(mine), 128);
-          bulk_store_commit();
-        }
+        fc2_emit_128_columns(t_acc + part * 128, s2a, valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr, mine, lane,
+                             &acc_empty[abuf]);
       }
       if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }

@@ -144,18 +144,46 @@ __global__ void __launch_bounds__(kPlanBlock) plan_count_kernel(PlanArgs a, int 
     a.block_hist[static_cast<size_t>(blockIdx.x) * local_experts + i] = hist[i];
 }
 // scan: per expert, exclusive prefix over the blocks; then one warp turns the totals into slot
-// bases and the chunk list
+// bases and the chunk list.  The blocks of an expert are cut into segments, one thread each
+// (neighbouring threads hold neighbouring experts, so every access is a full line); values are
+// fetched eight at a time before anything is stored, so the loads do not queue behind the stores.
 __global__ void __launch_bounds__(1024) plan_scan_kernel(PlanArgs a, int local_experts, int blocks) {
-  for (int le = threadIdx.x; le < local_experts; le += 1024) {
-    int running = 0;
-#pragma unroll 8
-    for (int b = 0; b < blocks; ++b) {
-      const size_t i = static_cast<size_t>(b) * local_experts + le;
-      const int c = a.block_hist[i];
-      a.block_hist[i] = running;
-      running += c;
+  __shared__ int seg_sum[1024];
+  const int segs = local_experts <= 1024 ? min(32, 1024 / local_experts) : 1;
+  const int per_seg = (blocks + segs - 1) / segs;
+  for (int le0 = 0; le0 < local_experts; le0 += 1024) {   // one pass unless there are more than 1024 experts
+    const int seg = segs > 1 ? threadIdx.x / local_experts : 0;
+    const int le = segs > 1 ? threadIdx.x % local_experts : le0 + threadIdx.x;
+    const bool active = seg < segs && le < local_experts;
+    const int b0 = min(blocks, seg * per_seg), b1 = min(blocks, b0 + per_seg);
+    int sum = 0;
+    if (active) {
+      for (int b = b0; b < b1; b += 8) {
+        int c[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c[j] = b + j < b1 ? a.block_hist[static_cast<size_t>(b + j) * local_experts + le] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += c[j];
+      }
     }
-    a.expert_counts[le] = running;
+    __syncthreads();   // the previous pass has read seg_sum
+    seg_sum[threadIdx.x] = sum;
+    __syncthreads();
+    if (active) {
+      int running = 0;
+      for (int s2 = 0; s2 < seg; ++s2) running += seg_sum[s2 * local_experts + le];
+      if (seg == segs - 1) a.expert_counts[le] = running + sum;
+      for (int b = b0; b < b1; b += 8) {
+        int c[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c[j] = b + j < b1 ? a.block_hist[static_cast<size_t>(b + j) * local_experts + le] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (b + j < b1) a.block_hist[static_cast<size_t>(b + j) * local_experts + le] = running;
+          running += c[j];
+        }
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x >= 32) return;
