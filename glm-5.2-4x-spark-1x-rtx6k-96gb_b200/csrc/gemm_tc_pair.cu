@@ -1,7 +1,7 @@
 // Expert GEMMs of large prefill batches on CTA pairs (tcgen05 cta_group::2).
 //
 // FC2 instance: the pair's B tile is 256 down rows (128 per CTA), each CTA's accumulator is 128
-// slots x 256 features and leaves as 128-byte bulk stores like the one-CTA FC2 kernel's.
+// slots x 256 features and leaves as whole row pieces like the one-CTA FC2 kernel's (fc2_store.cuh).
 //
 // FC1: same computation as the FC1 instance of gemm_tc_prefill.cu (the reference's fused-MoE FC1 stage,
 // native/cuda/kernels/b12x_direct.cu:479-508, and SIMT gate/up MLP, mlp.cu:218-273), for experts
@@ -31,6 +31,7 @@
 
 #include "common.cuh"
 #include "epilogue.cuh"
+#include "fc2_store.cuh"
 #include "internal.h"
 #include "tc_ptx.cuh"
 
@@ -55,8 +56,7 @@ struct PairCfg {
   static constexpr int kEpiWarps = kFC1 ? 16 : 8;
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kChunkCache = 256;
-  static constexpr int kOutPitch = 144;                   // FC2: 128 staging bytes per thread, conflict-free pitch
-  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * 32 * kOutPitch;
+  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * Fc2Stage<128>::kBytesPerWarp;   // FC2: a 32 x 128 staging tile per warp
   static constexpr size_t kSmemBytes =
       static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
@@ -256,45 +256,16 @@ expert_pair_kernel(FfnArgs a, const __grid_constant__ PairMaps maps) {
           }
         }
       } else {
-        // 128 columns per thread in two halves: scale, round to bf16, park 128 bytes in the thread's
-        // own staging row, send them with one bulk store (a full line of the destination row)
-        uint8_t* mine = out_stage + (static_cast<size_t>(warp - 2) * 32 + lane) * C::kOutPitch;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int c0 = part * 128 + half * 64;
-          uint32_t y[4][16];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) tc_load16(t_acc + c0 + q * 16, y[q]);
-          tc_wait_ld();
-          if (half == 1) {   // everything is in registers: hand the accumulator back
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
-          }
-          bulk_store_wait_read();   // the previous store has finished reading the staging row
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2g))) |
-                     (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2g))) << 16);
-            uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
-            s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          }
-          fence_async_smem();
-          if (valid) bulk_store(dst + ft * C::kFeatPerTile + c0, smem_u32(mine), 128);
-          bulk_store_commit();
-        }
+        // this warp's 128 of the CTA's 256 columns leave as whole rows through its staging tile
+        fc2_emit_128_columns<128>(t_acc + part * 128, s2g, valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr,
+                             out_stage + static_cast<size_t>(warp - 2) * Fc2Stage<128>::kBytesPerWarp, lane,
+                             [&] { mbar_arrive_cluster(lead_acc_empty); });
       }
       aphase ^= 1u;
     }
   }
 
   // ---- teardown ----
-  if (!kFC1 && warp >= 2) bulk_store_wait_all();
-  __syncwarp();
   if (*abort_flag != 0u) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
     if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(kErrWaitTimeout));

@@ -13,9 +13,8 @@
 //   FC2  B = 128 down rows, accumulators double-buffered in tensor memory: its K loop is only eight
 //        stages long, so an epilogue that held the single buffer of a 256-column tile drained the
 //        pipeline at every tile (measured at T = 8192: 1.08 ms with N = 256, 0.86 ms with N = 128).
-//        The epilogue thread scales, rounds to bf16, parks 128 bytes of its token's row in shared
-//        memory and sends them with one asynchronous bulk store: full 128-byte lines to local or
-//        peer memory instead of 32 lanes scattering 16-byte pieces over 32 rows.
+//        The epilogue warp scales, rounds to bf16, parks its 32 rows x 128 columns in shared memory
+//        and writes them out as whole 256-byte row pieces (fc2_store.cuh).
 //
 // FC1 uses N = 256: half the scale copies and fewer bytes brought into shared memory per unit of
 // math than N = 128 (measured: FC1 1.63 -> 1.33 ms at T = 8192); its 48-stage K loop hides the one
@@ -26,6 +25,7 @@
 
 #include "common.cuh"
 #include "epilogue.cuh"
+#include "fc2_store.cuh"
 #include "internal.h"
 #include "tc_ptx.cuh"
 
@@ -56,50 +56,11 @@ struct PfCfg {
   static constexpr int kParts = kEpiWarps / 4;
   static constexpr int kThreads = 32 * (2 + kEpiWarps);
   static constexpr int kChunkCache = 256;
-  // FC2 epilogue: each thread owns 128 staging bytes (64 bf16 of its row); the 144-byte pitch keeps
-  // the 16-byte shared stores of a quarter warp on distinct banks
-  static constexpr int kOutPitch = 144;
-  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * 32 * kOutPitch;
+  // FC2 epilogue: every warp parks its 32 rows x 128 columns before they leave as whole rows
+  static constexpr int kOutBytes = kFC1 ? 0 : kEpiWarps * Fc2Stage<128>::kBytesPerWarp;
   static constexpr size_t kSmemBytes =
       static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
-
-// FC2 epilogue of one thread: 128 accumulator columns of its token row leave in two halves: scale,
-// round to bf16, park 128 bytes in the thread's own staging row, then hand them to one asynchronous
-// bulk store.  Each store writes a full 128-byte line of the destination row (local memory or a
-// peer's), instead of 32 lanes scattering 16-byte pieces over 32 rows.  The accumulator is handed
-// back (one arrival per warp) as soon as the second half is in registers.  dst == nullptr: a slot
-// without a token, nothing is stored.
-__device__ __forceinline__ void fc2_emit_128_columns(uint32_t t_acc, float s2, uint16_t* dst, uint8_t* mine, int lane,
-                                                     uint64_t* acc_empty_bar) {
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t y[4][16];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) tc_load16(t_acc + half * 64 + q * 16, y[q]);
-    tc_wait_ld();
-    if (half == 1) {   // everything is in registers: hand the accumulator back
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar);
-    }
-    bulk_store_wait_read();   // the previous store has finished reading the staging row
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t w[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        w[i] = static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i]), s2))) |
-               (static_cast<uint32_t>(f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2))) << 16);
-      uint4* s4 = reinterpret_cast<uint4*>(mine + q * 32);
-      s4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      s4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    }
-    fence_async_smem();
-    if (dst != nullptr) bulk_store(dst + half * 64, smem_u32(mine), 128);
-    bulk_store_commit();
-  }
-}
 
 template <bool kFC1, int kWN>
 __global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
@@ -308,17 +269,15 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           }
         }
       } else {
-        uint8_t* mine = out_stage + (static_cast<size_t>(warp - 2) * 32 + lane) * C::kOutPitch;
-        fc2_emit_128_columns(t_acc + part * 128, s2a, valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr, mine, lane,
-                             &acc_empty[abuf]);
+        fc2_emit_128_columns<128>(t_acc + part * 128, s2a, valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr,
+                             out_stage + static_cast<size_t>(warp - 2) * Fc2Stage<128>::kBytesPerWarp, lane,
+                             [&] { mbar_arrive(&acc_empty[abuf]); });
       }
       if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }
   }
 
   // ---- teardown ----
-  if (!kFC1 && warp >= 2) bulk_store_wait_all();
-  __syncwarp();
   if (*abort_flag != 0u) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
     if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(kErrWaitTimeout));
