@@ -269,15 +269,22 @@ quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
   uint4* prow = reinterpret_cast<uint4*>(a.payload_out + static_cast<size_t>(row) * (code_bytes + kblocks));
   for (int i = threadIdx.x; i < row_vecs; i += kFusedThreads) prow[i] = row_img[i];
   const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(img + code_bytes);
-  for (int k = 0; k < a.top_k; ++k) {
-    const int route = row * a.top_k + k;
-    const int slot = a.route_slot[route];
-    if (slot < 0) continue;   // route of an expert that lives on another shard
-    uint4* dst4 = reinterpret_cast<uint4*>(a.act_codes + static_cast<size_t>(slot) * code_bytes);
-    for (int i = threadIdx.x; i < code_bytes / 16; i += kFusedThreads) dst4[i] = row_img[i];
-    for (int j = threadIdx.x; j < kblocks / 4; j += kFusedThreads)
-      *reinterpret_cast<uint32_t*>(a.act_sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
-    if (threadIdx.x == 0) a.slot_out[slot] = a.route_rows + static_cast<size_t>(route) * a.hidden;
+  // the slots of up to eight routes are fetched together: one load latency instead of one per route
+  for (int k0 = 0; k0 < a.top_k; k0 += 8) {
+    int slots[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) slots[j] = k0 + j < a.top_k ? a.route_slot[row * a.top_k + k0 + j] : -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int slot = slots[j];
+      if (slot < 0) continue;   // route of an expert that lives on another shard, or no route
+      const int route = row * a.top_k + k0 + j;
+      uint4* dst4 = reinterpret_cast<uint4*>(a.act_codes + static_cast<size_t>(slot) * code_bytes);
+      for (int i = threadIdx.x; i < code_bytes / 16; i += kFusedThreads) dst4[i] = row_img[i];
+      for (int w = threadIdx.x; w < kblocks / 4; w += kFusedThreads)
+        *reinterpret_cast<uint32_t*>(a.act_sf + sf_tile_offset(slot, 4 * w, kblocks)) = sf_words[w];
+      if (threadIdx.x == 0) a.slot_out[slot] = a.route_rows + static_cast<size_t>(route) * a.hidden;
+    }
   }
 }
 
