@@ -453,9 +453,9 @@ def run_ep(args, dist, rank, world, local_rank):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch from the ncu captures summarised
 # under profiles/, per expert touched: decode kernel (820.55 MB, 57 experts touched) and prefill
-# kernel (1014.57 MB, 64 experts).
+# kernel (1003.59 MB, 64 experts).
 NCU_FC1_TRAFFIC_PER_EXPERT = 820.55e6 / 57
-NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT = 1014.57e6 / 64
+NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT = 1003.59e6 / 64
 
 
 def main():
