@@ -496,3 +496,38 @@ def test_tensor_core_router_matches_oracle_at_prefill_sizes(pkg, T):
     np.testing.assert_allclose(w.cpu().numpy()[same], ow[same], atol=3e-6, rtol=1e-5)
     assert torch.isfinite(out.float()).all()
     layer.close()
+
+
+def test_layer_loaded_from_a_checkpoint_matches_the_direct_load(pkg, small_layer, tmp_path):
+    """Sharded safetensors in the checkpoint's layout -> load_moe_layer: the resident weights read back
+    as written and a forward is bit-equal to the same layer set through load_quantized_layer."""
+    import copy
+    from glmrt_b200 import checkpoint as CK
+    from glmrt_b200.layer import MoeLayer
+    from tests.checkpoint_fixture import write_snapshot
+    H, I, E = small_layer.dims
+    K, T = 4, 40
+    stored_router = write_snapshot(str(tmp_path / "snap"), small_layer, layer_id=7, shards=3)
+    cat = CK.TensorCatalog(str(tmp_path / "snap"))
+    layer = MoeLayer(H, I, E, K, max_tokens=64)
+    report = CK.load_moe_layer(layer, cat, 7)
+    assert report.experts_loaded == list(range(E)) and report.weight_bytes == E * 3 * (H * I // 2 + H * I // 16 + 8)
+    for e in (0, E - 1):
+        (gc, gs, g2), (uc, us, u2), (dc, ds, d2) = layer.read_expert(e)
+        np.testing.assert_array_equal(gc, small_layer.gate[e])
+        np.testing.assert_array_equal(us, small_layer.up_s[e])
+        np.testing.assert_array_equal(dc, small_layer.down[e])
+        assert (g2, u2, d2) == tuple(float(v) for v in small_layer.scale2[e])
+    ref = copy.copy(small_layer)
+    ref.router_w = stored_router                       # the checkpoint holds the router weight as bf16
+    direct = make(pkg, ref, K, 64)
+    hid = to_dev(O.make_hidden(4242, T, H))
+    out_a, idx_a, w_a = layer.forward(hid, want_routes=True)
+    out_b, idx_b, w_b = direct.forward(hid, want_routes=True)
+    layer.check(); direct.check()
+    assert torch.equal(idx_a, idx_b) and torch.equal(w_a, w_b) and torch.equal(out_a, out_b)
+    # a rank of a two-way expert-parallel layer takes only its own experts
+    shard = MoeLayer(H, I, E, K, max_tokens=64, ep_world=2, ep_rank=1)
+    assert CK.load_moe_layer(shard, cat, 7).experts_loaded == list(range(1, E, 2))
+    for l in (layer, direct, shard):
+        l.close()
