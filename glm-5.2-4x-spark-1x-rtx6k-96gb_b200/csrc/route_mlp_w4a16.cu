@@ -2,9 +2,11 @@
 // computation of the reference's SIMT kernels behind
 //   glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_grouped_staged_accumulate_f32[_async]
 //   glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32[_async]
-// (native/cuda/kernels/mlp.cu:218-420, declared at native/include/glmrt_native.h:572-597):
+//   glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16[_async]
+// (native/cuda/kernels/mlp.cu:218-518, declared at native/include/glmrt_native.h:572-607):
 //   activation[route, m] = silu(x . gate[m]) * (x . up[m])             float32, staged in a workspace
 //   accumulator[row, o] += route_weight * (activation[route] . down[o]) float32 atomics
+//   single row: out[o] = bf16(sum over the routes of row 0, in route order), truncating, no accumulator
 // with every weight dequantised as codebook[code] * e4m3(scale) * scale_2 (common.h:52-58) and no
 // quantisation of activations: the arithmetic of the Python reference (moe_ref.py:17-21), unlike
 // the layer object's tensor-core path, which is W4A4.  It exists for callers of those symbols and
@@ -115,11 +117,45 @@ w4a16_down_kernel(const uint32_t* __restrict__ row_indices, const float* __restr
   if (lane == 0) atomicAdd(&accumulator[dest * output_dim + out_col], route_weights[route] * acc);   // mlp.cu:310-312
 }
 
+// single row: one warp per output feature walks the routes of row 0 in order (mlp.cu:474-518)
+__global__ void __launch_bounds__(kThreads)
+w4a16_down_single_row_kernel(const uint32_t* __restrict__ row_indices, const float* __restrict__ route_weights,
+                             const glmrt_nvfp4_route_batched_metadata_t* __restrict__ metadata,
+                             const float* __restrict__ activations, uint16_t* __restrict__ out, size_t routes,
+                             size_t max_intermediate, size_t output_dim) {
+  const size_t out_col = blockIdx.x * static_cast<size_t>(kWarps) + threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  if (out_col >= output_dim) return;
+  float total = 0.0f;
+  for (size_t route = 0; route < routes; ++route) {
+    if (row_indices[route] != 0) continue;
+    const ExpertPtrs e = from_metadata(metadata[route]);
+    const uint8_t* w_row = e.down_w + out_col * e.down_w_stride;
+    const uint8_t* s_row = e.down_s + out_col * e.down_s_stride;
+    const float* act = activations + route * max_intermediate;
+    float acc = 0.0f;
+    for (size_t j = lane; j < e.intermediate / 16; j += 32) {
+      const float sc = e4m3_to_f32(s_row[j]);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        const uint32_t wb = w_row[j * 8 + b];
+        acc = fmaf(act[j * 16 + 2 * b], wval(wb & 15u, sc, e.d2), acc);
+        acc = fmaf(act[j * 16 + 2 * b + 1], wval(wb >> 4, sc, e.d2), acc);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    total = fmaf(route_weights[route], acc, total);
+  }
+  if (lane == 0) out[out_col] = f32_to_bf16_trunc(total);
+}
+
 glmrt_status_t run(const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights, const ExpertPtrs& grouped,
                    const glmrt_nvfp4_route_batched_metadata_t* metadata, float* workspace, float* accumulator, size_t rows,
                    size_t routes, size_t hidden_dim, size_t hidden_row_stride, size_t max_intermediate, size_t output_dim,
-                   void* cuda_stream, const char* what) {
-  if (hidden == nullptr || row_indices == nullptr || route_weights == nullptr || workspace == nullptr || accumulator == nullptr)
+                   void* cuda_stream, const char* what, uint16_t* single_row_out = nullptr) {
+  if (hidden == nullptr || row_indices == nullptr || route_weights == nullptr || workspace == nullptr ||
+      (accumulator == nullptr && single_row_out == nullptr))
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, std::string(what) + ": null pointer argument");
   if (rows == 0 || routes == 0 || hidden_dim == 0 || max_intermediate == 0 || output_dim == 0 ||
       hidden_dim % 16 != 0 || max_intermediate % 16 != 0 || hidden_row_stride < hidden_dim)
@@ -134,6 +170,12 @@ glmrt_status_t run(const uint16_t* hidden, const uint32_t* row_indices, const fl
   w4a16_activation_kernel<<<static_cast<unsigned>((n1 + kWarps - 1) / kWarps), kThreads, 0, s>>>(
       hidden, row_indices, grouped, metadata, workspace, rows, routes, hidden_dim, hidden_row_stride, max_intermediate);
   GLMRT_LAUNCH_CHECK("w4a16_activation_kernel");
+  if (single_row_out != nullptr) {
+    w4a16_down_single_row_kernel<<<static_cast<unsigned>((output_dim + kWarps - 1) / kWarps), kThreads, 0, s>>>(
+        row_indices, route_weights, metadata, workspace, single_row_out, routes, max_intermediate, output_dim);
+    GLMRT_LAUNCH_CHECK("w4a16_down_single_row_kernel");
+    return ok();
+  }
   w4a16_down_kernel<<<static_cast<unsigned>((n2 + kWarps - 1) / kWarps), kThreads, 0, s>>>(
       row_indices, route_weights, grouped, metadata, workspace, accumulator, rows, routes, max_intermediate, output_dim);
   GLMRT_LAUNCH_CHECK("w4a16_down_kernel");
@@ -200,5 +242,27 @@ extern "C" glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_sta
     size_t output_dim) {
   return sync_null(glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32_async(
       hidden, row_indices, route_weights, route_metadata, activation_workspace, accumulator, rows, routes, hidden_dim,
+      hidden_row_stride, max_intermediate, output_dim, nullptr));
+}
+
+extern "C" glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16_async(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace, uint16_t* out, size_t rows,
+    size_t routes, size_t hidden_dim, size_t hidden_row_stride, size_t max_intermediate, size_t output_dim,
+    void* cuda_stream) {
+  const char* what = "nvfp4_silu_gated_mlp_route (single row)";
+  if (route_metadata == nullptr || out == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, std::string(what) + ": null route metadata or output");
+  if (rows != 1) return fail(GLMRT_STATUS_INVALID_ARGUMENT, std::string(what) + ": rows must be 1");   // mlp.cu:729-731
+  return run(hidden, row_indices, route_weights, ExpertPtrs{}, route_metadata, activation_workspace, nullptr, rows, routes,
+             hidden_dim, hidden_row_stride, max_intermediate, output_dim, cuda_stream, what, out);
+}
+
+extern "C" glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace, uint16_t* out, size_t rows,
+    size_t routes, size_t hidden_dim, size_t hidden_row_stride, size_t max_intermediate, size_t output_dim) {
+  return sync_null(glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16_async(
+      hidden, row_indices, route_weights, route_metadata, activation_workspace, out, rows, routes, hidden_dim,
       hidden_row_stride, max_intermediate, output_dim, nullptr));
 }

@@ -242,6 +242,19 @@ glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumul
     const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace,
     float* accumulator, size_t rows, size_t routes, size_t hidden_dim,
     size_t hidden_row_stride, size_t max_intermediate, size_t output_dim, void* cuda_stream);
+/* The batched route MLP for a single token row (glmrt_native.h:598-607, mlp.cu:474-518, 1186-1231):
+ * rows must be 1; out[o] = bf16(sum over the routes whose row index is 0, in route order, of
+ * route_weight * (activation[route] . down[o])), truncated, written (not accumulated). */
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace,
+    uint16_t* out, size_t rows, size_t routes, size_t hidden_dim, size_t hidden_row_stride,
+    size_t max_intermediate, size_t output_dim);
+glmrt_status_t glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16_async(
+    const uint16_t* hidden, const uint32_t* row_indices, const float* route_weights,
+    const glmrt_nvfp4_route_batched_metadata_t* route_metadata, float* activation_workspace,
+    uint16_t* out, size_t rows, size_t routes, size_t hidden_dim, size_t hidden_row_stride,
+    size_t max_intermediate, size_t output_dim, void* cuda_stream);
 /* b12x_direct.cu:203-219: fixed-order float32 sum of the 8 per-route bf16 rows of width
  * 6144 per token, truncated to bf16.  routed_bf16 is [rows * 8, 6144]. */
 glmrt_status_t glmrt_cuda_b12x_spark_sum_topk8_bf16_async(

@@ -366,6 +366,27 @@ def test_w4a16_route_mlp_entry_points_match_the_float32_reference(lib, pkg):
     assert lib.call_status("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_accumulate_f32_async", ptr(x), ptr(ri),
                            ptr(rwt), None, ptr(work), ptr(acc2), C.c_size_t(rows), C.c_size_t(routes), C.c_size_t(H),
                            C.c_size_t(stride), C.c_size_t(I), C.c_size_t(H), stream()) == 1
+    # single row (mlp.cu:474-518): routes whose row index is 0 are summed in route order and the row is
+    # written as truncated bf16; other routes are ignored; rows other than 1 are refused
+    one_idx = np.zeros(routes, np.uint32)
+    one_idx[[2, 9]] = 1
+    oi = dev(one_idx.view(np.int32))
+    out1 = torch.full((H,), 7.0, dtype=torch.bfloat16, device="cuda")
+    lib.call("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16_async", ptr(x), ptr(oi), ptr(rwt),
+             ptr(meta_dev), ptr(work), ptr(out1), C.c_size_t(1), C.c_size_t(routes), C.c_size_t(H), C.c_size_t(stride),
+             C.c_size_t(I), C.c_size_t(H), stream())
+    torch.cuda.synchronize()
+    want1 = np.zeros(H, np.float64)
+    for r in range(routes):
+        if one_idx[r] == 0:
+            want1 += np.float64(rw[r]) * O.expert_forward(x32[0][None, :], ref.expert(int(experts[r])))[0].astype(np.float64)
+    got1 = out1.float().cpu().numpy()
+    s1 = np.abs(want1).max()
+    assert np.abs(got1 - want1).max() <= 2 ** -7 * s1         # one bf16 truncation of a float32 sum
+    assert (np.abs(got1) <= np.abs(want1) + 2e-5 * s1).all()  # truncation never rounds away from zero
+    assert lib.call_status("glmrt_cuda_nvfp4_silu_gated_mlp_route_bf16_batched_staged_single_row_bf16_async", ptr(x), ptr(oi),
+                           ptr(rwt), ptr(meta_dev), ptr(work), ptr(out1), C.c_size_t(2), C.c_size_t(routes), C.c_size_t(H),
+                           C.c_size_t(stride), C.c_size_t(I), C.c_size_t(H), stream()) == 1
 
 
 @pytest.mark.parametrize("rows", [5, 200])
