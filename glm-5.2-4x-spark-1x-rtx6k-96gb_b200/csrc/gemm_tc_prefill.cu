@@ -149,8 +149,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           const int kx = ks * kStageBytesK;
           const size_t ksf = static_cast<size_t>(ks) * 4;
           mbar_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(s_a, &map_act, &full_bar[stage], kx, ch.slot_base, pol);
-          bulk_load(s_sfa, sfa + (sfa_tile0 + ksf) * 512, kSfStageBytes, &full_bar[stage], pol);
+          // weight tiles first: they come from HBM, the rows from L2 (measured: 1 % of the step)
           if (kFC1) {
             // 128 gate rows, then 128 up rows, each with its own scale tile
             tma_load_2d(s_b, &map_w0, &full_bar[stage], kx, w_row, pol);
@@ -167,6 +166,8 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
                         &full_bar[stage], pol);
             }
           }
+          tma_load_2d(s_a, &map_act, &full_bar[stage], kx, ch.slot_base, pol);
+          bulk_load(s_sfa, sfa + (sfa_tile0 + ksf) * 512, kSfStageBytes, &full_bar[stage], pol);
         }
         __syncwarp();
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
