@@ -30,6 +30,28 @@
 #include "tc_ptx.cuh"
 
 namespace glmrt {
+
+// Optional timeline of one CTA (build.py --trace defines GLMRT_B200_TRACE and builds a separate
+// library): clock64 stamps of the producer (slot free seen, loads issued), the issuer (stage full
+// seen, MMAs issued; accumulator wait begin / end per tile) and the first epilogue warp
+// (accumulator full wait begin / end, accumulator released, tile done).  [kernel: 0 FC1, 1 FC2].
+#ifdef GLMRT_B200_TRACE
+constexpr int kTraceCta = 5, kTraceStages = 2048, kTraceTiles = 256;
+__device__ long long g_prefill_stage_trace[2][4][kTraceStages];
+__device__ long long g_prefill_tile_trace[2][6][kTraceTiles];
+#define GLMRT_TRACE_STAGE(kind, ev, n)                                                        \
+  do {                                                                                        \
+    if (blockIdx.x == kTraceCta && (n) < kTraceStages) g_prefill_stage_trace[kind][ev][n] = clock64(); \
+  } while (0)
+#define GLMRT_TRACE_TILE(kind, ev, n)                                                         \
+  do {                                                                                        \
+    if (blockIdx.x == kTraceCta && (n) < kTraceTiles) g_prefill_tile_trace[kind][ev][n] = clock64(); \
+  } while (0)
+#else
+#define GLMRT_TRACE_STAGE(kind, ev, n) ((void)0)
+#define GLMRT_TRACE_TILE(kind, ev, n) ((void)0)
+#endif
+
 namespace {
 
 using namespace tc;
@@ -129,6 +151,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     // ================= TMA producer =================
     const uint64_t pol = policy_evict_last();   // weight tiles serve every chunk of their expert, rows every feature tile
     const uint8_t* sfa = kFC1 ? a.act1_sf : a.act2_sf;
+    [[maybe_unused]] int traced = 0;
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -141,6 +164,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       const size_t sfa_tile0 = static_cast<size_t>(ch.slot_base / 128) * k_tiles64;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
+        if (lane == 0) GLMRT_TRACE_STAGE(kFC1 ? 0 : 1, 0, traced);
         if (elect_one()) {
           const uint32_t s_a = smem_u32(smem + static_cast<size_t>(stage) * C::kStageBytes);
           const uint32_t s_b = s_a + C::kABytes;
@@ -170,11 +194,14 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           bulk_load(s_sfa, sfa + (sfa_tile0 + ksf) * 512, kSfStageBytes, &full_bar[stage], pol);
         }
         __syncwarp();
+        if (lane == 0) GLMRT_TRACE_STAGE(kFC1 ? 0 : 1, 1, traced);
+        ++traced;
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
+    [[maybe_unused]] int traced = 0;
     int stage = 0;
     uint32_t phase = 0;
     int abuf = 0;
@@ -185,12 +212,15 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
       if (halves > 1 && chunk_of(it, tile).tokens == 0) continue;
+      if (lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 0, it);
       if (!mbar_wait_warp(&acc_empty[abuf], aphase ^ 1u, abort_flag)) { alive = false; break; }
       tc_fence_after();
+      if (lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 1, it);
       const uint32_t d0 = tmem_base + abuf * kWN;
       for (int ks = 0; ks < k_stages; ++ks) {
         if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { alive = false; break; }
         tc_fence_after();
+        if (lane == 0) GLMRT_TRACE_STAGE(kFC1 ? 0 : 1, 2, traced);
         const uint32_t t_sfa = tmem_base + C::kSfCol + sf_flip * C::kSfSetCols;
         const uint32_t t_sfb = t_sfa + 16;
         sf_flip ^= 1u;
@@ -213,6 +243,8 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           tc_commit(&empty_bar[stage]);
         }
         __syncwarp();
+        if (lane == 0) GLMRT_TRACE_STAGE(kFC1 ? 0 : 1, 3, traced);
+        ++traced;
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
       if (!alive) break;
@@ -239,8 +271,10 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       const float s2a = a.scale2[ch.expert * 3 + (kFC1 ? 0 : 2)];
       const float s2b = kFC1 ? a.scale2[ch.expert * 3 + 1] : 0.0f;
       uint16_t* dst = (!kFC1 && valid) ? a.slot_out[slot] : nullptr;
+      if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 2, it);
       if (!mbar_wait_warp(&acc_full[abuf], aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
+      if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 3, it);
       const uint32_t t_acc = tmem_base + lane_base + abuf * kWN;
       if (kFC1) {
         // gate occupies columns [0, kWN/2), up [kWN/2, kWN); 16 warps share the 16-feature blocks
@@ -257,6 +291,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[abuf]);
+        if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(0, 4, it);
 #pragma unroll
         for (int j = 0; j < kBlocksPerWarp; ++j) {
           const int b = part * kBlocksPerWarp + j;
@@ -274,6 +309,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
                              out_stage + static_cast<size_t>(warp - 2) * Fc2Stage<128>::kBytesPerWarp, lane,
                              [&] { mbar_arrive(&acc_empty[abuf]); });
       }
+      if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 5, it);
       if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
     }
   }
@@ -309,3 +345,12 @@ glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& m, int 
 }
 
 }  // namespace glmrt
+
+#ifdef GLMRT_B200_TRACE
+// Copies the last launches' stamps to the host: stages [2][4][2048], tiles [2][6][256] (int64).
+extern "C" int glmrt_b200_debug_prefill_trace(long long* stages, long long* tiles) {
+  cudaError_t e = cudaMemcpyFromSymbol(stages, glmrt::g_prefill_stage_trace, sizeof(glmrt::g_prefill_stage_trace));
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(tiles, glmrt::g_prefill_tile_trace, sizeof(glmrt::g_prefill_tile_trace));
+  return static_cast<int>(e);
+}
+#endif
