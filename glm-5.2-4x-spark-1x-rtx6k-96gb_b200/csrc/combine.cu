@@ -8,6 +8,7 @@
 //   * sum_topk8, weighted scatter-add and row gather keep the reference entry points
 //     (b12x_direct.cu:203-219, residual.cu:666-678, residual.cu:133-158).
 #include "common.cuh"
+#include "ep_flags.cuh"
 #include "internal.h"
 
 namespace glmrt {
@@ -33,7 +34,18 @@ template <bool kResidual>
 __global__ void __launch_bounds__(kThreads)
 combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __restrict__ topk_weights,
                       const int32_t* __restrict__ route_slot, uint16_t* __restrict__ out, int rows, int top_k,
-                      int hidden, const uint16_t* __restrict__ residual, const uint16_t* __restrict__ shared) {
+                      int hidden, const uint16_t* __restrict__ residual, const uint16_t* __restrict__ shared,
+                      EpWait wait, uint32_t* error_word) {
+  if (wait.flags != nullptr) {
+    // expert-parallel path: the route rows are stored by the owners of the experts; their flags say when
+    __shared__ uint32_t s_wait_err;
+    if (threadIdx.x == 0) {
+      s_wait_err = ep_wait_all_serial(wait);
+      if (s_wait_err != 0u) atomicOr(error_word, s_wait_err);
+    }
+    __syncthreads();
+    if (s_wait_err != 0u) return;
+  }
   const int vec_per_row = hidden / 8;
   const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
   if (gid >= static_cast<size_t>(rows) * vec_per_row) return;
@@ -150,14 +162,17 @@ unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / 
 
 glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
-                                     cudaStream_t stream, const uint16_t* residual, const uint16_t* shared) {
+                                     cudaStream_t stream, const uint16_t* residual, const uint16_t* shared,
+                                     const EpWait* wait, uint32_t* error_word) {
   const unsigned grid = grid_for(static_cast<size_t>(rows) * (hidden / 8));
+  EpWait w;
+  if (wait != nullptr && error_word != nullptr) w = *wait;
   if (residual != nullptr)
     combine_routes_kernel<true><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
-                                                               hidden, residual, shared);
+                                                               hidden, residual, shared, w, error_word);
   else
     combine_routes_kernel<false><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
-                                                                hidden, nullptr, nullptr);
+                                                                hidden, nullptr, nullptr, w, error_word);
   GLMRT_LAUNCH_CHECK("combine_routes_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -6,51 +6,33 @@
 // (native/src/glmrt_native.cc:1593-1659).  On one NVSwitch box both directions become stores into
 // the peer's own memory issued from inside kernels:
 //
-//   counts    every rank publishes its routes-per-expert histogram to every peer; from the N
-//             histograms each rank derives the SAME slot layout for every owner, so no reply is
-//             needed before rows can be pushed;
-//   dispatch  the home rank of a token stores the route's NVFP4 row (codes, tiled scales) and the
-//             address of its result row straight into the owning rank's slot buffers;
-//   combine   the owner's FC2 epilogue stores each route's bf16 result row through that address
-//             into the home rank's staging rows; the home rank then runs the ordinary combine.
+//   counts    every rank publishes its routes-per-expert histogram to every peer (from the tail of
+//             the router's selection kernel); from the N histograms each rank derives the SAME
+//             slot layout for every owner, so no reply is needed before rows can be pushed;
+//   dispatch  one kernel per rank waits for the histograms, derives the layout, quantises each of
+//             its token rows once in shared memory and stores the row (codes, tiled scales) and
+//             the address of the route's result row straight into the owning rank's slot buffers;
+//   combine   the owner's FC1 kernel waits for the pushed rows, its FC2 epilogue stores each
+//             route's bf16 result row through that address into the home rank's staging rows and
+//             the last CTA raises the "combine" flag; the home rank's combine kernel waits for it.
 //
 // Flags are epoch counters that only grow (no reset races across layers or steps).  Every wait is
-// bounded and reports kErrWaitTimeout instead of spinning forever.  All loads that feed TMA or the
-// tensor core read local memory only; peers are only ever written to.
+// bounded and reports kErrWaitTimeout instead of spinning forever.  A rank without a valid plan
+// (a histogram never arrived, the layout does not fit) pushes nothing and says so (poison word),
+// so that no owner computes on slots nobody filled.  All loads that feed TMA or the tensor core
+// read local memory only; peers are only ever written to.
 #include "common.cuh"
+#include "ep_flags.cuh"
 #include "internal.h"
+#include "quant_block.cuh"
 
 namespace glmrt {
 namespace {
 
 constexpr int kEpThreads = 1024;
-constexpr uint64_t kFlagWaitLimitNs = 2000000000ull;
+constexpr int kPushThreads = 256;
 
-__device__ __forceinline__ uint64_t timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Bounded wait until *flag >= epoch.  Returns false on expiry.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-  const uint64_t t0 = timer_ns();
-  while (true) {
-    if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if (timer_ns() - t0 > kFlagWaitLimitNs) return false;
-    __nanosleep(200);
-  }
-}
-
-// ---- counts: histogram of this rank's routes, published to every rank ----------------------
+// ---- counts: histogram of a rank without rows (ranks with rows publish from the router's tail) ----
 __global__ void __launch_bounds__(kEpThreads) ep_count_kernel(EpArgs a, const uint32_t* topk_indices, int routes) {
   extern __shared__ int hist[];
   for (int e = threadIdx.x; e < a.experts; e += kEpThreads) hist[e] = 0;
@@ -74,172 +56,291 @@ __global__ void __launch_bounds__(kEpThreads) ep_count_kernel(EpArgs a, const ui
   if (threadIdx.x < a.world) st_release_sys(&a.peer_ctrl[threadIdx.x]->flag_counts[a.rank], a.epoch);
 }
 
-// ---- plan: wait for all histograms, derive every owner's slot layout, build own chunk list ----
-__global__ void __launch_bounds__(kEpThreads) ep_plan_kernel(EpArgs a, PlanArgs p) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
+// ---- plan + quantise + dispatch ---------------------------------------------------------------
+// Every CTA derives the layout itself (the tables are small and sit in L2): totals per expert,
+// this rank's offset inside each expert's range, and per owner the first slot of each of its
+// experts.  CTA 0 also writes this rank's own work-item list and counters.  Then CTA r handles
+// token row r: quantise once, push to the owner of each of its routes.
+__global__ void __launch_bounds__(kPushThreads)
+ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidden, uint8_t* __restrict__ payload,
+                        int rows, int top_k, int hidden_dim) {
+  extern __shared__ uint4 ep_smem[];
+  // layout tables first (3 ints per expert), then the payload image of the row
+  int* s_tot = reinterpret_cast<int*>(ep_smem);
+  int* s_mine = s_tot + a.experts;
+  int* s_base = s_mine + a.experts;
+  uint8_t* img = reinterpret_cast<uint8_t*>(ep_smem) + ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15));
+  __shared__ int s_err;
+  __shared__ int s_owner_slots[kEpMaxWorld];
+  __shared__ int s_pos[64];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+  if (threadIdx.x == 0) s_err = 0;
   __syncthreads();
-  if (threadIdx.x < a.world && !wait_flag(&a.ctrl->flag_counts[threadIdx.x], a.epoch)) s_ok = 0;
+  if (threadIdx.x < a.world && !wait_flag(&a.ctrl->flag_counts[threadIdx.x], a.epoch))
+    atomicOr(&s_err, static_cast<int>(kErrWaitTimeout));
   __syncthreads();
-  const bool ok = s_ok != 0;
-  EpControl* c = a.ctrl;
-  // totals per expert and this rank's offset inside each expert's slot range
-  for (int e = threadIdx.x; e < a.experts; e += kEpThreads) {
+  const bool have_counts = s_err == 0;
+  for (int e = threadIdx.x; e < a.experts; e += kPushThreads) {
     int tot = 0, mine = 0;
     for (int s = 0; s < a.world; ++s) {
-      const int v = ok ? c->counts_all[s * kEpMaxExperts + e] : 0;
+      const int v = have_counts ? a.ctrl->counts_all[s * kEpMaxExperts + e] : 0;
       if (s < a.rank) mine += v;
       tot += v;
     }
-    c->total[e] = tot;
-    c->my_offset[e] = mine;
+    s_tot[e] = tot;
+    s_mine[e] = mine;
   }
   __syncthreads();
-  // one thread per owner walks that owner's experts in local order
-  if (threadIdx.x < a.world) {
-    const int owner = threadIdx.x;
-    int running = 0, chunks = 0, distinct = 0, routes = 0;
-    bool overflow = false;
-    for (int e = owner; e < a.experts; e += a.world) {
-      const int tot = c->total[e];
-      c->base_slot[e] = running;
-      if (owner == a.rank) {
-        p.expert_counts[e / a.world] = tot;
+  // warp o scans owner o's experts (e = o, o + world, ...) in local order: first slot of each
+  if (warp < a.world) {
+    const int owner = warp;
+    const int n_local = (a.experts - owner + a.world - 1) / a.world;
+    int running = 0;
+    for (int i0 = 0; i0 < n_local; i0 += 32) {
+      const int i = i0 + lane;
+      const int e = owner + i * a.world;
+      const int span = i < n_local ? expert_slot_span(s_tot[e], a.chunk_tokens) : 0;
+      int incl = span;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
+      }
+      if (i < n_local) s_base[e] = running + incl - span;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      s_owner_slots[owner] = running;
+      if (running > p.max_slots) atomicOr(&s_err, static_cast<int>(kErrSlotOverflow));
+    }
+  }
+  __syncthreads();
+
+  if (blockIdx.x == 0) {
+    // this rank's own work items: chunk offsets by a scan over its experts (warp 0), then every
+    // thread writes the chunks of the experts it owns
+    __shared__ int s_chunk_total;
+    const int n_local = (a.experts - a.rank + a.world - 1) / a.world;
+    __shared__ int s_coff[kEpMaxExperts];
+    if (warp == 0) {
+      int running = 0, distinct = 0, routes = 0;
+      for (int i0 = 0; i0 < n_local; i0 += 32) {
+        const int i = i0 + lane;
+        const int tot = i < n_local ? s_tot[a.rank + i * a.world] : 0;
+        const int n = (tot + p.chunk_tokens - 1) / p.chunk_tokens;
+        int incl = n;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += v;
+        }
+        if (i < n_local) s_coff[i] = running + incl - n;
+        running += __shfl_sync(0xffffffffu, incl, 31);
         distinct += tot != 0;
         routes += tot;
-        for (int off = 0; off < tot; off += p.chunk_tokens) {
-          if (chunks < p.max_chunks) {
-            Chunk ch;
-            ch.expert = e / a.world;
-            ch.slot_base = running + slot_of_position(off, p.chunk_tokens);
-            ch.tokens = min(p.chunk_tokens, tot - off);
-            ch.reserved = 0;
-            p.chunks[chunks] = ch;
-          }
-          ++chunks;
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        distinct += __shfl_xor_sync(0xffffffffu, distinct, d);
+        routes += __shfl_xor_sync(0xffffffffu, routes, d);
+      }
+      if (lane == 0) {
+        s_chunk_total = running;
+        if (running > p.max_chunks) atomicOr(&s_err, static_cast<int>(kErrChunkOverflow));
+        p.counters[kCntSlots] = static_cast<uint32_t>(s_owner_slots[a.rank]);
+        p.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+        p.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+      }
+    }
+    __syncthreads();
+    const bool plan_ok = s_err == 0;
+    for (int i = threadIdx.x; i < n_local; i += kPushThreads) {
+      const int e = a.rank + i * a.world;
+      const int tot = s_tot[e];
+      p.expert_counts[i] = tot;
+      if (plan_ok) {
+        int c = s_coff[i];
+        for (int off = 0; off < tot; off += p.chunk_tokens, ++c) {
+          Chunk ch;
+          ch.expert = i;
+          ch.slot_base = s_base[e] + slot_of_position(off, p.chunk_tokens);
+          ch.tokens = min(p.chunk_tokens, tot - off);
+          ch.reserved = 0;
+          p.chunks[c] = ch;
         }
       }
-      running += expert_slot_span(tot, p.chunk_tokens);
     }
-    if (running > p.max_slots) overflow = true;
-    if (overflow) atomicOr(&c->plan_error, 1);
-    if (owner == a.rank) {
-      uint32_t err = 0;
-      if (!ok) err |= kErrWaitTimeout;
-      if (chunks > p.max_chunks) err |= kErrChunkOverflow;
-      p.counters[kCntSlots] = static_cast<uint32_t>(running);
-      p.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
-      p.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
-      p.counters[kCntChunks] = static_cast<uint32_t>(chunks);  // finalised below
-      if (err != 0) atomicOr(&p.counters[kCntError], err);
+    if (threadIdx.x == 0) {
+      // never start expert work on an inconsistent plan
+      p.counters[kCntChunks] = plan_ok ? static_cast<uint32_t>(s_chunk_total) : 0u;
+      if (!plan_ok) atomicOr(&p.counters[kCntError], static_cast<uint32_t>(s_err));
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    // any owner over capacity (every rank computes the same answer) or a failed wait: no expert work
-    if (c->plan_error != 0) atomicOr(&p.counters[kCntError], static_cast<uint32_t>(kErrSlotOverflow));
-    if (p.counters[kCntError] != 0) p.counters[kCntChunks] = 0;
-    c->plan_error = 0;
+  const bool plan_ok = s_err == 0;
+  if (!plan_ok && threadIdx.x == 0) {
+    atomicOr(&p.counters[kCntError], static_cast<uint32_t>(s_err));
+    atomicOr(&a.ctrl->plan_failed, 1);   // read by the last CTA: one failing CTA poisons the whole push
   }
-}
 
-// ---- dispatch: push each local route's row into its owner's slot buffers --------------------
-__global__ void __launch_bounds__(256)
-ep_dispatch_kernel(EpArgs a, const uint8_t* payload, const uint32_t* topk_indices, int32_t* route_slot, int rows,
-                   int top_k, int hidden, const uint32_t* counters) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32;
-  const int lane = threadIdx.x % 32;
-  const int n = rows * top_k;
-  const bool bad_plan = counters[kCntError] != 0;
-  if (warp < n && !bad_plan) {
-    const uint32_t e = topk_indices[warp];
-    if (e < static_cast<uint32_t>(a.experts)) {
-      int pos = 0;
-      if (lane == 0) pos = atomicAdd(&a.ctrl->cursor[e], 1);
-      pos = __shfl_sync(0xffffffffu, pos, 0);
-      const int owner = static_cast<int>(e % a.world);
-      const int slot = a.ctrl->base_slot[e] + slot_of_position(a.ctrl->my_offset[e] + pos, a.chunk_tokens);
-      const int row = warp / top_k;
-      const int code_bytes = hidden / 2, kblocks = hidden / 16;
-      const uint8_t* src = payload + static_cast<size_t>(row) * (code_bytes + kblocks);
-      const uint4* src4 = reinterpret_cast<const uint4*>(src);
-      uint4* dst4 = reinterpret_cast<uint4*>(a.peer_act_codes[owner] + static_cast<size_t>(slot) * code_bytes);
-      for (int i = lane; i < code_bytes / 16; i += 32) dst4[i] = src4[i];
-      // scales leave as 4-byte words: four consecutive blocks of a slot are contiguous in the tiled layout
-      uint8_t* sf = a.peer_act_sf[owner];
-      const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(src + code_bytes);
-      for (int j = lane; j < kblocks / 4; j += 32)
-        *reinterpret_cast<uint32_t*>(sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
-      if (lane == 0) {
-        a.peer_slot_out[owner][slot] = a.my_rows_in_peer[owner] + static_cast<size_t>(warp) * hidden;
-        route_slot[warp] = slot;
+  const int row = blockIdx.x;
+  if (row < rows) {
+    const int code_bytes = hidden_dim / 2, kblocks = hidden_dim / 16;
+    const size_t row_bytes = static_cast<size_t>(code_bytes + kblocks);
+    if (plan_ok) {
+      if (hidden != nullptr) {
+        quantize_row_to_image(hidden + static_cast<size_t>(row) * hidden_dim, img, hidden_dim, kPushThreads);
+      } else {
+        const uint4* src = reinterpret_cast<const uint4*>(payload + row * row_bytes);
+        for (int i = threadIdx.x; i < static_cast<int>(row_bytes / 16); i += kPushThreads)
+          reinterpret_cast<uint4*>(img)[i] = src[i];
       }
-    } else if (lane == 0) {
-      route_slot[warp] = -1;
+      // positions of the row's routes among this rank's routes of each expert
+      if (threadIdx.x < top_k) {
+        const uint32_t e = p.topk_indices[row * top_k + threadIdx.x];
+        s_pos[threadIdx.x] = e < static_cast<uint32_t>(a.experts) ? atomicAdd(&a.ctrl->cursor[e], 1) : -1;
+      }
+      __syncthreads();
+      if (hidden != nullptr) {
+        uint4* prow = reinterpret_cast<uint4*>(payload + row * row_bytes);
+        for (int i = threadIdx.x; i < static_cast<int>(row_bytes / 16); i += kPushThreads)
+          prow[i] = reinterpret_cast<const uint4*>(img)[i];
+      }
+      const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(img + code_bytes);
+      for (int k = 0; k < top_k; ++k) {
+        const int route = row * top_k + k;
+        const int pos = s_pos[k];
+        if (pos < 0) {
+          if (threadIdx.x == 0) p.route_slot[route] = -1;
+          continue;
+        }
+        const int e = static_cast<int>(p.topk_indices[route]);
+        const int owner = e % a.world;
+        const int slot = s_base[e] + slot_of_position(s_mine[e] + pos, a.chunk_tokens);
+        uint4* dst4 = reinterpret_cast<uint4*>(a.peer_act_codes[owner] + static_cast<size_t>(slot) * code_bytes);
+        for (int i = threadIdx.x; i < code_bytes / 16; i += kPushThreads) dst4[i] = reinterpret_cast<const uint4*>(img)[i];
+        // scales leave as 4-byte words: four consecutive blocks of a slot are contiguous in the tiled layout
+        uint8_t* sf = a.peer_act_sf[owner];
+        for (int j = threadIdx.x; j < kblocks / 4; j += kPushThreads)
+          *reinterpret_cast<uint32_t*>(sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
+        if (threadIdx.x == 0) {
+          a.peer_slot_out[owner][slot] = a.my_rows_in_peer[owner] + static_cast<size_t>(route) * hidden_dim;
+          p.route_slot[route] = slot;
+        }
+      }
+    } else {
+      for (int k = threadIdx.x; k < top_k; k += kPushThreads) p.route_slot[row * top_k + k] = -1;
     }
-  } else if (warp < n && lane == 0) {
-    route_slot[warp] = -1;
   }
-  // last CTA to finish tells every owner that this rank's rows have landed
+
+  // last CTA to finish tells every owner that this rank's rows have landed -- or that none will
   __threadfence_system();
   __syncthreads();
   __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(&a.ctrl->done, 1) == static_cast<int>(gridDim.x) - 1;
+  if (threadIdx.x == 0) s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == static_cast<int>(gridDim.x) - 1;
   __syncthreads();
   if (s_last) {
     __threadfence_system();
-    if (threadIdx.x == 0) a.ctrl->done = 0;
-    if (threadIdx.x < a.world) st_release_sys(&a.peer_ctrl[threadIdx.x]->flag_dispatch[a.rank], a.epoch);
+    const bool failed = *reinterpret_cast<volatile int32_t*>(&a.ctrl->plan_failed) != 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      a.ctrl->ticket_dispatch = 0;
+      a.ctrl->plan_failed = 0;
+    }
+    if (threadIdx.x < a.world) {
+      EpControl* pc = a.peer_ctrl[threadIdx.x];
+      if (failed) {
+        pc->poison_dispatch[a.rank] = a.epoch;
+        __threadfence_system();
+      }
+      st_release_sys(&pc->flag_dispatch[a.rank], a.epoch);
+    }
   }
 }
 
-__global__ void ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, uint32_t* error_word,
-                               uint32_t* chunk_count) {
-  if (threadIdx.x < world && !wait_flag(&flags[threadIdx.x], epoch)) {
-    atomicOr(error_word, static_cast<uint32_t>(kErrWaitTimeout));
+// Stand-alone wait / signal for engines whose kernels do not carry them (the SIMT verification engine).
+__global__ void ep_wait_kernel(EpWait w, uint32_t* error_word, uint32_t* chunk_count) {
+  if (threadIdx.x != 0) return;
+  const uint32_t err = ep_wait_all_serial(w);
+  if (err != 0) {
+    atomicOr(error_word, err);
     if (chunk_count != nullptr) *chunk_count = 0;   // never start expert work on rows that did not arrive
   }
 }
-
-__global__ void ep_signal_kernel(EpArgs a, int which) {
+__global__ void ep_signal_kernel(EpSignal s, const uint32_t* error_word) {
+  if (*error_word != 0u) return;   // a failed step tells no home rank that results have arrived
   __threadfence_system();
-  if (threadIdx.x < a.world) {
-    EpControl* pc = a.peer_ctrl[threadIdx.x];
-    st_release_sys(which == 0 ? &pc->flag_dispatch[a.rank] : &pc->flag_combine[a.rank], a.epoch);
-  }
+  if (threadIdx.x < s.world) st_release_sys(s.peer_flags[threadIdx.x], s.epoch);
 }
 
 }  // namespace
+
+glmrt_status_t launch_ep_wait(const EpWait& w, uint32_t* error_word, uint32_t* chunk_count, cudaStream_t stream) {
+  ep_wait_kernel<<<1, 32, 0, stream>>>(w, error_word, chunk_count);
+  GLMRT_LAUNCH_CHECK("ep_wait_kernel");
+  return GLMRT_STATUS_OK;
+}
+glmrt_status_t launch_ep_signal(const EpSignal& s, const uint32_t* error_word, cudaStream_t stream) {
+  ep_signal_kernel<<<1, 32, 0, stream>>>(s, error_word);
+  GLMRT_LAUNCH_CHECK("ep_signal_kernel");
+  return GLMRT_STATUS_OK;
+}
 
 glmrt_status_t launch_ep_count(const EpArgs& a, const uint32_t* topk_indices, int routes, cudaStream_t stream) {
   ep_count_kernel<<<1, kEpThreads, a.experts * sizeof(int), stream>>>(a, topk_indices, routes);
   GLMRT_LAUNCH_CHECK("ep_count_kernel");
   return GLMRT_STATUS_OK;
 }
-glmrt_status_t launch_ep_plan(const EpArgs& a, const PlanArgs& p, cudaStream_t stream) {
-  ep_plan_kernel<<<1, kEpThreads, 0, stream>>>(a, p);
-  GLMRT_LAUNCH_CHECK("ep_plan_kernel");
+
+RouterCountTail ep_count_tail(const EpArgs& a) {
+  RouterCountTail t{};
+  t.world = a.world;
+  t.epoch = a.epoch;
+  for (int p = 0; p < a.world; ++p) {
+    t.peer_counts[p] = a.peer_ctrl[p]->counts_all + a.rank * kEpMaxExperts;   // address arithmetic only
+    t.peer_flags[p] = a.peer_ctrl[p]->flag_counts + a.rank;
+  }
+  t.cursor = a.ctrl->cursor;
+  t.error_word = a.counters + kCntError;
+  t.ticket = &a.ctrl->ticket_select;
+  return t;
+}
+
+glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const uint16_t* hidden, uint8_t* payload,
+                                       int rows, int top_k, int hidden_dim, cudaStream_t stream) {
+  if (top_k > 64 || hidden_dim % 128 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: top_k must be <= 64 and hidden a multiple of 128");
+  const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
+  if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
+  ep_plan_dispatch_kernel<<<rows > 0 ? rows : 1, kPushThreads, smem, stream>>>(a, p, hidden, payload, rows, top_k, hidden_dim);
+  GLMRT_LAUNCH_CHECK("ep_plan_dispatch_kernel");
   return GLMRT_STATUS_OK;
 }
-glmrt_status_t launch_ep_dispatch(const EpArgs& a, const uint8_t* payload, const uint32_t* topk_indices,
-                                  int32_t* route_slot, int rows, int top_k, int hidden, const uint32_t* counters,
-                                  cudaStream_t stream) {
-  const int n = rows * top_k;
-  ep_dispatch_kernel<<<(n + 7) / 8, 256, 0, stream>>>(a, payload, topk_indices, route_slot, rows, top_k, hidden,
-                                                      counters);
-  GLMRT_LAUNCH_CHECK("ep_dispatch_kernel");
-  return GLMRT_STATUS_OK;
+
+EpWait ep_wait_dispatch(const EpArgs& a) {
+  EpWait w;
+  w.flags = a.ctrl->flag_dispatch;
+  w.poison = a.ctrl->poison_dispatch;
+  w.world = a.world;
+  w.epoch = a.epoch;
+  return w;
 }
-glmrt_status_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, uint32_t* error_word,
-                              uint32_t* chunk_count, cudaStream_t stream) {
-  ep_wait_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, error_word, chunk_count);
-  GLMRT_LAUNCH_CHECK("ep_wait_kernel");
-  return GLMRT_STATUS_OK;
+EpWait ep_wait_combine(const EpArgs& a) {
+  EpWait w;
+  w.flags = a.ctrl->flag_combine;
+  w.poison = nullptr;
+  w.world = a.world;
+  w.epoch = a.epoch;
+  return w;
 }
-glmrt_status_t launch_ep_signal(const EpArgs& a, int which, cudaStream_t stream) {
-  ep_signal_kernel<<<1, 32, 0, stream>>>(a, which);
-  GLMRT_LAUNCH_CHECK("ep_signal_kernel");
-  return GLMRT_STATUS_OK;
+EpSignal ep_signal_combine(const EpArgs& a) {
+  EpSignal s{};
+  for (int p = 0; p < a.world; ++p) s.peer_flags[p] = a.peer_ctrl[p]->flag_combine + a.rank;
+  s.ticket = &a.ctrl->ticket_fc2;
+  s.world = a.world;
+  s.epoch = a.epoch;
+  return s;
 }
 
 }  // namespace glmrt

@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "ep_flags.cuh"
 #include "epilogue.cuh"
 #include "internal.h"
 #include "tc_ptx.cuh"
@@ -43,14 +44,9 @@ struct Cfg {
   static constexpr int kSfbTiles = (kBN + 127) / 128;                      // scale tiles per k-block for B
   static constexpr int kStageBytes = kNumA * kABytes + kBBytes + kNumA * kSfStageBytes + kSfbTiles * kSfStageBytes;
   static constexpr int kStages = (221184 / kStageBytes) > 10 ? 10 : (221184 / kStageBytes);
-  // The k-blocks of a stage may rotate over kSplit independent accumulator sets, issued by
-  // kIssuers warps, that the epilogue adds in a fixed order.  Measured on B200: neither helps once
-  // the issuing warp stays converged and hands the instructions to one elected lane (elect.sync);
-  // issuing from a divergent `lane == 0` branch was what had limited the tensor pipe.  Both stay 1.
-  static constexpr int kSplit = 1;
-  static constexpr int kIssuers = 1;
-  static constexpr int kSetCols = kNumA * kBN;                             // columns of one accumulator set
-  static constexpr int kAccCols = kSplit * kSetCols;                       // accumulator columns per buffer
+  // One issuing warp, kept converged, hands the instructions of a stage to one elected lane
+  // (elect.sync); issuing from a divergent `lane == 0` branch had limited the tensor pipe.
+  static constexpr int kAccCols = kNumA * kBN;                             // accumulator columns per buffer
   static constexpr int kAccBufs = (2 * kAccCols + 16 * kNumA + 16 * kSfbTiles <= 512) ? 2 : 1;
   static constexpr int kSfCol = kAccBufs * kAccCols;                       // first scale column
   static constexpr int kColsUsed = kSfCol + 16 * kNumA + 16 * kSfbTiles;
@@ -91,10 +87,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], C::kIssuers);
+      mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&acc_full[b], C::kIssuers);
+      mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);
     }
     *abort_flag = 0u;
@@ -107,7 +103,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_chunks = static_cast<int>(a.counters[kCntChunks]);
+  // a step that has already reported an error runs no expert work (and tells no peer it did)
+  const bool step_failed = *reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u;
+  const int num_chunks = step_failed ? 0 : static_cast<int>(a.counters[kCntChunks]);
   const int num_tiles = num_chunks * feat_tiles;
   // The work items of this CTA's tiles are fetched once, up front: a global load at the head of
   // every tile would stall each role for a memory round trip and drain the TMA pipeline.
@@ -132,6 +130,16 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       uint32_t phase = 0;
       bool alive = true;
       int it = 0;
+      if (kFC1 && a.wait.flags != nullptr && (blockIdx.x == 0 || static_cast<int>(blockIdx.x) < num_tiles)) {
+        // expert-parallel path: the rows this kernel reads are pushed by the peers (CTA 0 waits even
+        // without work, so that no rank ever runs a step ahead of a peer that is still pushing)
+        const uint32_t werr = ep_wait_all_serial(a.wait);
+        if (werr != 0) {
+          *abort_flag = werr == kErrWaitTimeout ? 1u : 2u;
+          alive = false;
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
         const Chunk ch = chunk_of(it, tile);
         const int ft = tile % feat_tiles;
@@ -164,8 +172,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
-    const int issuer = 0;
-    if (issuer < C::kIssuers) {   // the whole warp runs the loop; one elected lane issues
+    {   // the whole warp runs the loop; one elected lane issues
       int stage = 0;
       uint32_t phase = 0;
       int abuf = 0;
@@ -192,7 +199,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           const uint32_t s_sfb = s_sfa0 + C::kNumA * kSfStageBytes;
           if (elect_one()) {
 #pragma unroll
-          for (int kb = issuer; kb < 4; kb += C::kIssuers) {
+          for (int kb = 0; kb < 4; ++kb) {
             tc_copy_sf(t_sfa0 + kb * 4, desc_sf(s_sfa0 + kb * 512));
             if (kFC1) tc_copy_sf(t_sfa0 + 16 + kb * 4, desc_sf(s_sfa0 + kSfStageBytes + kb * 512));
 #pragma unroll
@@ -200,9 +207,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
               tc_copy_sf(t_sfb + kb * 4 * C::kSfbTiles + t * 4, desc_sf(s_sfb + t * kSfStageBytes + kb * 512));
           }
 #pragma unroll
-          for (int kb = issuer; kb < 4; kb += C::kIssuers) {
-            const uint32_t acc = (ks != 0 || kb >= C::kSplit) ? 1u : 0u;
-            const uint32_t dset = d0 + (kb % C::kSplit) * C::kSetCols;
+          for (int kb = 0; kb < 4; ++kb) {
+            const uint32_t acc = (ks | kb) != 0 ? 1u : 0u;
+            const uint32_t dset = d0;
             const uint64_t bdesc = desc_sw128(s_b + kb * 32);
             const uint32_t sfb_addr = t_sfb + kb * 4 * C::kSfbTiles + sfb_q;
             tc_mma_nvf4(dset, desc_sw128(s_a0 + kb * 32), bdesc, idesc, t_sfa0 + kb * 4, sfb_addr, acc);
@@ -254,18 +261,6 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           tc_load8(t_acc + kBN + c0, u);
           tc_wait_ld();
 #pragma unroll
-          for (int sp = 1; sp < C::kSplit; ++sp) {   // add the other accumulator sets, ascending
-            uint32_t g2[8], u2[8];
-            tc_load8(t_acc + sp * C::kSetCols + c0, g2);
-            tc_load8(t_acc + sp * C::kSetCols + kBN + c0, u2);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              g[j] = __float_as_uint(__fadd_rn(__uint_as_float(g[j]), __uint_as_float(g2[j])));
-              u[j] = __float_as_uint(__fadd_rn(__uint_as_float(u[j]), __uint_as_float(u2[j])));
-            }
-          }
-#pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < ch.tokens)  // uniform across the warp
               swiglu_requant_store<true>(__fmul_rn(__uint_as_float(g[j]), s2a), __fmul_rn(__uint_as_float(u[j]), s2b),
@@ -281,18 +276,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           tc_load8(t_acc + c0, y);
           tc_wait_ld();
 #pragma unroll
-          for (int sp = 1; sp < C::kSplit; ++sp) {   // add the other accumulator sets, ascending
-            uint32_t y2[8];
-            tc_load8(t_acc + sp * C::kSetCols + c0, y2);
-            tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = __float_as_uint(__fadd_rn(__uint_as_float(y[j]), __uint_as_float(y2[j])));
-          }
-#pragma unroll
           for (int j = 0; j < 8; ++j) {
             const unsigned long long p =
                 __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(dst_lane), (c0 + j) & 31);
-            if (c0 + j < ch.tokens)
+            if (c0 + j < ch.tokens && p != 0ull)   // a slot nobody gave a destination is skipped
               reinterpret_cast<uint16_t*>(p)[feature] = f32_to_bf16_rne(__fmul_rn(__uint_as_float(y[j]), s2a));
           }
         }
@@ -306,14 +293,17 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
 
   // ---- teardown ----
   __syncwarp();
-  if (*abort_flag != 0u) {
+  const uint32_t aborted = *abort_flag;
+  if (aborted != 0u) {
     // let copies already in flight land before shared memory is released
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(kErrWaitTimeout));
+    if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(aborted == 2u ? kErrPeerFailed : kErrWaitTimeout));
   }
+  if (!kFC1 && a.signal.ticket != nullptr) __threadfence_system();   // result rows stored to their home ranks
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+  if (!kFC1 && a.signal.ticket != nullptr && aborted == 0u && !step_failed) ep_signal_last_cta(a.signal);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

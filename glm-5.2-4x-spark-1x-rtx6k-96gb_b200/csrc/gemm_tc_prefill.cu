@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "ep_flags.cuh"
 #include "epilogue.cuh"
 #include "fc2_store.cuh"
 #include "internal.h"
@@ -131,7 +132,9 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   // A plan made of 256-slot chunks (for the CTA-pair FC1 kernel) is taken as two halves of 128
   // slots; a half without tokens is skipped by every role alike.
   const int halves = a.chunk_tokens > 128 ? a.chunk_tokens / 128 : 1;
-  const int num_chunks = static_cast<int>(a.counters[kCntChunks]);
+  // a step that has already reported an error runs no expert work (and tells no peer it did)
+  const bool step_failed = *reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u;
+  const int num_chunks = step_failed ? 0 : static_cast<int>(a.counters[kCntChunks]);
   const int num_tiles = num_chunks * halves * feat_tiles;
   auto load_chunk = [&](int tile) -> Chunk {
     Chunk c = a.chunks[tile / (feat_tiles * halves)];
@@ -156,6 +159,18 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     uint32_t phase = 0;
     bool alive = true;
     int it = 0;
+    if (kFC1 && a.wait.flags != nullptr && (blockIdx.x == 0 || static_cast<int>(blockIdx.x) < num_tiles)) {
+      // expert-parallel path: the rows this kernel reads are pushed by the peers (CTA 0 waits even
+      // without work, so that no rank ever runs a step ahead of a peer that is still pushing)
+      uint32_t werr = lane == 0 ? ep_wait_all_serial(a.wait) : 0u;
+      werr = __shfl_sync(0xffffffffu, werr, 0);
+      if (werr != 0) {
+        if (lane == 0) *abort_flag = werr == kErrWaitTimeout ? 1u : 2u;
+        alive = false;
+      }
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __syncwarp();
+    }
     for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
       const Chunk ch = chunk_of(it, tile);
       if (ch.tokens == 0) continue;
@@ -315,13 +330,16 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   }
 
   // ---- teardown ----
-  if (*abort_flag != 0u) {
+  const uint32_t aborted = *abort_flag;
+  if (aborted != 0u) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
-    if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(kErrWaitTimeout));
+    if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(aborted == 2u ? kErrPeerFailed : kErrWaitTimeout));
   }
+  if (!kFC1 && a.signal.ticket != nullptr) __threadfence_system();   // result rows stored to their home ranks
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+  if (!kFC1 && a.signal.ticket != nullptr && aborted == 0u && !step_failed) ep_signal_last_cta(a.signal);
 }
 
 template <bool kFC1, int kWN>

@@ -15,6 +15,7 @@ enum DeviceError : uint32_t {
   kErrSlotOverflow = 2u,      // route plan needs more slots than the layer holds
   kErrChunkOverflow = 4u,     // more (expert, token-chunk) work items than the layer holds
   kErrBadExpert = 8u,         // a route names an expert id >= experts
+  kErrPeerFailed = 16u,       // a peer rank declared that it had no valid plan this step and pushed nothing
 };
 
 // Counters written by the route-plan kernel (device memory, uint32 each).
@@ -36,15 +37,29 @@ struct Chunk {      // one (expert, block of <= BN tokens) work item
 };
 
 // ---- router.cu ----
+struct RouterCountTail;
 glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* weight, bool weight_bf16,
                              const float* bias, float* logits, uint32_t* idx, float* scores, float* weights,
                              size_t rows, size_t hidden_dim, size_t experts, size_t top_k, float scaling,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const RouterCountTail* tail = nullptr);
 
 // splits in 2..8: `logits` holds that many partial tables [splits][rows][experts], added in order
+// Optional tail of the selection kernel in the expert-parallel path: the last CTA to finish counts
+// this rank's routes per expert, stores the histogram into every rank's count table, clears this
+// rank's per-expert cursors and the layer's error word, and raises the per-peer "counts" epoch flag.
+constexpr int kEpMaxWorld = 8;
+struct RouterCountTail {
+  int world = 0;                         // 0: no tail
+  uint32_t epoch = 0;
+  int32_t* peer_counts[kEpMaxWorld];     // this rank's row of each rank's count table
+  uint32_t* peer_flags[kEpMaxWorld];     // this rank's "counts" flag at each rank
+  int32_t* cursor;                       // [experts], local
+  uint32_t* error_word;                  // local
+  int32_t* ticket;                       // local, zero between launches
+};
 glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
                                     float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
-                                    cudaStream_t stream, int splits = 1);
+                                    cudaStream_t stream, int splits = 1, const RouterCountTail* tail = nullptr);
 // ---- router_tc.cu (prefill-sized batches) ----
 glmrt_status_t launch_split_router_weight(const float* w, uint16_t* w3, size_t experts, size_t hidden,
                                           cudaStream_t stream);
@@ -119,20 +134,19 @@ glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& 
 
 // ---- ep.cu (expert-parallel exchange over peer memory) ----
 constexpr int kEpMaxExperts = 1024;
-constexpr int kEpMaxWorld = 8;
 struct EpControl {
   // written by peers
   int32_t counts_all[kEpMaxWorld * kEpMaxExperts];  // [source rank][global expert] routes
   uint32_t flag_counts[kEpMaxWorld];                 // epoch of the last histogram received from each rank
   uint32_t flag_dispatch[kEpMaxWorld];               // epoch of the last completed row push from each rank
+  uint32_t poison_dispatch[kEpMaxWorld];             // epoch in which that rank had no valid plan and pushed nothing
   uint32_t flag_combine[kEpMaxWorld];                // epoch of the last completed result push from each owner
   // local only
-  int32_t total[kEpMaxExperts];       // routes per expert over all ranks
-  int32_t my_offset[kEpMaxExperts];   // first position of this rank's routes inside the expert's slot range
-  int32_t base_slot[kEpMaxExperts];   // first slot of the expert at its owner
   int32_t cursor[kEpMaxExperts];      // next free position among this rank's routes
-  int32_t done;
-  int32_t plan_error;
+  int32_t ticket_select;              // last-CTA tickets of the kernels that end with a publish step
+  int32_t ticket_dispatch;
+  int32_t ticket_fc2;
+  int32_t plan_failed;                // set by any CTA of the push kernel whose plan is invalid
 };
 struct EpArgs {
   int world, rank, experts;
@@ -146,22 +160,42 @@ struct EpArgs {
   uint16_t** peer_slot_out[kEpMaxWorld];
   uint16_t* my_rows_in_peer[kEpMaxWorld];   // this rank's route_rows as addressed from each peer
 };
+// Histogram publish of a rank without rows (the ranks with rows publish from the router's tail).
 glmrt_status_t launch_ep_count(const EpArgs& a, const uint32_t* topk_indices, int routes, cudaStream_t stream);
-glmrt_status_t launch_ep_plan(const EpArgs& a, const PlanArgs& p, cudaStream_t stream);
-glmrt_status_t launch_ep_dispatch(const EpArgs& a, const uint8_t* payload, const uint32_t* topk_indices,
-                                  int32_t* route_slot, int rows, int top_k, int hidden, const uint32_t* counters,
-                                  cudaStream_t stream);
-glmrt_status_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, uint32_t* error_word,
-                              uint32_t* chunk_count, cudaStream_t stream);
-glmrt_status_t launch_ep_signal(const EpArgs& a, int which, cudaStream_t stream);
+RouterCountTail ep_count_tail(const EpArgs& a);
+// Waits for every rank's histogram, derives the slot layout, quantises this rank's rows (or takes
+// their payload rows when `hidden` is null) and stores each route's row into its owner's slot
+// buffers; CTA 0 also writes this rank's own work-item list; the last CTA raises the "dispatch" flag.
+glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const uint16_t* hidden, uint8_t* payload,
+                                       int rows, int top_k, int hidden_dim, cudaStream_t stream);
+// Flags another kernel waits on before it touches what peers have written / raises when it is done.
+struct EpWait {
+  const uint32_t* flags = nullptr;    // [world], nullptr: nothing to wait for
+  const uint32_t* poison = nullptr;   // [world] or nullptr
+  int world = 0;
+  uint32_t epoch = 0;
+};
+struct EpSignal {
+  uint32_t* peer_flags[kEpMaxWorld];  // this rank's flag at each rank
+  int32_t* ticket = nullptr;          // nullptr: nothing to signal
+  int world = 0;
+  uint32_t epoch = 0;
+};
+glmrt_status_t launch_ep_wait(const EpWait& w, uint32_t* error_word, uint32_t* chunk_count, cudaStream_t stream);
+glmrt_status_t launch_ep_signal(const EpSignal& s, const uint32_t* error_word, cudaStream_t stream);
+EpWait ep_wait_dispatch(const EpArgs& a);
+EpWait ep_wait_combine(const EpArgs& a);
+EpSignal ep_signal_combine(const EpArgs& a);
 
 // ---- combine.cu ----
 // residual / shared (optional, [rows, hidden] bf16): fold the routed sum into the layer output,
 // out = bf16(residual + bf16(shared + routed)), instead of storing it.
+struct EpWait;
 glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* topk_weights,
                                      const int32_t* route_slot, uint16_t* out, int rows, int top_k, int hidden,
                                      cudaStream_t stream, const uint16_t* residual = nullptr,
-                                     const uint16_t* shared = nullptr);
+                                     const uint16_t* shared = nullptr, const EpWait* wait = nullptr,
+                                     uint32_t* error_word = nullptr);
 
 // ---- residual.cu ----
 glmrt_status_t launch_bf16_rows_to_fp8_row_scaled(const uint16_t* src, uint8_t* dst, size_t rows, size_t row_width,
@@ -191,6 +225,10 @@ struct FfnArgs {
   const Chunk* chunks; const uint32_t* counters;
   int hidden, inter, max_chunks, chunk_tokens;
   uint32_t* error_word;
+  // expert-parallel path: FC1 waits for the rows its peers push, FC2 tells the home ranks when its
+  // result rows have been stored
+  EpWait wait;
+  EpSignal signal;
 };
 glmrt_status_t launch_fc1_simt(const FfnArgs& a, cudaStream_t stream);
 glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);

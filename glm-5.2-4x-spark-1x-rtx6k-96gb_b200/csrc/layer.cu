@@ -4,8 +4,22 @@
 // It stands where the reference has RealNvfp4ProtocolV2Executor (resident expert preload:
 // rust/crates/glmrt-daemon/src/commands/expertd.rs:246-259, route.rs:2793-3054; per-request
 // execution: expert_probe/protocol_v2_executor.rs:1882-2493) plus the coordinator's router and
-// activation quantiser.  One layer object is driven by one host thread at a time.
+// activation quantiser.
+//
+// A layer handle joins two blocks of device memory with separate lifetimes: the WEIGHTS of its
+// local experts (with the router) and a WORKSPACE (route tables, slot-ordered operands, result rows,
+// exchange buffers and flags).  glmrt_b200_moe_layer_create makes both.  A lane
+// (glmrt_b200_moe_layer_create_lane) shares the weights of an existing layer and owns a fresh
+// workspace, so several host threads / streams can run the same experts at once, as the
+// reference's executor does with one route-tensor cache per execution lane
+// (expert_probe/protocol_v2_executor.rs:123-126,674-690; at most 8 lanes,
+// rust/crates/glmrt-transport/src/host_batch_set.rs:52).  A stacked layer
+// (glmrt_b200_moe_layer_create_stacked) owns its weights and shares the workspace of another
+// layer of the same shape: the 75 sparse layers of a model run one after another on one stream
+// and need one workspace between them.  One handle is driven by one host thread at a time;
+// handles that share a workspace must be used on one stream, in order.
 #include <cstring>
+#include <memory>
 #include <new>
 #include <vector>
 
@@ -15,6 +29,25 @@
 namespace glmrt {
 namespace {
 
+// Device allocations (and peer mappings) that live and die together.
+struct Block {
+  std::vector<void*> allocations;
+  std::vector<void*> ipc_mappings;
+  ~Block() {
+    for (void* p : ipc_mappings) cudaIpcCloseMemHandle(p);
+    for (void* p : allocations) cudaFree(p);
+  }
+};
+
+// Expert-parallel exchange state of one workspace (shared by every handle on that workspace: the
+// epoch must grow across all of them).
+struct EpState {
+  EpArgs args{};
+  bool attached = false;
+  uint32_t epoch = 0;
+  uint32_t global_rows = 0;   // rows of the whole batch over all ranks when the caller has said so, else 0
+};
+
 struct Layer {
   glmrt_b200_moe_config_t cfg{};
   int device = 0;
@@ -23,7 +56,8 @@ struct Layer {
   int max_slots = 0;
   int max_chunks = 0;
   bool have_sf_maps = false;   // the scale arrays are whole 2 KB groups: the CTA-pair FC1 kernel may run
-  std::vector<void*> allocations;
+  std::shared_ptr<Block> weights_block, work_block;
+  std::shared_ptr<EpState> eps;
   // weights (local experts stacked)
   uint8_t *gate_codes = nullptr, *up_codes = nullptr, *down_codes = nullptr;
   uint8_t *gate_sf = nullptr, *up_sf = nullptr, *down_sf = nullptr;
@@ -58,12 +92,8 @@ struct Layer {
   bool profiling = false;
   cudaEvent_t stage_events[GLMRT_B200_STAGE_COUNT + 1] = {};
   bool stage_valid = false;
-  // expert-parallel exchange
+  // expert-parallel exchange (control block in the workspace)
   EpControl* ep_ctrl = nullptr;
-  EpArgs ep{};
-  bool ep_attached = false;
-  uint32_t ep_epoch = 0;
-  std::vector<void*> ipc_mappings;
 };
 
 void mark(Layer* l, int stage_begin, cudaStream_t s) {
@@ -73,7 +103,7 @@ void mark(Layer* l, int stage_begin, cudaStream_t s) {
 size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
 
 template <typename T>
-glmrt_status_t dev_alloc(Layer* l, T** out, size_t count, bool zero = false) {
+glmrt_status_t dev_alloc(Block* b, T** out, size_t count, bool zero = false) {
   void* p = nullptr;
   const size_t bytes = round_up(count * sizeof(T), 256);
   cudaError_t err = cudaMalloc(&p, bytes);
@@ -81,18 +111,16 @@ glmrt_status_t dev_alloc(Layer* l, T** out, size_t count, bool zero = false) {
     cudaGetLastError();
     return fail_cuda(GLMRT_STATUS_ALLOCATION_FAILED, "cudaMalloc (layer buffer)", err);
   }
-  l->allocations.push_back(p);
+  b->allocations.push_back(p);
   if (zero) cudaMemset(p, 0, bytes);
   *out = static_cast<T*>(p);
   return GLMRT_STATUS_OK;
 }
 
 void destroy(Layer* l) {
-  for (void* p : l->ipc_mappings) cudaIpcCloseMemHandle(p);
   for (cudaEvent_t e : l->stage_events)
     if (e != nullptr) cudaEventDestroy(e);
-  for (void* p : l->allocations) cudaFree(p);
-  delete l;
+  delete l;   // the blocks free their memory when the last handle that shares them goes
 }
 
 bool local_expert(const Layer* l, uint32_t e) { return e % l->cfg.ep_world == l->cfg.ep_rank; }
@@ -168,7 +196,8 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
 }
 
 // Router: tensor-core logits for prefill-sized batches, SIMT kernels otherwise.
-glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_t s) {
+glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_t s,
+                          const RouterCountTail* tail = nullptr) {
   const auto& c = l->cfg;
   if (l->have_w3 && router_tc_supported(rows, c.hidden_dim, c.experts, hidden)) {
     int splits = router_tc_splits(rows, c.hidden_dim, c.experts, l->sm_count);
@@ -178,10 +207,10 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
                                                   c.hidden_dim, c.experts, l->counters + kCntRouterError,
                                                   l->sm_count, s, splits));
     return launch_router_select(table, l->router_b, l->topk_idx, l->topk_scores, l->topk_w, rows, c.experts,
-                                c.top_k, c.routed_scaling, s, splits);
+                                c.top_k, c.routed_scaling, s, splits, tail);
   }
   return launch_router(hidden, true, l->router_w, false, l->router_b, l->logits, l->topk_idx, l->topk_scores,
-                       l->topk_w, rows, c.hidden_dim, c.experts, c.top_k, c.routed_scaling, s);
+                       l->topk_w, rows, c.hidden_dim, c.experts, c.top_k, c.routed_scaling, s, tail);
 }
 
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
@@ -265,10 +294,10 @@ glmrt_status_t validate_forward(Layer* l, size_t rows) {
 
 using namespace glmrt;
 
-extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer) {
-  if (config == nullptr || out_layer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: null argument");
-  *out_layer = nullptr;
-  const glmrt_b200_moe_config_t c = *config;
+namespace glmrt {
+namespace {
+
+glmrt_status_t validate_config(const glmrt_b200_moe_config_t& c) {
   if (c.hidden_dim == 0 || c.hidden_dim % 256 != 0 || c.intermediate_dim == 0 || c.intermediate_dim % 256 != 0)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: hidden_dim and intermediate_dim must be positive multiples of 256");
   if (c.experts == 0 || c.experts > 1024 || c.top_k == 0 || c.top_k > 16 || c.top_k > c.experts)
@@ -278,14 +307,16 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   if (c.ep_world == 0 || c.ep_rank >= c.ep_world || c.ep_world > c.experts || c.ep_world > kEpMaxWorld)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: need 0 <= ep_rank < ep_world <= min(experts, 8)");
   if (!(c.routed_scaling > 0.0f)) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: routed_scaling must be positive");
-  GLMRT_RETURN_IF_ERROR(require_cuda());
-  Layer* l = new (std::nothrow) Layer();
-  if (l == nullptr) return fail(GLMRT_STATUS_ALLOCATION_FAILED, "layer create: out of host memory");
-  l->cfg = c;
+  return GLMRT_STATUS_OK;
+}
+
+// Geometry every handle derives from its configuration alone.
+void set_geometry(Layer* l) {
+  const auto& c = l->cfg;
   cudaGetDevice(&l->device);
   cudaDeviceGetAttribute(&l->sm_count, cudaDevAttrMultiProcessorCount, l->device);
   l->local_experts = static_cast<int>((c.experts - c.ep_rank + c.ep_world - 1) / c.ep_world);
-  const size_t H = c.hidden_dim, I = c.intermediate_dim, E = l->local_experts, T = c.max_tokens, K = c.top_k;
+  const size_t E = l->local_experts, T = c.max_tokens, K = c.top_k;
   const size_t routes = T * K;
   // Dense work items (128 / 256 slots): every expert's range is rounded up to 128 slots.  Batches of
   // at most 256 rows use 32-slot work items, each in a 128-slot group of its own (expert_slot_span).
@@ -293,43 +324,165 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_confi
   const size_t decode_slots = 128 * (std::min(E, decode_routes) + decode_routes / 32 + 1);
   l->max_slots = static_cast<int>(std::max(round_up(routes + E * 127, 128), decode_slots));
   l->max_chunks = static_cast<int>(E + (routes + 31) / 32);
+}
+
+glmrt_status_t alloc_weights(Layer* l) {
+  const auto& c = l->cfg;
+  l->weights_block = std::make_shared<Block>();
+  Block* b = l->weights_block.get();
+  const size_t H = c.hidden_dim, I = c.intermediate_dim, E = l->local_experts;
   glmrt_status_t st = GLMRT_STATUS_OK;
   auto A = [&](glmrt_status_t s) { if (st == GLMRT_STATUS_OK) st = s; };
-  A(dev_alloc(l, &l->gate_codes, E * I * H / 2));
-  A(dev_alloc(l, &l->up_codes, E * I * H / 2));
-  A(dev_alloc(l, &l->down_codes, E * H * I / 2));
-  A(dev_alloc(l, &l->gate_sf, E * I * H / 16));
-  A(dev_alloc(l, &l->up_sf, E * I * H / 16));
-  A(dev_alloc(l, &l->down_sf, E * H * I / 16));
-  A(dev_alloc(l, &l->scale2, E * 3, true));
-  A(dev_alloc(l, &l->router_w, static_cast<size_t>(c.experts) * H, true));
-  A(dev_alloc(l, &l->router_b, c.experts, true));
-  A(dev_alloc(l, &l->router_w3, static_cast<size_t>(c.experts) * 3 * H, true));
-  A(dev_alloc(l, &l->logits, T * c.experts));
-  A(dev_alloc(l, &l->topk_w, routes));
-  A(dev_alloc(l, &l->topk_scores, routes));
-  A(dev_alloc(l, &l->topk_idx, routes));
-  A(dev_alloc(l, &l->payload, T * (H / 2 + H / 16)));
-  A(dev_alloc(l, &l->route_slot, routes));
-  A(dev_alloc(l, &l->slot_route, static_cast<size_t>(l->max_slots)));
-  A(dev_alloc(l, &l->expert_counts, E));
-  A(dev_alloc(l, &l->expert_base, E));
-  A(dev_alloc(l, &l->block_hist, ((routes + 255) / 256 + 1) * E));
-  A(dev_alloc(l, &l->chunks, static_cast<size_t>(l->max_chunks)));
-  A(dev_alloc(l, &l->counters, kCntWords, true));
+  A(dev_alloc(b, &l->gate_codes, E * I * H / 2));
+  A(dev_alloc(b, &l->up_codes, E * I * H / 2));
+  A(dev_alloc(b, &l->down_codes, E * H * I / 2));
+  A(dev_alloc(b, &l->gate_sf, E * I * H / 16));
+  A(dev_alloc(b, &l->up_sf, E * I * H / 16));
+  A(dev_alloc(b, &l->down_sf, E * H * I / 16));
+  A(dev_alloc(b, &l->scale2, E * 3, true));
+  A(dev_alloc(b, &l->router_w, static_cast<size_t>(c.experts) * H, true));
+  A(dev_alloc(b, &l->router_b, c.experts, true));
+  A(dev_alloc(b, &l->router_w3, static_cast<size_t>(c.experts) * 3 * H, true));
+  l->have_w3 = false;
+  // the tensor-core router reads the split weight through a tensor map (lanes made later inherit it)
+  if (st == GLMRT_STATUS_OK && c.experts % 128 == 0 && c.hidden_dim % 64 == 0) {
+    st = make_codes_tensor_map(&l->map_w3, l->router_w3, c.experts, static_cast<uint64_t>(c.hidden_dim) * 3 * 2, 128);
+    l->have_w3 = st == GLMRT_STATUS_OK;
+  }
+  return st;
+}
+
+glmrt_status_t alloc_workspace(Layer* l) {
+  const auto& c = l->cfg;
+  l->work_block = std::make_shared<Block>();
+  l->eps = std::make_shared<EpState>();
+  Block* b = l->work_block.get();
+  const size_t H = c.hidden_dim, I = c.intermediate_dim, E = l->local_experts, T = c.max_tokens, K = c.top_k;
+  const size_t routes = T * K;
+  glmrt_status_t st = GLMRT_STATUS_OK;
+  auto A = [&](glmrt_status_t s) { if (st == GLMRT_STATUS_OK) st = s; };
+  A(dev_alloc(b, &l->logits, T * c.experts));
+  A(dev_alloc(b, &l->topk_w, routes));
+  A(dev_alloc(b, &l->topk_scores, routes));
+  A(dev_alloc(b, &l->topk_idx, routes));
+  A(dev_alloc(b, &l->payload, T * (H / 2 + H / 16)));
+  A(dev_alloc(b, &l->route_slot, routes));
+  A(dev_alloc(b, &l->slot_route, static_cast<size_t>(l->max_slots)));
+  A(dev_alloc(b, &l->expert_counts, E));
+  A(dev_alloc(b, &l->expert_base, E));
+  A(dev_alloc(b, &l->block_hist, ((routes + 255) / 256 + 1) * E));
+  A(dev_alloc(b, &l->chunks, static_cast<size_t>(l->max_chunks)));
+  A(dev_alloc(b, &l->counters, kCntWords, true));
   // slot-ordered operands; zero-filled once so that padding slots hold finite values
-  A(dev_alloc(l, &l->act1_codes, static_cast<size_t>(l->max_slots) * H / 2, true));
-  A(dev_alloc(l, &l->act1_sf, static_cast<size_t>(l->max_slots) * H / 16, true));
-  A(dev_alloc(l, &l->act2_codes, static_cast<size_t>(l->max_slots) * I / 2, true));
-  A(dev_alloc(l, &l->act2_sf, static_cast<size_t>(l->max_slots) * I / 16, true));
-  A(dev_alloc(l, &l->route_rows, routes * H));
-  A(dev_alloc(l, &l->slot_out, static_cast<size_t>(l->max_slots)));
-  A(dev_alloc(l, &l->hidden_stage, T * H));
-  A(dev_alloc(l, &l->out_stage, T * H));
-  A(dev_alloc(l, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
-  A(dev_alloc(l, &l->sftmp, I * H / 16));
-  A(dev_alloc(l, &l->amax_tmp, 1, true));
-  if (c.ep_world > 1) A(dev_alloc(l, &l->ep_ctrl, 1, true));
+  A(dev_alloc(b, &l->act1_codes, static_cast<size_t>(l->max_slots) * H / 2, true));
+  A(dev_alloc(b, &l->act1_sf, static_cast<size_t>(l->max_slots) * H / 16, true));
+  A(dev_alloc(b, &l->act2_codes, static_cast<size_t>(l->max_slots) * I / 2, true));
+  A(dev_alloc(b, &l->act2_sf, static_cast<size_t>(l->max_slots) * I / 16, true));
+  A(dev_alloc(b, &l->route_rows, routes * H));
+  // destinations start out null: a slot nobody dispatched to is skipped by the FC2 epilogues
+  A(dev_alloc(b, &l->slot_out, static_cast<size_t>(l->max_slots), true));
+  A(dev_alloc(b, &l->hidden_stage, T * H));
+  A(dev_alloc(b, &l->out_stage, T * H));
+  A(dev_alloc(b, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
+  A(dev_alloc(b, &l->sftmp, I * H / 16));
+  A(dev_alloc(b, &l->amax_tmp, 1, true));
+  if (c.ep_world > 1) A(dev_alloc(b, &l->ep_ctrl, 1, true));
+  // partial logits of the tensor-core router: largest splits * rows over the batch sizes this
+  // workspace can see (splits * tiles <= SM count)
+  l->logits_partial = nullptr;
+  l->logits_partial_floats = 0;
+  if (c.max_tokens > 128 && c.experts % 128 == 0 && c.hidden_dim % 64 == 0) {
+    size_t need = 0;
+    for (size_t rows = 129; rows <= c.max_tokens; rows += 128) {
+      const size_t r = std::min<size_t>(rows + 127, c.max_tokens);
+      const int sp = router_tc_splits(r, c.hidden_dim, c.experts, l->sm_count);
+      if (sp > 1) need = std::max(need, static_cast<size_t>(sp) * r * c.experts);
+    }
+    if (need != 0) {
+      A(dev_alloc(b, &l->logits_partial, need));
+      if (st == GLMRT_STATUS_OK) l->logits_partial_floats = need;
+    }
+  }
+  return st;
+}
+
+// Per-handle state that must not be inherited when a handle is cloned.
+void reset_instance_state(Layer* l) {
+  l->have_maps = false;
+  l->have_sf_maps = false;
+  l->launches_last = 0;
+  l->last_rows = 0;
+  l->profiling = false;
+  l->stage_valid = false;
+  for (cudaEvent_t& e : l->stage_events) e = nullptr;
+}
+
+bool same_shape(const glmrt_b200_moe_config_t& a, const glmrt_b200_moe_config_t& b) {
+  return a.hidden_dim == b.hidden_dim && a.intermediate_dim == b.intermediate_dim && a.experts == b.experts &&
+         a.top_k == b.top_k && a.max_tokens == b.max_tokens && a.ep_world == b.ep_world && a.ep_rank == b.ep_rank;
+}
+
+}  // namespace
+}  // namespace glmrt
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer) {
+  if (config == nullptr || out_layer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer create: null argument");
+  *out_layer = nullptr;
+  GLMRT_RETURN_IF_ERROR(validate_config(*config));
+  GLMRT_RETURN_IF_ERROR(require_cuda());
+  Layer* l = new (std::nothrow) Layer();
+  if (l == nullptr) return fail(GLMRT_STATUS_ALLOCATION_FAILED, "layer create: out of host memory");
+  l->cfg = *config;
+  set_geometry(l);
+  glmrt_status_t st = alloc_weights(l);
+  if (st == GLMRT_STATUS_OK) st = alloc_workspace(l);
+  if (st != GLMRT_STATUS_OK) {
+    destroy(l);
+    return st;
+  }
+  *out_layer = l;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_create_lane(void* layer, uint32_t max_tokens, void** out_lane) {
+  Layer* parent = static_cast<Layer*>(layer);
+  if (parent == nullptr || out_lane == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_lane: null argument");
+  *out_lane = nullptr;
+  if (max_tokens > (1u << 20)) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_lane: max_tokens must be at most 1048576");
+  int dev = -1;
+  cudaGetDevice(&dev);
+  if (dev != parent->device) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_lane: the layer's device must be current");
+  Layer* l = new (std::nothrow) Layer(*parent);   // weight pointers and their block are shared
+  if (l == nullptr) return fail(GLMRT_STATUS_ALLOCATION_FAILED, "create_lane: out of host memory");
+  reset_instance_state(l);
+  if (max_tokens != 0) l->cfg.max_tokens = max_tokens;
+  set_geometry(l);
+  glmrt_status_t st = alloc_workspace(l);          // replaces every work pointer and the exchange state
+  if (st != GLMRT_STATUS_OK) {
+    destroy(l);
+    return st;
+  }
+  *out_lane = l;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_moe_layer_create_stacked(const glmrt_b200_moe_config_t* config,
+                                                              void* workspace_layer, void** out_layer) {
+  Layer* donor = static_cast<Layer*>(workspace_layer);
+  if (config == nullptr || donor == nullptr || out_layer == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_stacked: null argument");
+  *out_layer = nullptr;
+  GLMRT_RETURN_IF_ERROR(validate_config(*config));
+  if (!same_shape(*config, donor->cfg))
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_stacked: the layer must have the shape, max_tokens and shard of the layer whose workspace it shares");
+  int dev = -1;
+  cudaGetDevice(&dev);
+  if (dev != donor->device) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "create_stacked: the donor layer's device must be current");
+  Layer* l = new (std::nothrow) Layer(*donor);     // work pointers, their block and the exchange state are shared
+  if (l == nullptr) return fail(GLMRT_STATUS_ALLOCATION_FAILED, "create_stacked: out of host memory");
+  reset_instance_state(l);
+  l->cfg = *config;
+  glmrt_status_t st = alloc_weights(l);            // replaces every weight pointer
   if (st != GLMRT_STATUS_OK) {
     destroy(l);
     return st;
@@ -357,25 +510,6 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_dev
   if (err == cudaSuccess) err = cudaMemcpyAsync(l->router_b, bias_f32.ptr, bbytes, cudaMemcpyDeviceToDevice, s);
   if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "set_router copy", err);
   GLMRT_RETURN_IF_ERROR(launch_split_router_weight(l->router_w, l->router_w3, l->cfg.experts, l->cfg.hidden_dim, s));
-  if (!l->have_w3 && l->cfg.experts % 128 == 0 && l->cfg.hidden_dim % 64 == 0) {
-    GLMRT_RETURN_IF_ERROR(make_codes_tensor_map(&l->map_w3, l->router_w3, l->cfg.experts,
-                                                static_cast<uint64_t>(l->cfg.hidden_dim) * 3 * 2, 128));
-    l->have_w3 = true;
-    if (l->logits_partial == nullptr && l->cfg.max_tokens > 128) {
-      // largest splits * rows over the batch sizes this layer can see (splits * tiles <= SM count)
-      size_t need = 0;
-      for (size_t rows = 129; rows <= l->cfg.max_tokens; rows += 128) {
-        const size_t r = std::min<size_t>(rows + 127, l->cfg.max_tokens);
-        const int sp = router_tc_splits(r, l->cfg.hidden_dim, l->cfg.experts, l->sm_count);
-        if (sp > 1) need = std::max(need, static_cast<size_t>(sp) * r * l->cfg.experts);
-      }
-      if (need != 0) {
-        glmrt_status_t st = dev_alloc(l, &l->logits_partial, need);
-        if (st != GLMRT_STATUS_OK) return st;
-        l->logits_partial_floats = need;
-      }
-    }
-  }
   return ok();
 }
 
@@ -605,6 +739,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_check(void* layer, void* cuda_str
   if (e & kErrSlotOverflow) msg += " route plan exceeds slot capacity;";
   if (e & kErrChunkOverflow) msg += " route plan exceeds chunk capacity;";
   if (e & kErrBadExpert) msg += " a route names an expert id outside the layer;";
+  if (e & kErrPeerFailed) msg += " a peer rank had no valid plan this step and sent no rows;";
   return fail(GLMRT_STATUS_INTERNAL_ERROR, msg);
 }
 
@@ -696,7 +831,7 @@ glmrt_status_t require_ep(Layer* l, bool attached) {
   if (l == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
   if (l->cfg.ep_world < 2 || l->ep_ctrl == nullptr)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel entry point on a layer created with ep_world == 1");
-  if (attached && !l->ep_attached)
+  if (attached && !l->eps->attached)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel forward before glmrt_b200_ep_attach");
   return GLMRT_STATUS_OK;
 }
@@ -712,69 +847,73 @@ void local_ep_buffers(Layer* l, glmrt_b200_ep_buffers_t* out) {
 glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t rows, uint16_t* out,
                         cudaStream_t s) {
   const auto& c = l->cfg;
-  const int chunk_tokens = c.max_tokens <= 256 ? 32 : 128;   // same on every rank (same configuration)
-  const int routes = static_cast<int>(rows * c.top_k);
-  EpArgs a = l->ep;
-  a.epoch = l->ep_epoch;
+  // Work-item size of the step: every rank must choose the same (it fixes the slot layout), so it
+  // follows the size of the whole batch where the caller has stated it, else the layer's capacity.
+  const uint32_t batch = l->eps->global_rows != 0 ? l->eps->global_rows : c.max_tokens;
+  const int chunk_tokens = batch <= 256 ? 32 : 128;
+  EpArgs a = l->eps->args;
+  a.epoch = l->eps->epoch;
   a.chunk_tokens = chunk_tokens;
   switch (phase) {
     case 0: {
+      // router; the tail of its selection kernel publishes this rank's routes-per-expert histogram
       mark(l, GLMRT_B200_STAGE_ROUTER, s);
-      if (rows > 0)
-        GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s));
+      if (rows > 0) {
+        const RouterCountTail tail = ep_count_tail(a);
+        GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s, &tail));
+      } else {
+        GLMRT_RETURN_IF_ERROR(launch_ep_count(a, l->topk_idx, 0, s));
+      }
       mark(l, GLMRT_B200_STAGE_QUANTIZE, s);
-      // the histogram only needs the routes: it goes out to the peers first and travels while the
-      // rows are quantised
-      GLMRT_RETURN_IF_ERROR(launch_ep_count(a, l->topk_idx, routes, s));
-      if (rows > 0)
-        GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
-                                                           GLMRT_B200_FP4_RULE_NEAREST_LOW, s));
-      mark(l, GLMRT_B200_STAGE_PLAN, s);
       return GLMRT_STATUS_OK;
     }
     case 1: {
+      // wait for every histogram, derive the layout, quantise the rows and push them to their owners
+      mark(l, GLMRT_B200_STAGE_PLAN, s);
       PlanArgs p{};
       p.topk_indices = l->topk_idx;
       p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
       p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
       p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
       p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
-  p.expert_base = l->expert_base; p.block_hist = l->block_hist;
+      p.expert_base = l->expert_base; p.block_hist = l->block_hist;
       p.chunks = l->chunks; p.counters = l->counters;
-      GLMRT_RETURN_IF_ERROR(launch_ep_plan(a, p, s));
       mark(l, GLMRT_B200_STAGE_DISPATCH, s);
-      if (routes > 0)
-        return launch_ep_dispatch(a, l->payload, l->topk_idx, l->route_slot, static_cast<int>(rows),
-                                  static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), l->counters, s);
-      return launch_ep_signal(a, 0, s);   // nothing to push: just tell the owners
+      return launch_ep_plan_dispatch(a, p, hidden, l->payload, static_cast<int>(rows), static_cast<int>(c.top_k),
+                                     static_cast<int>(c.hidden_dim), s);
     }
     case 2: {
-      GLMRT_RETURN_IF_ERROR(launch_ep_wait(l->ep_ctrl->flag_dispatch, static_cast<int>(c.ep_world), a.epoch,
-                                           l->counters + kCntError, l->counters + kCntChunks, s));
+      // expert FFN on what arrived: FC1 waits for the peers' rows, FC2 stores each result row into
+      // its home rank and raises the "combine" flag when the last CTA is done
       FfnArgs f = ffn_args(l, chunk_tokens);
       mark(l, GLMRT_B200_STAGE_FC1, s);
       if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
+        GLMRT_RETURN_IF_ERROR(launch_ep_wait(ep_wait_dispatch(a), l->counters + kCntError, l->counters + kCntChunks, s));
         GLMRT_RETURN_IF_ERROR(launch_fc1_simt(f, s));
         mark(l, GLMRT_B200_STAGE_FC2, s);
         GLMRT_RETURN_IF_ERROR(launch_fc2_simt(f, s));
-      } else {
-        if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
-        const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
-        GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, s)
-                                                 : launch_fc1_tc_prefill(f, maps, l->sm_count, s));
-        mark(l, GLMRT_B200_STAGE_FC2, s);
-        GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, s)
-                                                 : launch_fc2_tc_prefill(f, maps, l->sm_count, s));
+        mark(l, GLMRT_B200_STAGE_COMBINE, s);
+        return launch_ep_signal(ep_signal_combine(a), l->counters + kCntError, s);
       }
+      f.wait = ep_wait_dispatch(a);
+      f.signal = ep_signal_combine(a);
+      if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
+      const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
+      GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, s)
+                                               : launch_fc1_tc_prefill(f, maps, l->sm_count, s));
+      mark(l, GLMRT_B200_STAGE_FC2, s);
+      GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc2_tc(f, maps, l->sm_count, s)
+                                               : launch_fc2_tc_prefill(f, maps, l->sm_count, s));
       mark(l, GLMRT_B200_STAGE_COMBINE, s);
-      return launch_ep_signal(a, 1, s);   // results of this owner have been stored to their home ranks
+      return GLMRT_STATUS_OK;
     }
     case 3: {
-      GLMRT_RETURN_IF_ERROR(launch_ep_wait(l->ep_ctrl->flag_combine, static_cast<int>(c.ep_world), a.epoch,
-                                           l->counters + kCntError, nullptr, s));
-      if (rows > 0)
-        GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, nullptr, out, static_cast<int>(rows),
-                                                    static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), s));
+      if (rows > 0) {
+        const EpWait w = ep_wait_combine(a);
+        GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, l->route_slot, out, static_cast<int>(rows),
+                                                    static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), s,
+                                                    nullptr, nullptr, &w, l->counters + kCntError));
+      }
       mark(l, GLMRT_B200_STAGE_COUNT, s);
       l->stage_valid = l->profiling;
       return GLMRT_STATUS_OK;
@@ -837,7 +976,7 @@ extern "C" glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handle
     std::memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * i, 64);
     cudaError_t err = cudaIpcOpenMemHandle(&ptrs[i], h, cudaIpcMemLazyEnablePeerAccess);
     if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaIpcOpenMemHandle (peer access between the GPUs is required)", err);
-    l->ipc_mappings.push_back(ptrs[i]);
+    l->work_block->ipc_mappings.push_back(ptrs[i]);
   }
   out_mapped->act_codes = ptrs[0];
   out_mapped->act_sf = ptrs[1];
@@ -871,8 +1010,17 @@ extern "C" glmrt_status_t glmrt_b200_ep_attach(void* layer, const glmrt_b200_ep_
   }
   if (a.peer_ctrl[a.rank] != l->ep_ctrl)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: the entry of this rank must be its own local buffers");
-  l->ep = a;
-  l->ep_attached = true;
+  l->eps->args = a;
+  l->eps->attached = true;
+  return ok();
+}
+
+extern "C" glmrt_status_t glmrt_b200_ep_set_global_rows(void* layer, uint32_t global_rows) {
+  Layer* l = static_cast<Layer*>(layer);
+  GLMRT_RETURN_IF_ERROR(require_ep(l, false));
+  if (static_cast<uint64_t>(global_rows) > static_cast<uint64_t>(l->cfg.max_tokens) * l->cfg.ep_world)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_set_global_rows: more rows than the ranks can hold");
+  l->eps->global_rows = global_rows;
   return ok();
 }
 
@@ -883,7 +1031,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_ep_phase_async(void* laye
   Layer* l = static_cast<Layer*>(layer);
   GLMRT_RETURN_IF_ERROR(validate_ep_forward(l, hidden_bf16, rows, output_bf16));
   if (phase > 3) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_ep: phase must be 0..3");
-  if (phase == 0) ++l->ep_epoch;
+  if (phase == 0) ++l->eps->epoch;
   const uint64_t before = launches_total();
   GLMRT_RETURN_IF_ERROR(ep_phase(l, phase, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
                                  static_cast<uint16_t*>(output_bf16.ptr), static_cast<cudaStream_t>(cuda_stream)));

@@ -12,50 +12,12 @@
 
 #include "common.cuh"
 #include "internal.h"
+#include "quant_block.cuh"
 
 namespace glmrt {
 namespace {
 
 constexpr int kThreads = 256;
-
-// One 16-element block: E4M3 scale of amax/6, then E2M1 codes, low nibble first.
-//
-// kNearestLow is the rule of the Python reference (quant_ref.py:41-46): the code nearest to the
-// IEEE quotient x / scale, ties towards the smaller magnitude.  The quotient is never formed:
-// for a bf16 x (8 significant bits), an E4M3 scale (4 bits) and a code midpoint m (0.25 .. 5),
-// x / scale is either exactly m or differs from it by more than 2^-9 relative, far more than the
-// rounding of the division, so fl(x / scale) > m holds exactly when |x| > m * scale, and m * scale
-// is exact in float32.  Seven comparisons against exact products replace sixteen divisions.
-template <bool kNearestLow>
-__device__ __forceinline__ void quantize_block16(const float (&v)[16], uint32_t& lo, uint32_t& hi, uint32_t& sbyte) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  sbyte = f32_to_e4m3_satfinite(__fdiv_rn(amax, 6.0f));
-  const float scale = e4m3_to_f32(sbyte);
-  lo = 0; hi = 0;
-  if (kNearestLow) {
-    if (scale != 0.0f) {
-      const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale,
-                  t5 = 3.5f * scale, t6 = 5.0f * scale;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float m = fabsf(v[i]);
-        const uint32_t mag = (m > t0) + (m > t1) + (m > t2) + (m > t3) + (m > t4) + (m > t5) + (m > t6);
-        const uint32_t c = mag | ((v[i] < 0.0f && mag != 0u) ? 8u : 0u);
-        if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-      }
-    }
-  } else {
-    const float inv = scale == 0.0f ? 0.0f : __fdiv_rn(1.0f, scale);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float q = fminf(fmaxf(__fmul_rn(v[i], inv), -6.0f), 6.0f);
-      const uint32_t c = fp4_code_rne_payload(q);
-      if (i < 8) lo |= c << (4 * i); else hi |= c << (4 * (i - 8));
-    }
-  }
-}
 
 // ---- activation payload -------------------------------------------------------------
 template <bool kNearestLow, bool kVector>

@@ -117,7 +117,7 @@ extern "C" glmrt_status_t glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async(cons
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "bf16_rows_to_fp8_row_scaled: null pointer or empty shape");
   if (row_width > SIZE_MAX - sizeof(float) || dst_row_stride_bytes < row_width + sizeof(float) ||
       dst_row_stride_bytes % alignof(float) != 0 || row_width % alignof(float) != 0 || rows > SIZE_MAX / row_width ||
-      rows > 0x7fffffffull)
+      rows > 0x7fffffffull || reinterpret_cast<uintptr_t>(dst) % alignof(float) != 0)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT,
                 "bf16_rows_to_fp8_row_scaled: the row stride must hold the row and a float32 scale, 4-byte aligned");
   GLMRT_RETURN_IF_ERROR(require_cuda());
@@ -132,7 +132,8 @@ extern "C" glmrt_status_t glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_asyn
   if (src == nullptr || row_indices == nullptr || dst == nullptr || rows == 0 || row_width == 0)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "gather_rows_f32_to_fp8_row_scaled: null pointer or empty shape");
   if (row_width > SIZE_MAX - sizeof(float) || dst_row_stride_bytes < row_width + sizeof(float) ||
-      dst_row_stride_bytes % alignof(float) != 0 || row_width % alignof(float) != 0 || rows > 0x7fffffffull)
+      dst_row_stride_bytes % alignof(float) != 0 || row_width % alignof(float) != 0 || rows > 0x7fffffffull ||
+      reinterpret_cast<uintptr_t>(dst) % alignof(float) != 0)
     return fail(GLMRT_STATUS_INVALID_ARGUMENT,
                 "gather_rows_f32_to_fp8_row_scaled: the row stride must hold the row and a float32 scale, 4-byte aligned");
   GLMRT_RETURN_IF_ERROR(require_cuda());

@@ -184,12 +184,12 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
                                      float* __restrict__ topk_weights, int rows, int experts, int top_k,
-                                     float scaling, int splits) {
+                                     float scaling, int splits, RouterCountTail tail) {
   extern __shared__ float smem[];
   const int warps = blockDim.x / 32;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int row = blockIdx.x * warps + warp;
-  if (row >= rows) return;
+  if (row < rows) {
   float* sel = smem + static_cast<size_t>(warp) * 2 * experts;
   float* raw = sel + experts;
   for (int e = lane; e < experts; e += 32) {
@@ -254,6 +254,41 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     if (topk_scores != nullptr) topk_scores[out + lane + 32] = my_score2;
     topk_weights[out + lane + 32] = my_score2 / sum * scaling;
   }
+  }  // row < rows
+  if (tail.world == 0) return;
+  // Expert-parallel path: the last CTA to finish counts this rank's routes per expert and publishes
+  // the histogram to every rank (the first step of the exchange, otherwise a launch of its own).
+  __shared__ int s_is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_is_last = atomicAdd(tail.ticket, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+  int* hist = reinterpret_cast<int*>(smem);   // 2 * experts floats per warp are free again
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int routes = rows * top_k;
+  const volatile uint32_t* all_idx = topk_indices;   // written by other CTAs of this grid
+  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
+    const uint32_t e = all_idx[r];
+    if (e < static_cast<uint32_t>(experts)) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int c = hist[e];
+    for (int p = 0; p < tail.world; ++p) tail.peer_counts[p][e] = c;
+    tail.cursor[e] = 0;
+  }
+  if (threadIdx.x == 0) {
+    *tail.error_word = 0u;   // a new step begins: clear the layer's error word
+    *tail.ticket = 0;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < static_cast<unsigned>(tail.world)) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tail.peer_flags[threadIdx.x]), "r"(tail.epoch) : "memory");
+  }
 }
 
 glmrt_status_t validate(const void* hidden, const void* weight, const float* bias, const uint32_t* idx,
@@ -275,7 +310,7 @@ glmrt_status_t validate(const void* hidden, const void* weight, const float* bia
 glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* weight, bool weight_bf16,
                              const float* bias, float* logits, uint32_t* idx, float* scores, float* weights,
                              size_t rows, size_t hidden_dim, size_t experts, size_t top_k, float scaling,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const RouterCountTail* tail) {
   const dim3 grid(static_cast<unsigned>((rows + kTM - 1) / kTM), static_cast<unsigned>((experts + kTN - 1) / kTN));
   const int r = static_cast<int>(rows), h = static_cast<int>(hidden_dim), e = static_cast<int>(experts);
   const bool small = hidden_bf16 && rows <= kSmallMaxRows && hidden_dim <= 128 * kSmallWarps * kSmallMaxSteps && hidden_dim % 128 == 0 &&
@@ -303,17 +338,19 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
   else
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "router: float32 hidden with bf16 weights is not supported");
   GLMRT_LAUNCH_CHECK("router_logits_kernel");
-  return launch_router_select(logits, bias, idx, scores, weights, rows, experts, top_k, scaling, stream);
+  return launch_router_select(logits, bias, idx, scores, weights, rows, experts, top_k, scaling, stream, 1, tail);
 }
 
 glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
                                     float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
-                                    cudaStream_t stream, int splits) {
+                                    cudaStream_t stream, int splits, const RouterCountTail* tail) {
   const int warps = 4;
+  RouterCountTail t{};
+  if (tail != nullptr) t = *tail;
   const size_t smem = static_cast<size_t>(warps) * 2 * experts * sizeof(float);
   router_select_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, smem, stream>>>(
       logits, bias, idx, scores, weights, static_cast<int>(rows), static_cast<int>(experts),
-      static_cast<int>(top_k), scaling, splits);
+      static_cast<int>(top_k), scaling, splits, t);
   GLMRT_LAUNCH_CHECK("router_select_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -1,4 +1,4 @@
-"""Expert-parallel set-up and benchmark driver.
+"""Expert-parallel set-up and forward calls.
 
 One process per GPU (``torch.distributed`` for the rendezvous only): every rank creates a layer
 shard, exchanges CUDA IPC handles of its exchange buffers, learns under which address each peer sees
@@ -10,7 +10,6 @@ rank; rows and results move as in-kernel stores over NVLink, no NCCL collective 
 from __future__ import annotations
 
 import ctypes as C
-import json
 
 import torch
 
@@ -75,6 +74,12 @@ def attach_distributed(layer: MoeLayer, dist) -> None:
     dist.all_gather_object(views, [int(b.route_rows) for b in peers])
     attach(layer, peers, [views[o][rank] for o in range(world)])
     dist.barrier()
+
+
+def set_global_rows(layer: MoeLayer, global_rows: int) -> None:
+    """Tell the exchange how many rows the whole batch has over all ranks (same value on every
+    rank): up to 256 it runs decode-sized work items, above prefill-sized ones."""
+    layer.lib.call("glmrt_b200_ep_set_global_rows", layer.handle, C.c_uint32(global_rows))
 
 
 def forward_ep(layer: MoeLayer, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

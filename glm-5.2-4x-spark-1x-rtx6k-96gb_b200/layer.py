@@ -50,6 +50,32 @@ class MoeLayer:
         self.lib.call("glmrt_b200_moe_layer_create", C.byref(self.cfg), C.byref(self.handle))
         self.device = torch.device("cuda", torch.cuda.current_device())
 
+    def _clone_with_handle(self, handle: C.c_void_p) -> "MoeLayer":
+        other = object.__new__(MoeLayer)
+        other.__dict__.update(self.__dict__)
+        other.handle = handle
+        return other
+
+    def create_lane(self, max_tokens: int = 0) -> "MoeLayer":
+        """A handle on the same expert weights with a workspace of its own (glmrt_b200_moe_layer_create_lane):
+        lanes can run concurrently on different streams / host threads.  ``max_tokens``: the lane's
+        row capacity (0 = this layer's)."""
+        h = C.c_void_p()
+        self.lib.call("glmrt_b200_moe_layer_create_lane", self.handle, C.c_uint32(max_tokens), C.byref(h))
+        lane = self._clone_with_handle(h)
+        if max_tokens:
+            lane.max_tokens = max_tokens
+            lane.cfg = N.MoeConfig(self.hidden, self.inter, self.experts, self.top_k, max_tokens, self.ep_world,
+                                   self.ep_rank, self.cfg.flags, self.cfg.routed_scaling)
+        return lane
+
+    def create_stacked(self) -> "MoeLayer":
+        """Another layer of the same shape with weights of its own that shares this layer's workspace
+        (glmrt_b200_moe_layer_create_stacked): the next sparse layer of a model."""
+        h = C.c_void_p()
+        self.lib.call("glmrt_b200_moe_layer_create_stacked", C.byref(self.cfg), self.handle, C.byref(h))
+        return self._clone_with_handle(h)
+
     def close(self) -> None:
         if self.handle:
             self.lib.call("glmrt_b200_moe_layer_destroy", self.handle)

@@ -415,6 +415,25 @@ enum {
 
 glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer);
 glmrt_status_t glmrt_b200_moe_layer_destroy(void* layer);
+/* An execution lane: a handle that shares the expert weights and router of `layer` and owns a  */
+/* workspace of its own, so that several host threads / streams can run the same experts at     */
+/* once -- the reference executor keeps one route-tensor cache per lane behind a mutex and      */
+/* serves up to 8 lanes (expert_probe/protocol_v2_executor.rs:123-126,674-690;                  */
+/* rust/crates/glmrt-transport/src/host_batch_set.rs:52).  Every layer entry point accepts a    */
+/* lane.  max_tokens: row capacity of the lane's workspace (0 = the layer's), e.g. a decode lane */
+/* and a prefill lane on the same experts.  Weights may be (re)loaded through any handle, with   */
+/* no forward in flight on the others.  The memory of the weights is released when the last     */
+/* handle that shares it is destroyed.  The layer's device must be current.                      */
+glmrt_status_t glmrt_b200_moe_layer_create_lane(void* layer, uint32_t max_tokens, void** out_lane);
+/* A layer with weights of its own that shares the WORKSPACE of `workspace_layer` (same shape,  */
+/* max_tokens and shard): the sparse layers of a model run one after the other                   */
+/* (docs/balanced-path.md:53-66: 75 serially dependent sparse layers per cycle), so a stack     */
+/* needs the expert weights of every layer but one workspace.  Handles that share a workspace   */
+/* must run on one stream, in order; in the expert-parallel path the exchange buffers belong    */
+/* to the workspace, so a stack attaches once (through any of its layers) and the epoch         */
+/* counter of the exchange runs through all of them.                                             */
+glmrt_status_t glmrt_b200_moe_layer_create_stacked(const glmrt_b200_moe_config_t* config, void* workspace_layer,
+                                                   void** out_layer);
 /* float32 router weight [experts, hidden_dim] and bias [experts] (device memory). */
 glmrt_status_t glmrt_b200_moe_layer_set_router(void* layer, glmrt_device_buffer_t weight_f32,
                                                glmrt_device_buffer_t bias_f32, void* cuda_stream);
@@ -564,6 +583,10 @@ glmrt_status_t glmrt_b200_ep_attach(void* layer, const glmrt_b200_ep_buffers_t* 
  * 3 combine.  forward_ep_async runs 0..3; the phase entry point lets one process step several
  * ranks that share a device (kernels that wait on one another must not be queued behind each
  * other).  Waits are bounded; expiry is reported by glmrt_b200_moe_layer_check. */
+/* Optional: the row count of the whole batch over all ranks for the steps that follow (0 =     */
+/* unknown).  All ranks must state the same value.  The exchange uses decode-sized work items    */
+/* up to 256 rows and prefill-sized ones above; without this call it goes by max_tokens.         */
+glmrt_status_t glmrt_b200_ep_set_global_rows(void* layer, uint32_t global_rows);
 glmrt_status_t glmrt_b200_moe_layer_forward_ep_async(void* layer, glmrt_device_buffer_t hidden_bf16,
                                                      size_t rows, glmrt_device_buffer_t output_bf16,
                                                      void* cuda_stream);

@@ -1,7 +1,7 @@
 """Multi-process check of the expert-parallel forward: run under torchrun, one rank per GPU.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port P glm-5.2-4x-spark-1x-rtx6k-96gb_b200/ep_selfcheck.py
+        --master-port P tests/ep_selfcheck.py
 
 Every rank loads its shard of a small seeded layer, the ranks exchange rows and results over
 NVLink peer memory, and rank 0 compares the gathered output with a single-shard layer run on its
@@ -17,7 +17,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-HERE = os.path.dirname(os.path.abspath(__file__))
+HERE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "glm-5.2-4x-spark-1x-rtx6k-96gb_b200")
 
 
 def _load():

@@ -90,7 +90,7 @@ def main(ref_root: str) -> None:
     np.savez_compressed(os.path.join(HERE, "router.npz"), **router)
 
     # ---- NVFP4 MoE layer (small shapes) -------------------------------------
-    def e4m3_cast(x):  # RNE, clamped: the survey's oracle composition
+    def e4m3_cast(x):  # RNE, clamped to the largest finite E4M3 value before the cast
         return torch.clamp(x, max=448.0).to(torch.float8_e4m3fn)
 
     def ref_quantize_weight(w):

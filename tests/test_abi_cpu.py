@@ -141,3 +141,19 @@ def test_protocol_codec_validates_its_arguments(lib, pkg):
     # the executor refuses a null layer before it looks at the frame
     assert lib.call_status("glmrt_b200_pv2_execute", None, frame, C.c_size_t(len(frame)), small, C.c_size_t(16),
                            C.byref(n), None) == 1
+
+
+def test_row_scaled_fp8_packers_refuse_a_misaligned_destination(lib, pkg):
+    """The row-scaled FP8 packers store each row's float32 scale behind the row's bytes: the
+    destination itself must be 4-byte aligned like the width and the stride, or the store would
+    fault on the device.  Checked before any CUDA call, so it answers without a GPU."""
+    aligned, odd = C.c_void_p(4096), C.c_void_p(4098)
+    for sym, extra in (("glmrt_cuda_bf16_rows_to_fp8_e4m3_row_scaled_async", ()),
+                       ("glmrt_cuda_gather_rows_f32_to_fp8_e4m3_row_scaled_async", (C.c_void_p(8192),))):
+        args = (C.c_size_t(2), C.c_size_t(64), C.c_size_t(68), None)
+        assert lib.call_status(sym, aligned, *extra, odd, *args) == 1
+        assert "4-byte aligned" in lib.last_error()
+    # lanes and stacked layers validate their arguments without a device as well
+    out = C.c_void_p()
+    assert lib.call_status("glmrt_b200_moe_layer_create_lane", None, C.c_uint32(0), C.byref(out)) == 1
+    assert lib.call_status("glmrt_b200_moe_layer_create_stacked", None, None, C.byref(out)) == 1

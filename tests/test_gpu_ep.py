@@ -114,10 +114,73 @@ def test_ep_across_real_gpus_when_more_than_one_is_visible(pkg):
         pytest.skip("needs at least 2 GPUs")
     world = 2 if n < 4 else 4
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    script = os.path.join(root, "glm-5.2-4x-spark-1x-rtx6k-96gb_b200", "ep_selfcheck.py")
+    script = os.path.join(root, "tests", "ep_selfcheck.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29533", script],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert f"EP_SELFCHECK_OK world={world}" in r.stdout
+
+
+def test_a_rank_without_a_plan_poisons_its_push_and_owners_run_nothing(pkg, small_layer):
+    """Rank 0 gives up waiting for rank 2's histogram (bounded wait, about 2 s) and therefore has no
+    slot layout; ranks 1 and 2, whose plans succeed, have reserved slots for rank 0's routes.  Rank
+    0 must say that it pushed nothing, and the owners must then run no expert work on those slots
+    (no result row is stored anywhere) and report the step as failed."""
+    from glmrt_b200 import ep as EP
+    from glmrt_b200.layer import MoeLayer
+    from glmrt_b200.native import GlmrtError
+    K, world = 4, 3
+    shards = []
+    for r in range(world):
+        l = MoeLayer(512, 256, 16, K, max_tokens=64, ep_world=world, ep_rank=r)
+        l.load_quantized_layer(small_layer)
+        shards.append(l)
+    EP.attach_in_process(shards)
+    x = to_dev(O.make_hidden(2, 30, 512))
+    parts = [EP.partition_rows(30, world, r) for r in range(world)]
+    ins = [x[s:s + n].contiguous() for s, n in parts]
+    outs = [torch.zeros_like(i) for i in ins]
+    # one good step first, so that stale destinations of an earlier step exist
+    for phase in range(4):
+        for r in range(world):
+            EP.forward_ep_phase(shards[r], phase, ins[r], outs[r])
+        torch.cuda.synchronize()
+    for l in shards:
+        l.check()
+    before = [l.debug("ROUTE_ROWS", np.uint16).copy() for l in shards]
+    # the failing step
+    EP.forward_ep_phase(shards[0], 0, ins[0], outs[0])
+    EP.forward_ep_phase(shards[1], 0, ins[1], outs[1])
+    EP.forward_ep_phase(shards[0], 1, ins[0], outs[0])     # rank 2 has not published: expires, poisons
+    torch.cuda.synchronize()
+    EP.forward_ep_phase(shards[2], 0, ins[2], outs[2])     # late
+    for r in (1, 2):
+        EP.forward_ep_phase(shards[r], 1, ins[r], outs[r])
+    torch.cuda.synchronize()
+    for r in (1, 2):
+        EP.forward_ep_phase(shards[r], 2, ins[r], outs[r])
+    torch.cuda.synchronize()
+    with pytest.raises(GlmrtError) as e0:
+        shards[0].check()
+    assert "bounded wait" in str(e0.value)
+    for r in (1, 2):
+        with pytest.raises(GlmrtError) as ei:
+            shards[r].check()
+        assert "no valid plan" in str(ei.value)
+    after = [l.debug("ROUTE_ROWS", np.uint16) for l in shards]
+    for b, a in zip(before, after):
+        np.testing.assert_array_equal(a, b)
+    # the context is still usable and the next step is clean
+    for phase in range(4):
+        for r in range(world):
+            EP.forward_ep_phase(shards[r], phase, ins[r], outs[r])
+        torch.cuda.synchronize()
+    for l in shards:
+        l.check()
+    _, _, oo = O.layer_forward(small_layer, O.make_hidden(2, 30, 512), K, mode="O1")
+    got = np.concatenate([to_bits(o) for o in outs], axis=0)
+    assert O.rel_l2_per_token(got, oo).max() <= 2e-2
+    for l in shards:
+        l.close()

@@ -531,3 +531,176 @@ def test_layer_loaded_from_a_checkpoint_matches_the_direct_load(pkg, small_layer
     assert CK.load_moe_layer(shard, cat, 7).experts_loaded == list(range(1, E, 2))
     for l in (layer, direct, shard):
         l.close()
+
+
+# ---------------------------------------------------------------------------------------------
+# Headline shapes against the CPU oracle: a row's arithmetic is independent of the other rows of
+# its batch (mode O1), so a few rows of a large batch can be checked on the CPU by dequantising
+# only the experts those rows selected.
+# ---------------------------------------------------------------------------------------------
+def oracle_rows_error(layer, hid_bits, idx, w, out_bits, rows):
+    """Max per-token relative L2 error of `rows` of a forward pass against O.moe_forward (O1) on the
+    same rows, with the weights of the selected experts read back from the device one at a time."""
+    cache = {}
+
+    def getw(e):
+        if e not in cache:
+            (gc, gs, g2), (uc, us, u2), (dc, ds, d2) = layer.read_expert(e)
+            cache.clear()  # one expert at a time keeps host memory flat
+            cache[e] = O.ExpertWeights(O.dequantize_weight(gc, gs, g2), O.dequantize_weight(uc, us, u2),
+                                       O.dequantize_weight(dc, ds, d2))
+        return cache[e]
+
+    rows = np.asarray(rows)
+    oo = O.moe_forward(hid_bits[rows], getw, idx[rows], w[rows], mode="O1")
+    return O.rel_l2_per_token(out_bits[rows], oo)
+
+
+def glm_layer(seed, T, bias=None, K=8):
+    from glmrt_b200.layer import MoeLayer
+    H, I, E = 6144, 2048, 256
+    layer = MoeLayer(H, I, E, K, max_tokens=T)
+    layer.fill_synthetic(seed, 0.02)
+    rng = np.random.default_rng(seed)
+    rw = (rng.standard_normal((E, H), np.float32) * np.float32(0.02)).astype(np.float32)
+    b = np.zeros(E, np.float32) if bias is None else bias.astype(np.float32)
+    layer.set_router(torch.from_numpy(rw), torch.from_numpy(b))
+    return layer, rw, b
+
+
+@pytest.mark.parametrize("T,n_rows", [(64, 8), (8192, 8)])
+def test_glm52_shape_headline_sizes_match_oracle_on_sampled_rows(pkg, T, n_rows):
+    """The two sizes the throughput figures are quoted on (decode T = 64, prefill T = 8192), GLM-5.2
+    layer shape, uniform router: router indices of every row against the oracle, and the output
+    of sampled rows against O.moe_forward within the layer gate."""
+    layer, rw, bias = glm_layer(3, T)
+    hid = O.make_hidden(9000 + T, T, 6144)
+    out, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    layer.check()
+    gi, gw, ob = idx.cpu().numpy(), w.cpu().numpy(), to_bits(out)
+    x64 = O.bf16_to_f32(hid).astype(np.float64)
+    s64 = 1.0 / (1.0 + np.exp(-(x64 @ rw.astype(np.float64).T))) + bias
+    oi, ow, _, _ = O.router_topk(O.bf16_to_f32(hid), rw, bias, 8)
+    assert O.router_indices_equivalent(gi, oi, s64)
+    rows = np.linspace(0, T - 1, n_rows).astype(np.int64)
+    np.testing.assert_allclose(gw[rows], ow[rows], rtol=2e-5, atol=1e-6)
+    err = oracle_rows_error(layer, hid, gi, gw, ob, rows)
+    print(f"glm52 T={T}: {n_rows} sampled rows vs O1: max per-token rel L2 = {err.max():.3e}")
+    assert err.max() <= TOL
+    layer.close()
+
+
+@pytest.mark.parametrize("T", [16, 2048])
+def test_glm52_shape_zipf_routing_matches_oracle_on_sampled_rows(pkg, T):
+    """Load-skewed routing at the GLM-5.2 layer shape (popularity ~ rank^-1.2): T = 16 is the
+    speculative-verify batch 4 x (1 + 3 drafts) on the decode kernels, T = 2048 puts many token
+    chunks on the hot experts and none on the cold ones."""
+    rng = np.random.default_rng(17)
+    rw = (rng.standard_normal((256, 6144), np.float32) * np.float32(0.02)).astype(np.float32)
+    hid = O.make_hidden(9100 + T, T, 6144)
+    import bench   # the benchmark's calibration of the skewed router (repository root is on sys.path)
+    bias = bench.zipf_bias(rw, O.bf16_to_f32(O.make_hidden(9101, 1024, 6144)), 1.2)
+    from glmrt_b200.layer import MoeLayer
+    layer = MoeLayer(6144, 2048, 256, 8, max_tokens=T)
+    layer.fill_synthetic(5, 0.02)
+    layer.set_router(torch.from_numpy(rw), torch.from_numpy(bias))
+    out, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    layer.check()
+    gi, gw, ob = idx.cpu().numpy(), w.cpu().numpy(), to_bits(out)
+    x64 = O.bf16_to_f32(hid).astype(np.float64)
+    s64 = 1.0 / (1.0 + np.exp(-(x64 @ rw.astype(np.float64).T))) + bias
+    oi, _, _, _ = O.router_topk(O.bf16_to_f32(hid), rw, bias, 8)
+    assert O.router_indices_equivalent(gi, oi, s64)
+    counts = np.bincount(gi.reshape(-1), minlength=256)
+    assert counts[:8].sum() > 4 * counts[-64:].sum()          # the routing really is skewed
+    np.testing.assert_array_equal(layer.debug("EXPERT_COUNTS", np.int32)[:256], counts)
+    rows = np.linspace(0, T - 1, 6).astype(np.int64)
+    err = oracle_rows_error(layer, hid, gi, gw, ob, rows)
+    print(f"glm52 zipf T={T}: max per-token rel L2 = {err.max():.3e}, hottest expert {counts.max()} of {T * 8} routes")
+    assert err.max() <= TOL
+    layer.close()
+
+
+def test_router_choice_of_a_row_across_batch_size_classes(pkg):
+    """The logits of a row come from the SIMT kernel up to 128 rows and from the tensor-core kernel
+    above: the two sum in different orders, so a row's selection may differ between the classes
+    only where two experts' selection scores are within 1e-6 of each other."""
+    layer, rw, bias = glm_layer(4, 512)
+    hid = O.make_hidden(9200, 512, 6144)
+    x = to_dev(hid)
+    _, idx_big, w_big = layer.forward(x, want_routes=True)
+    _, idx_small, w_small = layer.forward(x[:96].contiguous(), want_routes=True)
+    layer.check()
+    x64 = O.bf16_to_f32(hid[:96]).astype(np.float64)
+    s64 = 1.0 / (1.0 + np.exp(-(x64 @ rw.astype(np.float64).T))) + bias
+    assert O.router_indices_equivalent(idx_small.cpu().numpy(), idx_big[:96].cpu().numpy().astype(np.int64), s64)
+    same = (idx_small.cpu().numpy() == idx_big[:96].cpu().numpy()).all(axis=1)
+    np.testing.assert_allclose(w_small.cpu().numpy()[same], w_big[:96].cpu().numpy()[same], rtol=2e-5, atol=1e-6)
+    layer.close()
+
+
+# ---------------------------------------------------------------------------------------------
+# Lanes (shared weights, own workspace) and stacked layers (own weights, shared workspace)
+# ---------------------------------------------------------------------------------------------
+def test_two_lanes_on_two_streams_match_serial_execution(pkg, small_layer):
+    """Two lanes of one layer run at the same time on two streams; each must give exactly what
+    the layer gives when it runs the same batch alone (the reference executor's lanes share the
+    resident experts and keep per-lane route tensors)."""
+    K = 4
+    layer = make(pkg, small_layer, K, 512)
+    lanes = [layer.create_lane(), layer.create_lane()]
+    xs = [to_dev(O.make_hidden(600 + i, T, 512)) for i, T in enumerate((300, 40))]
+    refs = [to_bits(layer.forward(x)).copy() for x in xs]
+    layer.check()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.zeros_like(x) for x in xs]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for lane, st, x, o in zip(lanes, streams, xs, outs):
+            with torch.cuda.stream(st):
+                lane.forward(x, o)
+    for st in streams:
+        st.synchronize()
+    for lane, st in zip(lanes, streams):
+        with torch.cuda.stream(st):
+            lane.check()
+    for o, r in zip(outs, refs):
+        np.testing.assert_array_equal(to_bits(o), r)
+    # the weights outlive the handle that created them
+    layer.close()
+    again = to_bits(lanes[0].forward(xs[0]))
+    lanes[0].check()
+    np.testing.assert_array_equal(again, refs[0])
+    for lane in lanes:
+        lane.close()
+
+
+def test_stacked_layers_share_one_workspace(pkg):
+    """Three layers with different weights on one workspace, chained output -> input like the
+    sparse layers of a model: same result as three independent layers."""
+    K, H, I, E, T = 4, 512, 256, 16, 48
+    refs = [O.make_layer(40 + i, H, I, E) for i in range(3)]
+    x0 = to_dev(O.make_hidden(77, T, H))
+    # independent layers
+    y = x0
+    for ref in refs:
+        l = make(pkg, ref, K, 64)
+        y = l.forward(y).clone()
+        l.check()
+        l.close()
+    expect = to_bits(y)
+    # one workspace
+    base = make(pkg, refs[0], K, 64)
+    stack = [base]
+    for ref in refs[1:]:
+        l = base.create_stacked()
+        l.load_quantized_layer(ref)
+        stack.append(l)
+    y = x0
+    for l in stack:
+        y = l.forward(y).clone()
+    for l in stack:
+        l.check()
+    np.testing.assert_array_equal(to_bits(y), expect)
+    for l in reversed(stack):
+        l.close()

@@ -19,7 +19,7 @@ def test_e4m3_decode_matches_reference_table(golden_dir):
     g = _load(golden_dir, "formats.npz")
     np.testing.assert_array_equal(O.e4m3_decode(np.arange(256, dtype=np.uint8)), g["e4m3_table"])
     # python/reference/tests/test_nvfp4_real_tensor_fixture_ref.py:22-63 and
-    # sparse_mlp/math.rs:235: 0x38 -> 1.0; survey-checked 0x7e -> 448
+    # sparse_mlp/math.rs:235: 0x38 -> 1.0; 0x7e -> 448 is the largest finite E4M3 value
     assert O.e4m3_decode(0x38) == 1.0 and O.e4m3_decode(0x7E) == 448.0
 
 

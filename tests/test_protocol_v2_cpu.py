@@ -3,8 +3,10 @@
 byte-level checks against an independent ``struct``/``hashlib`` restatement of the wire layout.
 
 The reference's tests hold no golden byte strings (they are round trips and rejections), and its
-Rust cannot be built here, so byte-level parity with the Rust encoder is unpinned; what pins the
-bytes is the layout documented in protocol_v2.rs, restated twice (C and this file), and SHA-256 /
+Rust cannot be built here.  What pins the bytes: the frame header (magic, version, kind, header
+length rule, flags and wire-bytes offsets) by the reference's own C++ frame validator, compiled
+from the reference tree (last tests of this file); row descriptors, route entries and payload only
+by the layout documented in protocol_v2.rs, restated twice (C and this file), and SHA-256 /
 compact ids checked against hashlib.
 """
 import hashlib
@@ -284,3 +286,95 @@ def test_stream_data_frames_parse_with_their_own_rules(P, Err):
     assert view.header.route_count == offset and view.row_descriptor_count == 0 and view.hidden_payload() == payload
     with pytest.raises(Err, match="not built by this encoder"):
         make_request(P, 1, P.ExpertV2SourceKind.Decode, hidden_dim=32, flags=flags).encode()
+
+
+# ---------------------------------------------------------------------------------------------
+# The reference's own frame validator (native/src/glmrt_native.cc, compiled by oracle/build_ref.py
+# into oracle/_ref/) on the frames this repository encodes: pins magic, version, kind, the header
+# length rule (96, or 128 with the debug-checksum flag), the flags offset (84 in requests, 68 in
+# responses) and the wire-bytes offset (76 / 60).  Row descriptors, route entries and the payload
+# are not looked at by that validator and stay pinned only by the restated layout above.
+# ---------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def ref_validate():
+    import ctypes
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    from oracle import build_ref
+    path = build_ref.build()
+    if path is None:
+        pytest.skip("the reference tree is not present and oracle/_ref holds no built validator")
+    lib = ctypes.CDLL(path)
+    fn = lib.glmrt_ref_validate_protocol_v2_frame
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_char_p, ctypes.c_size_t]
+
+    def validate(frame: bytes, kind: int):
+        msg = ctypes.create_string_buffer(256)
+        st = fn(frame, len(frame), kind, msg, 256)
+        return st, msg.value.decode()
+    return validate
+
+
+def all_test_frames(P):
+    """(frame, kind) for every shape of request and response frame the tests of this file build."""
+    K = P.ExpertV2SourceKind
+    D = P.ExpertV2Dtype
+    out = []
+    for rows, kind in ((1, K.Decode), (2, K.MtpVerify), (8, K.MtpVerify), (16, K.Prefill), (257, K.Prefill)):
+        out.append((make_request(P, rows, kind, hidden_dim=64).encode(), 1))
+    out.append((make_request(P, 1, K.Decode).encode(), 1))
+    out.append((make_request(P, 3, K.Decode, dtype=D.Nvfp4E2m1Fp8E4m3).encode(), 1))
+    out.append((make_request(P, 2, K.Decode, hidden_dim=32, flags=P.EXPERT_PROTOCOL_V2_FLAG_DEBUG_CHECKSUM).encode(), 1))
+    out.append((make_request(P, 2, K.Decode, hidden_dim=64, stride=160).encode(), 1))
+    ok = P.ExpertProtocolV2Status.Ok
+    out.append((P.ExpertProtocolV2Response(42, 9, 3, 1, 6144, D.Bf16, ok, bytes(range(256)) * 48).encode(), 2))
+    out.append((P.ExpertProtocolV2Response(1, 1, 0, 2, 64, D.Bf16, ok, b"\x11" * 320, 160).encode(), 2))
+    for dtype, row in ((D.Fp8E4m3RowScaled, 6148), (D.Nvfp4E2m1Fp8E4m3, 3456)):
+        out.append((P.ExpertProtocolV2Response(7, 1, 2, 2, 6144, dtype, ok, bytes([0x35]) * (2 * row)).encode(), 2))
+    chunk = P.ExpertProtocolV2Response(5, 1, 0, 3, 64, D.Bf16, ok, b"\x22" * 384)
+    chunk.with_row_indices([4, 0, 9], more_chunks=True)
+    out.append((chunk.encode(), 2))
+    checked = P.ExpertProtocolV2Response(5, 1, 0, 3, 64, D.Bf16, ok, b"\x22" * 384)
+    checked.with_debug_checksum().with_row_indices([2, 1, 0], False)
+    out.append((checked.encode(), 2))
+    return out
+
+
+def test_frames_pass_the_reference_validator(P, ref_validate):
+    frames = all_test_frames(P)
+    assert len(frames) >= 15
+    for frame, kind in frames:
+        st, msg = ref_validate(frame, kind)
+        assert st == 0, f"reference validator refused a kind-{kind} frame of {len(frame)} bytes: {msg}"
+        # the other kind's offsets must not fit: a request is no response
+        assert ref_validate(frame, 3 - kind)[0] != 0
+
+
+def test_reference_validator_and_this_codec_reject_the_same_malformed_frames(P, Err, ref_validate):
+    good = make_request(P, 2, P.ExpertV2SourceKind.Decode, hidden_dim=64).encode()
+    resp = P.ExpertProtocolV2Response(1, 1, 0, 2, 64, P.ExpertV2Dtype.Bf16, P.ExpertProtocolV2Status.Ok, b"\x11" * 256).encode()
+    cases = {
+        "short": good[:80],
+        "magic": b"X" + good[1:],
+        "version": good[:8] + struct.pack("<H", 3) + good[10:],
+        "header_len": good[:12] + struct.pack("<I", 128) + good[16:],
+        "wire_bytes": good[:76] + struct.pack("<Q", len(good) + 1) + good[84:],
+        "truncated": good[:-1],
+    }
+    for name, frame in cases.items():
+        st, msg = ref_validate(frame, 1)
+        assert st != 0, name
+        with pytest.raises(Err):
+            P.ExpertProtocolV2Request.decode(frame)
+    bad_resp = resp[:60] + struct.pack("<Q", len(resp) + 4) + resp[68:]
+    assert ref_validate(bad_resp, 2)[0] != 0
+    with pytest.raises(Err):
+        P.ExpertProtocolV2Response.decode(bad_resp)
+    # the debug-checksum flag decides the header length: setting it on a 96-byte header is refused by both
+    flagged = good[:84] + struct.pack("<I", P.EXPERT_PROTOCOL_V2_FLAG_DEBUG_CHECKSUM) + good[88:]
+    assert ref_validate(flagged, 1)[0] != 0
+    with pytest.raises(Err):
+        P.ExpertProtocolV2Request.decode(flagged)
