@@ -36,6 +36,8 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
                       const int32_t* __restrict__ route_slot, uint16_t* __restrict__ out, int rows, int top_k,
                       int hidden, const uint16_t* __restrict__ residual, const uint16_t* __restrict__ shared,
                       EpWait wait, uint32_t* error_word) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (wait.flags != nullptr) {
     // expert-parallel path: the route rows are stored by the owners of the experts; their flags say when
     __shared__ uint32_t s_wait_err;
@@ -168,11 +170,12 @@ glmrt_status_t launch_combine_routes(const uint16_t* route_rows, const float* to
   EpWait w;
   if (wait != nullptr && error_word != nullptr) w = *wait;
   if (residual != nullptr)
-    combine_routes_kernel<true><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
-                                                               hidden, residual, shared, w, error_word);
+    launch_pdl(combine_routes_kernel<true>, dim3(grid), dim3(kThreads), 0, stream, route_rows, topk_weights, route_slot,
+               out, rows, top_k, hidden, residual, shared, w, error_word);
   else
-    combine_routes_kernel<false><<<grid, kThreads, 0, stream>>>(route_rows, topk_weights, route_slot, out, rows, top_k,
-                                                                hidden, nullptr, nullptr, w, error_word);
+    launch_pdl(combine_routes_kernel<false>, dim3(grid), dim3(kThreads), 0, stream, route_rows, topk_weights, route_slot,
+               out, rows, top_k, hidden, static_cast<const uint16_t*>(nullptr), static_cast<const uint16_t*>(nullptr), w,
+               error_word);
   GLMRT_LAUNCH_CHECK("combine_routes_kernel");
   return GLMRT_STATUS_OK;
 }

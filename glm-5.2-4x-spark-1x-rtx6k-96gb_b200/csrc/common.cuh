@@ -62,6 +62,36 @@ inline glmrt_status_t ensure_smem_limit(std::atomic<uint64_t>& done, Kernel kern
   return GLMRT_STATUS_OK;
 }
 
+// ---- programmatic dependent launch ----
+// The kernels of a forward pass are launched so that each may begin while its predecessor on the
+// stream is still running: a kernel raises pdl_launch_dependents() as its first statement (its
+// successor's CTAs may then take free SM resources and run their own set-up: barrier
+// initialisation, tensor-memory allocation), and calls pdl_wait() before its first access to
+// global memory that an earlier kernel may still be producing (or still reading).  pdl_wait()
+// returns once every earlier kernel has completed and its writes are visible; both are no-ops in
+// a kernel launched the ordinary way, and an ordinary launch after such a kernel waits for its
+// completion as always.  GLMRT_B200_NO_PDL=1 in the environment turns the launch attribute off.
+bool pdl_enabled();
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 // ---- device-side formats ----
 #ifdef __CUDACC__
 

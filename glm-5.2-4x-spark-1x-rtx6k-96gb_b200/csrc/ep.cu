@@ -59,8 +59,8 @@ __global__ void __launch_bounds__(kEpThreads) ep_count_kernel(EpArgs a, const ui
 // ---- plan + quantise + dispatch ---------------------------------------------------------------
 // Every CTA derives the layout itself (the tables are small and sit in L2): totals per expert,
 // this rank's offset inside each expert's range, and per owner the first slot of each of its
-// experts.  CTA 0 also writes this rank's own work-item list and counters.  Then CTA r handles
-// token row r: quantise once, push to the owner of each of its routes.
+// experts.  CTA 0 also writes this rank's own work-item list and counters.  Then the CTAs walk the
+// token rows (row = CTA index, + grid size, ...): quantise once, push to the owner of each route.
 __global__ void __launch_bounds__(kPushThreads)
 ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidden, uint8_t* __restrict__ payload,
                         int rows, int top_k, int hidden_dim) {
@@ -75,8 +75,10 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   __shared__ int s_pos[64];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) s_err = 0;
   __syncthreads();
+  pdl_wait();   // the routes (and the cleared cursors) come from the router's kernels
   if (threadIdx.x < a.world && !wait_flag(&a.ctrl->flag_counts[threadIdx.x], a.epoch))
     atomicOr(&s_err, static_cast<int>(kErrWaitTimeout));
   __syncthreads();
@@ -184,9 +186,9 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
     atomicOr(&a.ctrl->plan_failed, 1);   // read by the last CTA: one failing CTA poisons the whole push
   }
 
-  const int row = blockIdx.x;
-  if (row < rows) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const int code_bytes = hidden_dim / 2, kblocks = hidden_dim / 16;
+    __syncthreads();   // the previous row's image and positions have been read
     const size_t row_bytes = static_cast<size_t>(code_bytes + kblocks);
     if (plan_ok) {
       if (hidden != nullptr) {
@@ -313,7 +315,10 @@ glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: top_k must be <= 64 and hidden a multiple of 128");
   const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
   if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
-  ep_plan_dispatch_kernel<<<rows > 0 ? rows : 1, kPushThreads, smem, stream>>>(a, p, hidden, payload, rows, top_k, hidden_dim);
+  // every CTA derives the layout once, so large batches walk their rows with a bounded grid
+  const int grid = rows > 0 ? (rows < 1184 ? rows : 1184) : 1;
+  launch_pdl(ep_plan_dispatch_kernel, dim3(grid), dim3(kPushThreads), smem, stream, a, p, hidden, payload,
+             rows, top_k, hidden_dim);
   GLMRT_LAUNCH_CHECK("ep_plan_dispatch_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(kThreadsTC, 1)
 expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                    const __grid_constant__ CUtensorMap map_b) {
   using C = Cfg<kFC1, kBN>;
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,6 +104,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above (barriers, tensor memory) ran while the previous kernel was finishing; from
+  // here on this kernel reads what that kernel wrote.
+  pdl_wait();
   // a step that has already reported an error runs no expert work (and tells no peer it did)
   const bool step_failed = *reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u;
   const int num_chunks = step_failed ? 0 : static_cast<int>(a.counters[kCntChunks]);
@@ -328,7 +332,7 @@ glmrt_status_t launch_one(const FfnArgs& a, const CUtensorMap& a0, const CUtenso
   using C = Cfg<kFC1, kBN>;
   static std::atomic<uint64_t> configured{0};
   GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_kernel<kFC1, kBN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_kernel)"));
-  expert_gemm_kernel<kFC1, kBN><<<sm_count, kThreadsTC, C::kSmemBytes, stream>>>(a, a0, a1, b);
+  launch_pdl(expert_gemm_kernel<kFC1, kBN>, dim3(sm_count), dim3(kThreadsTC), C::kSmemBytes, stream, a, a0, a1, b);
   GLMRT_LAUNCH_CHECK("expert_gemm_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
 expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act,
                           const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1) {
   using C = PfCfg<kFC1, kWN>;
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(C::kStages) * C::kStageBytes);
@@ -129,6 +130,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_wait();   // set-up above overlapped the previous kernel's tail; its results are read from here on
   // A plan made of 256-slot chunks (for the CTA-pair FC1 kernel) is taken as two halves of 128
   // slots; a half without tokens is skipped by every role alike.
   const int halves = a.chunk_tokens > 128 ? a.chunk_tokens / 128 : 1;
@@ -348,7 +350,7 @@ glmrt_status_t launch_tokens(const FfnArgs& a, const CUtensorMap& act, const CUt
   using C = PfCfg<kFC1, kWN>;
   static std::atomic<uint64_t> configured{0};
   GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_tokens_kernel<kFC1, kWN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)"));
-  expert_gemm_tokens_kernel<kFC1, kWN><<<sm_count, C::kThreads, C::kSmemBytes, stream>>>(a, act, w0, w1);
+  launch_pdl(expert_gemm_tokens_kernel<kFC1, kWN>, dim3(sm_count), dim3(C::kThreads), C::kSmemBytes, stream, a, act, w0, w1);
   GLMRT_LAUNCH_CHECK("expert_gemm_tokens_kernel");
   return GLMRT_STATUS_OK;
 }

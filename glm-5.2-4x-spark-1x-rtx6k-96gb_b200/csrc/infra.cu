@@ -7,6 +7,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace glmrt {
@@ -39,6 +41,13 @@ glmrt_status_t require_cuda() {
     return fail(GLMRT_STATUS_CUDA_UNAVAILABLE, "no CUDA device is available");
   }
   return GLMRT_STATUS_OK;
+}
+bool pdl_enabled() {
+  static const bool on = []() {
+    const char* v = std::getenv("GLMRT_B200_NO_PDL");
+    return !(v != nullptr && v[0] != '\0' && v[0] != '0');
+  }();
+  return on;
 }
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 uint64_t launches_total() { return g_launches.load(std::memory_order_relaxed); }

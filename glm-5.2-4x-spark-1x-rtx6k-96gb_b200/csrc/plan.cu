@@ -20,6 +20,7 @@ constexpr int kPlanThreads = 1024;
 constexpr int kMaxLocalExperts = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
+  pdl_launch_dependents();
   __shared__ int cnt[kMaxLocalExperts];
   __shared__ int base[kMaxLocalExperts];
   __shared__ int s_error;
@@ -27,6 +28,7 @@ __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
   for (int i = threadIdx.x; i < local_experts; i += kPlanThreads) cnt[i] = 0;
   if (threadIdx.x == 0) s_error = 0;
   __syncthreads();
+  pdl_wait();   // the routes come from the router's kernels
   const int n = a.rows * a.top_k;
   for (int r = threadIdx.x; r < n; r += kPlanThreads) {
     const uint32_t e = a.topk_indices[r];
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
 glmrt_status_t launch_route_plan(const PlanArgs& a, cudaStream_t stream) {
   const int n = a.rows * a.top_k;
   if (n <= 8192) {   // one CTA, one launch
-    route_plan_kernel<<<1, kPlanThreads, 0, stream>>>(a);
+    launch_pdl(route_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, a);
     GLMRT_LAUNCH_CHECK("route_plan_kernel");
     return GLMRT_STATUS_OK;
   }

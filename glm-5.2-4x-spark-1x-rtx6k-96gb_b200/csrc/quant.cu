@@ -205,6 +205,8 @@ unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / 
 constexpr int kFusedThreads = 256;   // measured faster than one thread per 16-element block (384 for hidden 6144)
 __global__ void __launch_bounds__(kFusedThreads)
 quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ uint4 row_img[];
   uint8_t* img = reinterpret_cast<uint8_t*>(row_img);
   const int row = blockIdx.x;
@@ -259,7 +261,7 @@ bool quantize_dispatch_supported(const uint16_t* in, const DispatchArgs& a) {
 
 glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& a, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(a.hidden) / 2 + a.hidden / 16;
-  quantize_dispatch_kernel<<<a.rows, kFusedThreads, smem, stream>>>(in, a);
+  launch_pdl(quantize_dispatch_kernel, dim3(a.rows), dim3(kFusedThreads), smem, stream, in, a);
   GLMRT_LAUNCH_CHECK("quantize_dispatch_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -104,6 +104,8 @@ template <typename WT>
 __global__ void __launch_bounds__(kSmallThreads)
 router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict__ w, float* __restrict__ logits,
                            int rows, int hidden, int experts, int chunk_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float partial[kSmallWarps][kSmallChunkRows][kSmallExperts];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int e0 = blockIdx.x * kSmallExperts;
@@ -185,6 +187,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
                                      float* __restrict__ topk_weights, int rows, int experts, int top_k,
                                      float scaling, int splits, RouterCountTail tail) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   const int warps = blockDim.x / 32;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -321,11 +325,11 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
     const dim3 ctas(static_cast<unsigned>((experts + kSmallExperts - 1) / kSmallExperts),
                     static_cast<unsigned>((r + chunk_rows - 1) / chunk_rows));
     if (weight_bf16)
-      router_logits_small_kernel<uint16_t><<<ctas, kSmallThreads, 0, stream>>>(
-          static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e, chunk_rows);
+      launch_pdl(router_logits_small_kernel<uint16_t>, ctas, dim3(kSmallThreads), 0, stream,
+                 static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e, chunk_rows);
     else
-      router_logits_small_kernel<float><<<ctas, kSmallThreads, 0, stream>>>(
-          static_cast<const uint16_t*>(hidden), static_cast<const float*>(weight), logits, r, h, e, chunk_rows);
+      launch_pdl(router_logits_small_kernel<float>, ctas, dim3(kSmallThreads), 0, stream,
+                 static_cast<const uint16_t*>(hidden), static_cast<const float*>(weight), logits, r, h, e, chunk_rows);
   } else if (hidden_bf16 && weight_bf16)
     router_logits_kernel<uint16_t, uint16_t><<<grid, kTM * kTN, 0, stream>>>(
         static_cast<const uint16_t*>(hidden), static_cast<const uint16_t*>(weight), logits, r, h, e);
@@ -348,9 +352,9 @@ glmrt_status_t launch_router_select(const float* logits, const float* bias, uint
   RouterCountTail t{};
   if (tail != nullptr) t = *tail;
   const size_t smem = static_cast<size_t>(warps) * 2 * experts * sizeof(float);
-  router_select_kernel<<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, smem, stream>>>(
-      logits, bias, idx, scores, weights, static_cast<int>(rows), static_cast<int>(experts),
-      static_cast<int>(top_k), scaling, splits, t);
+  launch_pdl(router_select_kernel, dim3(static_cast<unsigned>((rows + warps - 1) / warps)), dim3(warps * 32), smem, stream,
+             logits, bias, idx, scores, weights, static_cast<int>(rows), static_cast<int>(experts),
+             static_cast<int>(top_k), scaling, splits, t);
   GLMRT_LAUNCH_CHECK("router_select_kernel");
   return GLMRT_STATUS_OK;
 }
