@@ -29,13 +29,24 @@ struct Fc2Stage {
   static constexpr int kRowsPerStore = 32 / kLanesPerRow;
 };
 
+// Sixteen bytes of bf16 pairs added to global memory, each 16-bit lane rounded to nearest even
+// (one instruction instead of a load, eight additions and a store; performed by the L2).
+__device__ __forceinline__ void red_add_bf16x8(void* dst, const uint4& v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // t_acc: tensor-memory address (lane quadrant and first column) of the warp's 128 columns;
 // dst: this lane's destination (row pointer plus the tile's first feature) or nullptr for a slot
 // without a token; stage: the warp's Fc2Stage<kPass>::kBytesPerWarp bytes; release(): called by
 // lane 0 once all 128 columns are in registers, hands the accumulator back to the MMA issuer.
-template <int kPass, typename Release>
+// kFused: the destination is the token's row of the layer output and `weight2` holds the route
+// weight as a bf16 pair: bf16(weight * bf16(y)) is ADDED to the destination (the weighted
+// scatter-add combine of moe_ref.py:35-36 inside the down projection; the products are rounded as
+// the oracle rounds them, the sums in the order the routes happen to finish).
+template <int kPass, bool kFused = false, typename Release>
 __device__ __forceinline__ void fc2_emit_128_columns(uint32_t t_acc, float s2, uint16_t* dst, uint8_t* stage, int lane,
-                                                     Release&& release) {
+                                                     Release&& release, uint32_t weight2 = 0u) {
   using S = Fc2Stage<kPass>;
   uint8_t* mine = stage + lane * S::kPitch;
   const int sub = lane / S::kLanesPerRow, piece = lane % S::kLanesPerRow;
@@ -59,6 +70,7 @@ __device__ __forceinline__ void fc2_emit_128_columns(uint32_t t_acc, float s2, u
         const __nv_bfloat162 p = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(y[q][2 * i]), s2),
                                                        __fmul_rn(__uint_as_float(y[q][2 * i + 1]), s2));
         w[half][q][i] = *reinterpret_cast<const uint32_t*>(&p);
+        if (kFused) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(w[half][q][i]) : "r"(weight2), "r"(w[half][q][i]));
       }
     }
   }
@@ -81,7 +93,10 @@ __device__ __forceinline__ void fc2_emit_128_columns(uint32_t t_acc, float s2, u
       const int row = S::kRowsPerStore * r + sub;
       const unsigned long long p = __shfl_sync(0xffffffffu, my_dst, row);
       const uint4 v = *reinterpret_cast<const uint4*>(stage + row * S::kPitch + piece * 16);
-      if (p != 0ull) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p) + pass * kPass * 2 + piece * 16) = v;
+      if (p != 0ull) {
+        uint8_t* where = reinterpret_cast<uint8_t*>(p) + pass * kPass * 2 + piece * 16;
+        if (kFused) red_add_bf16x8(where, v); else *reinterpret_cast<uint4*>(where) = v;
+      }
     }
   }
 }

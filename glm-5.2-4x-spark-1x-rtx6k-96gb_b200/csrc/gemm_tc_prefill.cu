@@ -85,7 +85,9 @@ struct PfCfg {
       static_cast<size_t>(kStages) * kStageBytes + 1024 + 256 + kChunkCache * sizeof(Chunk) + kOutBytes;
 };
 
-template <bool kFC1, int kWN>
+// kFusedCombine (FC2 only): results are not stored as one row per route but added, weighted, into
+// the token's row of the layer output (a.slot_out holds those rows, a.slot_weight the weights).
+template <bool kFC1, int kWN, bool kFusedCombine = false>
 __global__ void __launch_bounds__(PfCfg<kFC1, kWN>::kThreads, 1)
 expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act,
                           const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1) {
@@ -288,6 +290,7 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
       const float s2a = a.scale2[ch.expert * 3 + (kFC1 ? 0 : 2)];
       const float s2b = kFC1 ? a.scale2[ch.expert * 3 + 1] : 0.0f;
       uint16_t* dst = (!kFC1 && valid) ? a.slot_out[slot] : nullptr;
+      const uint32_t weight2 = (kFusedCombine && valid) ? a.slot_weight[slot] : 0u;
       if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 2, it);
       if (!mbar_wait_warp(&acc_full[abuf], aphase, abort_flag)) { alive = false; break; }
       tc_fence_after();
@@ -322,9 +325,10 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
           }
         }
       } else {
-        fc2_emit_128_columns<128>(t_acc + part * 128, s2a, valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr,
-                             out_stage + static_cast<size_t>(warp - 2) * Fc2Stage<128>::kBytesPerWarp, lane,
-                             [&] { mbar_arrive(&acc_empty[abuf]); });
+        uint16_t* where = valid ? dst + ft * C::kFeatPerTile + part * 128 : nullptr;
+        uint8_t* park = out_stage + static_cast<size_t>(warp - 2) * Fc2Stage<128>::kBytesPerWarp;
+        fc2_emit_128_columns<128, kFusedCombine>(t_acc + part * 128, s2a, where, park, lane,
+                                                 [&] { mbar_arrive(&acc_empty[abuf]); }, weight2);
       }
       if (warp == 2 && lane == 0) GLMRT_TRACE_TILE(kFC1 ? 0 : 1, 5, it);
       if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
@@ -344,13 +348,13 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   if (!kFC1 && a.signal.ticket != nullptr && aborted == 0u && !step_failed) ep_signal_last_cta(a.signal);
 }
 
-template <bool kFC1, int kWN>
+template <bool kFC1, int kWN, bool kFusedCombine = false>
 glmrt_status_t launch_tokens(const FfnArgs& a, const CUtensorMap& act, const CUtensorMap& w0, const CUtensorMap& w1,
                              int sm_count, cudaStream_t stream) {
   using C = PfCfg<kFC1, kWN>;
   static std::atomic<uint64_t> configured{0};
-  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_tokens_kernel<kFC1, kWN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)"));
-  launch_pdl(expert_gemm_tokens_kernel<kFC1, kWN>, dim3(sm_count), dim3(C::kThreads), C::kSmemBytes, stream, a, act, w0, w1);
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_tokens_kernel<kFC1, kWN, kFusedCombine>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_tokens_kernel)"));
+  launch_pdl(expert_gemm_tokens_kernel<kFC1, kWN, kFusedCombine>, dim3(sm_count), dim3(C::kThreads), C::kSmemBytes, stream, a, act, w0, w1);
   GLMRT_LAUNCH_CHECK("expert_gemm_tokens_kernel");
   return GLMRT_STATUS_OK;
 }
@@ -361,6 +365,7 @@ glmrt_status_t launch_fc1_tc_prefill(const FfnArgs& a, const TensorMaps& m, int 
   return launch_tokens<true, 256>(a, m.act1, m.gate, m.up, sm_count, stream);
 }
 glmrt_status_t launch_fc2_tc_prefill(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
+  if (a.slot_weight != nullptr) return launch_tokens<false, 128, true>(a, m.act2, m.down, m.down, sm_count, stream);
   return launch_tokens<false, 128>(a, m.act2, m.down, m.down, sm_count, stream);
 }
 

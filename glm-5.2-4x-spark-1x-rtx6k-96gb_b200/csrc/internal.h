@@ -125,6 +125,11 @@ struct DispatchArgs {
   uint16_t* route_rows;          // bf16 [rows * top_k, H]: destination rows of FC2
   uint16_t** slot_out;           // [max_slots] destination row pointer per slot
   uint8_t* payload_out;          // fused quantise + dispatch only: where the payload rows are written
+  // Fused combine (the down GEMM adds weight * row straight into the layer output): a slot's
+  // destination is then its token's output row and its route weight travels beside it.
+  uint16_t* combine_out = nullptr;       // [rows, hidden] bf16 layer output, or nullptr: per-route rows
+  const float* topk_weights = nullptr;   // [rows * top_k]
+  uint32_t* slot_weight = nullptr;       // [max_slots] the route weight as a bf16 pair
 };
 glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
 // quant.cu: quantises bf16 rows [rows, hidden] and dispatches them in one kernel (payload rows
@@ -222,6 +227,7 @@ struct FfnArgs {
   const uint8_t* act1_codes; const uint8_t* act1_sf;                                   // dispatch output
   uint8_t* act2_codes; uint8_t* act2_sf;                                               // FC1 output
   uint16_t* const* slot_out;                                                           // FC2 destination rows
+  const uint32_t* slot_weight = nullptr;   // non-null: FC2 adds weight * row into the destination (fused combine)
   const Chunk* chunks; const uint32_t* counters;
   int hidden, inter, max_chunks, chunk_tokens;
   uint32_t* error_word;

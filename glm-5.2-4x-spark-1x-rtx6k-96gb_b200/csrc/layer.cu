@@ -79,6 +79,7 @@ struct Layer {
   uint8_t *act1_codes = nullptr, *act1_sf = nullptr, *act2_codes = nullptr, *act2_sf = nullptr;
   uint16_t* route_rows = nullptr;
   uint16_t** slot_out = nullptr;
+  uint32_t* slot_weight = nullptr;   // route weight per slot (fused combine of large batches)
   uint16_t *hidden_stage = nullptr, *out_stage = nullptr;
   // scratch for weight loading
   float* wtmp = nullptr;
@@ -235,6 +236,19 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   // The plan needs only the routes, so it runs first and the rows are quantised and dispatched by
   // one kernel (its time is reported as the dispatch stage, the quantise stage then reads 0).
   const bool fused = hidden != nullptr && quantize_dispatch_supported(hidden, d);
+  // Large batches with all experts local: the down projection adds weight * row straight into the
+  // output rows (no per-route rows, no combine pass).  Batches of at most 256 rows keep the
+  // ordered combine: there a row must not depend on its batch, bit for bit.
+  const bool fused_combine = fused && chunk_tokens == 128 && c.ep_world == 1 && residual == nullptr && shared == nullptr &&
+                             l->slot_weight != nullptr &&
+                             !(c.flags & (GLMRT_B200_LAYER_ENGINE_SIMT | GLMRT_B200_LAYER_ORDERED_COMBINE));
+  if (fused_combine) {
+    d.combine_out = out;
+    d.topk_weights = l->topk_w;
+    d.slot_weight = l->slot_weight;
+    cudaError_t zerr = cudaMemsetAsync(out, 0, rows * static_cast<size_t>(c.hidden_dim) * 2, stream);
+    if (zerr != cudaSuccess) return fail_cuda(GLMRT_STATUS_COPY_FAILED, "clear the output rows", zerr);
+  }
   mark(l, GLMRT_B200_STAGE_QUANTIZE, stream);
   if (!fused && hidden != nullptr)
     GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
@@ -252,6 +266,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
   GLMRT_RETURN_IF_ERROR(fused ? launch_quantize_dispatch(hidden, d, stream) : launch_dispatch(d, stream));
   FfnArgs f = ffn_args(l, chunk_tokens);
+  if (fused_combine) f.slot_weight = l->slot_weight;
   mark(l, GLMRT_B200_STAGE_FC1, stream);
   if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
     GLMRT_RETURN_IF_ERROR(launch_fc1_simt(f, stream));
@@ -273,9 +288,10 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   mark(l, GLMRT_B200_STAGE_COMBINE, stream);
   // routes without a slot (another shard's expert, a "no route" entry, a refused plan) are skipped
   const int32_t* mask = l->route_slot;
-  GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
-                                              static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream,
-                                              residual, shared));
+  if (!fused_combine)
+    GLMRT_RETURN_IF_ERROR(launch_combine_routes(l->route_rows, l->topk_w, mask, out, static_cast<int>(rows),
+                                                static_cast<int>(c.top_k), static_cast<int>(c.hidden_dim), stream,
+                                                residual, shared));
   mark(l, GLMRT_B200_STAGE_COUNT, stream);
   l->stage_valid = l->profiling;
   l->last_rows = static_cast<uint32_t>(rows);
@@ -381,6 +397,7 @@ glmrt_status_t alloc_workspace(Layer* l) {
   A(dev_alloc(b, &l->route_rows, routes * H));
   // destinations start out null: a slot nobody dispatched to is skipped by the FC2 epilogues
   A(dev_alloc(b, &l->slot_out, static_cast<size_t>(l->max_slots), true));
+  if (c.max_tokens > 256 && c.ep_world == 1) A(dev_alloc(b, &l->slot_weight, static_cast<size_t>(l->max_slots), true));
   A(dev_alloc(b, &l->hidden_stage, T * H));
   A(dev_alloc(b, &l->out_stage, T * H));
   A(dev_alloc(b, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));

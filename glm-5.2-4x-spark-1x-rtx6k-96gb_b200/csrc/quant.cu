@@ -247,7 +247,15 @@ quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
       for (int i = threadIdx.x; i < code_bytes / 16; i += kFusedThreads) dst4[i] = row_img[i];
       for (int w = threadIdx.x; w < kblocks / 4; w += kFusedThreads)
         *reinterpret_cast<uint32_t*>(a.act_sf + sf_tile_offset(slot, 4 * w, kblocks)) = sf_words[w];
-      if (threadIdx.x == 0) a.slot_out[slot] = a.route_rows + static_cast<size_t>(route) * a.hidden;
+      if (threadIdx.x == 0) {
+        if (a.combine_out != nullptr) {
+          a.slot_out[slot] = a.combine_out + static_cast<size_t>(row) * a.hidden;
+          const uint32_t wb = f32_to_bf16_rne(a.topk_weights[route]);
+          a.slot_weight[slot] = wb | (wb << 16);
+        } else {
+          a.slot_out[slot] = a.route_rows + static_cast<size_t>(route) * a.hidden;
+        }
+      }
     }
   }
 }

@@ -33,7 +33,8 @@ def sf_tile_offsets(rows: int, kblocks: int) -> np.ndarray:
 class MoeLayer:
     """One routed-MoE layer resident on the current CUDA device.
 
-    ``engine``: "tc" (tcgen05 tensor-core kernels, the product path), "tc2" / "tc2-fc1" / "tc2-fc2"
+    ``engine``: "tc" (tcgen05 tensor-core kernels, the product path), "tc-ordered" (the same with the
+    ordered combine pass also above 256 rows), "tc2" / "tc2-fc1" / "tc2-fc2"
     (the same with both / one of the expert GEMMs of large batches on CTA pairs) or "simt" (the float64-accumulating verification kernels).
     """
 
@@ -41,8 +42,8 @@ class MoeLayer:
                  ep_world: int = 1, ep_rank: int = 0, engine: str = "tc", scaling: float = 2.5,
                  lib: N.NativeLibrary | None = None):
         self.lib = lib or N.library()
-        flags = {"tc": 0, "tc2": N.LAYER_PAIR_TILES, "tc2-fc1": N.LAYER_PAIR_FC1, "tc2-fc2": N.LAYER_PAIR_FC2,
-                 "simt": N.LAYER_ENGINE_SIMT}[engine]
+        flags = {"tc": 0, "tc-ordered": N.LAYER_ORDERED_COMBINE, "tc2": N.LAYER_PAIR_TILES,
+                 "tc2-fc1": N.LAYER_PAIR_FC1, "tc2-fc2": N.LAYER_PAIR_FC2, "simt": N.LAYER_ENGINE_SIMT}[engine]
         self.cfg = N.MoeConfig(hidden, inter, experts, top_k, max_tokens, ep_world, ep_rank, flags, scaling)
         self.hidden, self.inter, self.experts, self.top_k = hidden, inter, experts, top_k
         self.max_tokens, self.ep_world, self.ep_rank = max_tokens, ep_world, ep_rank

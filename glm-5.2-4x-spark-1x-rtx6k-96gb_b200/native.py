@@ -67,6 +67,7 @@ class LayerStats(C.Structure):
                 ("reserved", C.c_uint32)]
 
 
+LAYER_ORDERED_COMBINE = 8
 LAYER_ENGINE_SIMT = 1
 LAYER_PAIR_FC1 = 2
 LAYER_PAIR_FC2 = 4

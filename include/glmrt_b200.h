@@ -411,6 +411,13 @@ enum {
   GLMRT_B200_LAYER_PAIR_FC2 = 4u,    /* FC1 and/or FC2 on CTA pairs (tcgen05 cta_group::2) instead of one-CTA
                                         tiles; bit-identical results */
   GLMRT_B200_LAYER_PAIR_TILES = 6u,  /* both */
+  GLMRT_B200_LAYER_ORDERED_COMBINE = 8u, /* batches above 256 rows: keep one bf16 row per route and sum them in
+                                        route order in a pass of its own (bit-reproducible), instead of letting
+                                        the down projection add weight * row into the output rows as the routes
+                                        finish (the reference has both forms too: fixed-order top-k sum,
+                                        native/cuda/kernels/b12x_direct.cu:203-219, and in-kernel accumulation,
+                                        b12x_direct.cu:157-165,1291-1309, mlp.cu:275-314).  Batches of at most 256
+                                        rows always use the ordered form. */
 };
 
 glmrt_status_t glmrt_b200_moe_layer_create(const glmrt_b200_moe_config_t* config, void** out_layer);

@@ -140,9 +140,10 @@ def test_forward_routed_and_host_entry_points(pkg, small_layer):
 def test_forward_residual_folds_the_layer_output_into_the_combine(pkg, small_layer, T):
     """out = bf16(residual + bf16(shared + routed)) computed inside the combine kernel equals the
     plain forward followed by the oracle's residual step, bit for bit; without a shared-expert
-    row it is bf16(residual + routed)."""
+    row it is bf16(residual + routed).  (The residual fold lives in the ordered combine pass, so
+    the plain forward it is compared with uses that pass too, also at T = 300.)"""
     K = 4
-    layer = make(pkg, small_layer, K, 512, "tc")
+    layer = make(pkg, small_layer, K, 512, "tc-ordered")
     hid = O.make_hidden(2300 + T, T, 512)
     rng = np.random.default_rng(T)
     res = O.bf16_round(rng.standard_normal((T, 512), np.float32) * 2)
@@ -184,13 +185,15 @@ def test_decode_step_replays_from_a_cuda_graph(pkg, small_layer):
 
 
 def test_full_size_prefill_is_row_permutation_equivariant(pkg):
-    """At the full prefill size (GLM-5.2 layer, T = 8192) no CPU oracle is in reach; the property
-    checked instead needs no reference values: a token's result depends on its own row only, so
-    permuting the rows of the batch permutes the rows of the output bit for bit, and 64 of the
-    rows run alone (decode kernels) agree with their rows in the large batch within the gate."""
+    """At the full prefill size (GLM-5.2 layer, T = 8192) a property that needs no reference
+    values: a token's result depends on its own row only, so with the ordered combine permuting
+    the rows of the batch permutes the rows of the output bit for bit, and 64 of the rows run
+    alone (decode kernels) agree with their rows in the large batch within the gate.  The default
+    form (the down projection adds into the output rows as routes finish) sums the same products
+    in a different order: it must agree with the ordered form within bf16 accumulation noise."""
     from glmrt_b200.layer import MoeLayer
     H, I, E, K, T = 6144, 2048, 256, 8, 8192
-    layer = MoeLayer(H, I, E, K, max_tokens=T)
+    layer = MoeLayer(H, I, E, K, max_tokens=T, engine="tc-ordered")
     layer.fill_synthetic(11, 0.02)
     g = torch.Generator(device="cpu").manual_seed(5)
     layer.set_router((torch.randn(E, H, generator=g) * 0.02), torch.zeros(E))
@@ -207,6 +210,23 @@ def test_full_size_prefill_is_row_permutation_equivariant(pkg):
     err = O.rel_l2_per_token(to_bits(small), to_bits(out[rows]))
     print(f"T=8192 rows vs the same rows alone: max per-token rel L2 {err.max():.3e}")
     assert err.max() <= 1e-2
+    fused = layer.create_lane()
+    fused_flags = fused.cfg.flags
+    fused.close()
+    assert fused_flags != 0      # lanes inherit the flags of their layer
+    layer.close()
+    del layer
+    torch.cuda.empty_cache()
+    layer = MoeLayer(H, I, E, K, max_tokens=T)          # default: fused combine above 256 rows
+    layer.fill_synthetic(11, 0.02)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    layer.set_router((torch.randn(E, H, generator=g) * 0.02), torch.zeros(E))
+    out_f = layer.forward(x)
+    layer.check()
+    err = O.rel_l2_per_token(to_bits(out_f), to_bits(out))
+    print(f"T=8192 fused combine vs ordered combine: max per-token rel L2 {err.max():.3e}")
+    assert err.max() <= 1e-2
+    assert layer.stats().launches_last_forward == 8      # no combine pass
     layer.close()
 
 
@@ -425,7 +445,8 @@ def test_pair_tiles_match_oracle_and_one_cta_tiles(pkg, small_layer, T):
     oi, ow, oo = O.layer_forward(small_layer, hid, K, mode="O1")
     outs = {}
     for engine in ("tc2", "tc2-fc1", "tc2-fc2", "tc"):
-        layer = make(pkg, small_layer, K, 2048, engine)
+        # the pair kernels write one row per route; the one-CTA reference here does the same
+        layer = make(pkg, small_layer, K, 2048, "tc-ordered" if engine == "tc" else engine)
         out, idx, w = layer.forward(to_dev(hid), want_routes=True)
         layer.check()
         chunks = layer.debug("CHUNKS", np.int32).reshape(-1, 4)
@@ -647,7 +668,7 @@ def test_two_lanes_on_two_streams_match_serial_execution(pkg, small_layer):
     the layer gives when it runs the same batch alone (the reference executor's lanes share the
     resident experts and keep per-lane route tensors)."""
     K = 4
-    layer = make(pkg, small_layer, K, 512)
+    layer = make(pkg, small_layer, K, 512, "tc-ordered")   # bit-equality below needs the ordered combine at T = 300
     lanes = [layer.create_lane(), layer.create_lane()]
     xs = [to_dev(O.make_hidden(600 + i, T, 512)) for i, T in enumerate((300, 40))]
     refs = [to_bits(layer.forward(x)).copy() for x in xs]
