@@ -490,12 +490,34 @@ def prefill_block_single(torch, timer, layer, T, steps, warmup):
     res = timer.run(fwd, steps)
     stage_ms, distinct = profile_stages(lane, fwd, min(steps, 20))
     lane.check()
+    chunks = int(lane.stats().chunks)
     block = prefill_numbers(T, 1, res["ms_per_step"], stage_ms, distinct)
     block["timing"] = f"median of {res['blocks']} blocks of {steps} steps ({res['timed_s']:.2f} s timed)"
+    block["operand_delivery"] = operand_delivery(lane.lib, torch, chunks, stage_ms)
     lane.close()
     del batches, out
     torch.cuda.empty_cache()
     return block
+
+
+def operand_delivery(lib, torch, chunks, stage_ms):
+    """What bounds the token-major expert GEMMs: every CTA must bring 54 KB (FC1: 128 token rows, 128 gate
+    and 128 up rows of 128 bytes, three 2 KB scale groups) or 36 KB (FC2) into shared memory per
+    256-element K stage.  Bytes delivered / kernel time, beside the rate a probe kernel that issues the
+    same copies and consumes nothing reaches on this GPU with an L2-resident working set."""
+    import ctypes as C
+    gbs, ms = C.c_float(), C.c_float()
+    lib.call("glmrt_b200_probe_operand_delivery", C.c_size_t(48 << 20), C.c_uint32(4), C.c_uint32(8),
+             C.byref(gbs), C.byref(ms), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    fc1_bytes = chunks * (I // 128) * (H // 256) * 55296
+    fc2_bytes = chunks * (H // 128) * (I // 256) * 36864
+    fc1 = fc1_bytes / (stage_ms["fc1"] * 1e-3) / 1e9
+    fc2 = fc2_bytes / (stage_ms["fc2"] * 1e-3) / 1e9
+    return {"probe_l2_to_smem_gbs": float(gbs.value), "work_items_128_tokens": chunks,
+            "fc1_bytes_into_smem": fc1_bytes, "fc1_gbs": fc1, "fc1_frac_of_probe": fc1 / float(gbs.value),
+            "fc2_bytes_into_smem": fc2_bytes, "fc2_gbs": fc2, "fc2_frac_of_probe": fc2 / float(gbs.value),
+            "note": "the probe runs with the tensor pipe idle and the SM clock at its maximum; under the power cap of a "
+                    "GEMM the same per-clock rate delivers proportionally less"}
 
 
 def small_decode_block(torch, timer, layer, T, steps, warmup):
@@ -540,7 +562,7 @@ def ep_parity(torch, dist, EP, MoeLayer, layer, rank, world, T, seed=123):
     verdict = None
     if rank == 0:
         from oracle import glmrt_oracle as O   # checker only: per-token relative L2 of two bf16 arrays
-        single = MoeLayer(H, I, E, K_TOP, max_tokens=T)
+        single = MoeLayer(H, I, E, K_TOP, max_tokens=T, engine="tc-ordered")   # one row per route, summed in order, like the exchange
         single.fill_synthetic(0, 0.02)
         single.set_router(router_weight(torch), torch.zeros(E))
         ref = single.forward(x.cuda()).cpu().view(torch.int16).numpy()

@@ -222,10 +222,18 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
         const int slot = s_base[e] + slot_of_position(s_mine[e] + pos, a.chunk_tokens);
         uint4* dst4 = reinterpret_cast<uint4*>(a.peer_act_codes[owner] + static_cast<size_t>(slot) * code_bytes);
         for (int i = threadIdx.x; i < code_bytes / 16; i += kPushThreads) dst4[i] = reinterpret_cast<const uint4*>(img)[i];
-        // scales leave as 4-byte words: four consecutive blocks of a slot are contiguous in the tiled layout
-        uint8_t* sf = a.peer_act_sf[owner];
-        for (int j = threadIdx.x; j < kblocks / 4; j += kPushThreads)
-          *reinterpret_cast<uint32_t*>(sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
+        if (a.chunk_tokens >= 128) {
+          // prefill-sized step: the slot's scale bytes leave as one contiguous row, the owner re-tiles
+          uint4* srow = reinterpret_cast<uint4*>(a.peer_act_sf_rows[owner] + static_cast<size_t>(slot) * kblocks);
+          const uint4* s4 = reinterpret_cast<const uint4*>(img + code_bytes);
+          for (int j = threadIdx.x; j < kblocks / 16; j += kPushThreads) srow[j] = s4[j];
+        } else {
+          // decode-sized step: 4-byte words straight into the tiled layout (four consecutive blocks of
+          // a slot are contiguous there)
+          uint8_t* sf = a.peer_act_sf[owner];
+          for (int j = threadIdx.x; j < kblocks / 4; j += kPushThreads)
+            *reinterpret_cast<uint32_t*>(sf + sf_tile_offset(slot, 4 * j, kblocks)) = sf_words[j];
+        }
         if (threadIdx.x == 0) {
           a.peer_slot_out[owner][slot] = a.my_rows_in_peer[owner] + static_cast<size_t>(route) * hidden_dim;
           p.route_slot[route] = slot;
@@ -261,6 +269,33 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   }
 }
 
+// Owner side of a prefill-sized push: wait for every rank's rows, then move the scale rows of the
+// occupied slots into the tiled layout.  One thread per (slot, group of four blocks).
+__global__ void __launch_bounds__(256)
+ep_retile_scales_kernel(EpWait w, const uint8_t* __restrict__ sf_rows, uint8_t* __restrict__ sf_tiled, int kblocks,
+                        const uint32_t* counters, uint32_t* error_word, uint32_t* chunk_count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ uint32_t s_err;
+  if (threadIdx.x == 0) {
+    s_err = ep_wait_all_serial(w);
+    if (s_err != 0u) {
+      atomicOr(error_word, s_err);
+      if (blockIdx.x == 0) *chunk_count = 0;   // never start expert work on rows that did not arrive
+    }
+  }
+  __syncthreads();
+  if (s_err != 0u) return;
+  const int slots = static_cast<int>(counters[kCntSlots]);
+  const int words = kblocks / 4;
+  const long long total = static_cast<long long>(slots) * words;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += 256ll * gridDim.x) {
+    const int slot = static_cast<int>(i / words), j = static_cast<int>(i % words);
+    const uint32_t v = reinterpret_cast<const uint32_t*>(sf_rows + static_cast<size_t>(slot) * kblocks)[j];
+    *reinterpret_cast<uint32_t*>(sf_tiled + sf_tile_offset(slot, 4 * j, kblocks)) = v;
+  }
+}
+
 // Stand-alone wait / signal for engines whose kernels do not carry them (the SIMT verification engine).
 __global__ void ep_wait_kernel(EpWait w, uint32_t* error_word, uint32_t* chunk_count) {
   if (threadIdx.x != 0) return;
@@ -278,6 +313,14 @@ __global__ void ep_signal_kernel(EpSignal s, const uint32_t* error_word) {
 
 }  // namespace
 
+glmrt_status_t launch_ep_retile_scales(const EpArgs& a, const uint8_t* sf_rows, uint8_t* sf_tiled, int kblocks,
+                                       const uint32_t* counters, uint32_t* error_word, uint32_t* chunk_count,
+                                       cudaStream_t stream) {
+  launch_pdl(ep_retile_scales_kernel, dim3(592), dim3(256), 0, stream, ep_wait_dispatch(a), sf_rows, sf_tiled, kblocks,
+             counters, error_word, chunk_count);
+  GLMRT_LAUNCH_CHECK("ep_retile_scales_kernel");
+  return GLMRT_STATUS_OK;
+}
 glmrt_status_t launch_ep_wait(const EpWait& w, uint32_t* error_word, uint32_t* chunk_count, cudaStream_t stream) {
   ep_wait_kernel<<<1, 32, 0, stream>>>(w, error_word, chunk_count);
   GLMRT_LAUNCH_CHECK("ep_wait_kernel");
@@ -311,8 +354,8 @@ RouterCountTail ep_count_tail(const EpArgs& a) {
 
 glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const uint16_t* hidden, uint8_t* payload,
                                        int rows, int top_k, int hidden_dim, cudaStream_t stream) {
-  if (top_k > 64 || hidden_dim % 128 != 0)
-    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: top_k must be <= 64 and hidden a multiple of 128");
+  if (top_k > 64 || hidden_dim % 256 != 0)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: top_k must be <= 64 and hidden a multiple of 256");
   const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
   if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
   // every CTA derives the layout once, so large batches walk their rows with a bounded grid

@@ -26,6 +26,7 @@ enum Counter : int {
   kCntDistinct = 3,
   kCntLocalRoutes = 4,
   kCntRouterError = 5,   // error word of the tensor-core router kernel (cleared by that kernel)
+  kCntTicket = 6,        // last-CTA ticket of the router's selection kernel (zero between launches)
   kCntWords = 8,
 };
 
@@ -44,19 +45,8 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
                              cudaStream_t stream, const RouterCountTail* tail = nullptr);
 
 // splits in 2..8: `logits` holds that many partial tables [splits][rows][experts], added in order
-// Optional tail of the selection kernel in the expert-parallel path: the last CTA to finish counts
-// this rank's routes per expert, stores the histogram into every rank's count table, clears this
-// rank's per-expert cursors and the layer's error word, and raises the per-peer "counts" epoch flag.
 constexpr int kEpMaxWorld = 8;
-struct RouterCountTail {
-  int world = 0;                         // 0: no tail
-  uint32_t epoch = 0;
-  int32_t* peer_counts[kEpMaxWorld];     // this rank's row of each rank's count table
-  uint32_t* peer_flags[kEpMaxWorld];     // this rank's "counts" flag at each rank
-  int32_t* cursor;                       // [experts], local
-  uint32_t* error_word;                  // local
-  int32_t* ticket;                       // local, zero between launches
-};
+struct RouterCountTail;
 glmrt_status_t launch_router_select(const float* logits, const float* bias, uint32_t* idx, float* scores,
                                     float* weights, size_t rows, size_t experts, size_t top_k, float scaling,
                                     cudaStream_t stream, int splits = 1, const RouterCountTail* tail = nullptr);
@@ -114,6 +104,22 @@ struct PlanArgs {
   Chunk* chunks;                 // [max_chunks]
   uint32_t* counters;            // [kCntWords]
 };
+// Optional tails of the router's selection kernel, run by the last CTA of its grid to finish.
+//   expert-parallel path (world > 0): count this rank's routes per expert, store the histogram into
+//     every rank's count table, clear this rank's per-expert cursors and the layer's error word, and
+//     raise the per-peer "counts" epoch flag;
+//   one GPU, decode-sized batches (do_plan): build the route plan right there (one launch less).
+struct RouterCountTail {
+  int world = 0;                         // 0: no histogram publish
+  uint32_t epoch = 0;
+  int32_t* peer_counts[kEpMaxWorld];     // this rank's row of each rank's count table
+  uint32_t* peer_flags[kEpMaxWorld];     // this rank's "counts" flag at each rank
+  int32_t* cursor;                       // [experts], local
+  uint32_t* error_word;                  // local
+  int32_t* ticket = nullptr;             // local, zero between launches
+  int do_plan = 0;
+  PlanArgs plan;
+};
 glmrt_status_t launch_route_plan(const PlanArgs& a, cudaStream_t stream);
 
 struct DispatchArgs {
@@ -162,6 +168,7 @@ struct EpArgs {
   EpControl* peer_ctrl[kEpMaxWorld];
   uint8_t* peer_act_codes[kEpMaxWorld];
   uint8_t* peer_act_sf[kEpMaxWorld];
+  uint8_t* peer_act_sf_rows[kEpMaxWorld];   // row-major scale staging of prefill-sized pushes
   uint16_t** peer_slot_out[kEpMaxWorld];
   uint16_t* my_rows_in_peer[kEpMaxWorld];   // this rank's route_rows as addressed from each peer
 };
@@ -188,6 +195,12 @@ struct EpSignal {
 };
 glmrt_status_t launch_ep_wait(const EpWait& w, uint32_t* error_word, uint32_t* chunk_count, cudaStream_t stream);
 glmrt_status_t launch_ep_signal(const EpSignal& s, const uint32_t* error_word, cudaStream_t stream);
+// Prefill-sized steps: the home ranks push each slot's scale bytes as one contiguous row (a few
+// full lines over NVLink instead of a hundred 4-byte words); the owner waits for the pushes and
+// moves the rows of its occupied slots into the tiled layout the GEMM reads.
+glmrt_status_t launch_ep_retile_scales(const EpArgs& a, const uint8_t* sf_rows, uint8_t* sf_tiled, int kblocks,
+                                       const uint32_t* counters, uint32_t* error_word, uint32_t* chunk_count,
+                                       cudaStream_t stream);
 EpWait ep_wait_dispatch(const EpArgs& a);
 EpWait ep_wait_combine(const EpArgs& a);
 EpSignal ep_signal_combine(const EpArgs& a);

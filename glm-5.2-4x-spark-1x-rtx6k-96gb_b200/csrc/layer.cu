@@ -93,8 +93,9 @@ struct Layer {
   bool profiling = false;
   cudaEvent_t stage_events[GLMRT_B200_STAGE_COUNT + 1] = {};
   bool stage_valid = false;
-  // expert-parallel exchange (control block in the workspace)
+  // expert-parallel exchange (control block and scale staging in the workspace)
   EpControl* ep_ctrl = nullptr;
+  uint8_t* act1_sf_rows = nullptr;
 };
 
 void mark(Layer* l, int stage_begin, cudaStream_t s) {
@@ -214,10 +215,46 @@ glmrt_status_t run_router(Layer* l, const void* hidden, size_t rows, cudaStream_
                        l->topk_w, rows, c.hidden_dim, c.experts, c.top_k, c.routed_scaling, s, tail);
 }
 
+PlanArgs plan_args(const Layer* l, size_t rows, int chunk_tokens) {
+  const auto& c = l->cfg;
+  PlanArgs p{};
+  p.topk_indices = l->topk_idx;
+  p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
+  p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
+  p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
+  p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
+  p.expert_base = l->expert_base; p.block_hist = l->block_hist;
+  p.chunks = l->chunks; p.counters = l->counters;
+  return p;
+}
+
+// Decode-sized batches on one GPU: the route plan runs as the tail of the router's selection kernel.
+bool plan_in_router_tail(const Layer* l, size_t rows) { return rows <= 256 && l->cfg.ep_world == 1; }
+
+// Router followed by the routed path, for the entry points that route themselves.
+glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream,
+                          const uint16_t* residual = nullptr, const uint16_t* shared = nullptr, bool plan_done = false);
+glmrt_status_t run_router_and_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t s,
+                                     const uint16_t* residual = nullptr, const uint16_t* shared = nullptr) {
+  mark(l, GLMRT_B200_STAGE_ROUTER, s);
+  const bool tail_plan = plan_in_router_tail(l, rows);
+  if (tail_plan) {
+    RouterCountTail tail{};
+    tail.do_plan = 1;
+    tail.plan = plan_args(l, rows, 32);
+    tail.ticket = reinterpret_cast<int32_t*>(l->counters + kCntTicket);
+    GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s, &tail));
+  } else {
+    GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s));
+  }
+  return run_routed(l, hidden, rows, out, s, residual, shared, tail_plan);
+}
+
 // Everything after the router: quantise, plan, dispatch, expert FFN, combine.
 // `hidden` == nullptr: the payload rows are already in l->payload (a request that carried NVFP4 rows).
+// plan_done: the route plan has already been made (by the router's tail).
 glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_t* out, cudaStream_t stream,
-                          const uint16_t* residual = nullptr, const uint16_t* shared = nullptr) {
+                          const uint16_t* residual, const uint16_t* shared, bool plan_done) {
   const auto& c = l->cfg;
   // Work-item size: 32 slots for decode batches (weights on the MMA rows), 128 for prefill (tokens
   // on the MMA rows); on request 256 (GEMMs on CTA pairs) once the average expert receives more than
@@ -254,15 +291,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
     GLMRT_RETURN_IF_ERROR(launch_quantize_rows_payload(hidden, l->payload, rows, c.hidden_dim,
                                                        GLMRT_B200_FP4_RULE_NEAREST_LOW, stream));
   mark(l, GLMRT_B200_STAGE_PLAN, stream);
-  PlanArgs p{};
-  p.topk_indices = l->topk_idx;
-  p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
-  p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
-  p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
-  p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
-  p.expert_base = l->expert_base; p.block_hist = l->block_hist;
-  p.chunks = l->chunks; p.counters = l->counters;
-  GLMRT_RETURN_IF_ERROR(launch_route_plan(p, stream));
+  if (!plan_done) GLMRT_RETURN_IF_ERROR(launch_route_plan(plan_args(l, rows, chunk_tokens), stream));
   mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
   GLMRT_RETURN_IF_ERROR(fused ? launch_quantize_dispatch(hidden, d, stream) : launch_dispatch(d, stream));
   FfnArgs f = ffn_args(l, chunk_tokens);
@@ -333,10 +362,16 @@ void set_geometry(Layer* l) {
   cudaDeviceGetAttribute(&l->sm_count, cudaDevAttrMultiProcessorCount, l->device);
   l->local_experts = static_cast<int>((c.experts - c.ep_rank + c.ep_world - 1) / c.ep_world);
   const size_t E = l->local_experts, T = c.max_tokens, K = c.top_k;
-  const size_t routes = T * K;
+  // Routes this shard's experts may receive in one step.  With all experts local that is T * K.  An
+  // expert-parallel shard receives T * K when the routing is balanced and up to world times that
+  // when every route of every rank goes to its experts; it is sized for twice the balanced load
+  // (popularity ~ rank^-1.2 with the hot experts spread over the ranks gives 1.6), beyond which a
+  // step is refused with kErrSlotOverflow.
+  const size_t routes = c.ep_world > 1 ? T * K * std::min<size_t>(2, c.ep_world) : T * K;
   // Dense work items (128 / 256 slots): every expert's range is rounded up to 128 slots.  Batches of
   // at most 256 rows use 32-slot work items, each in a 128-slot group of its own (expert_slot_span).
-  const size_t decode_routes = std::min<size_t>(T, 256) * K;
+  // (a decode-sized batch is small enough to provide for all of it landing on one shard)
+  const size_t decode_routes = std::min<size_t>(T * c.ep_world, 256) * K;
   const size_t decode_slots = 128 * (std::min(E, decode_routes) + decode_routes / 32 + 1);
   l->max_slots = static_cast<int>(std::max(round_up(routes + E * 127, 128), decode_slots));
   l->max_chunks = static_cast<int>(E + (routes + 31) / 32);
@@ -403,7 +438,10 @@ glmrt_status_t alloc_workspace(Layer* l) {
   A(dev_alloc(b, &l->wtmp, std::max(I * H, static_cast<size_t>(1))));
   A(dev_alloc(b, &l->sftmp, I * H / 16));
   A(dev_alloc(b, &l->amax_tmp, 1, true));
-  if (c.ep_world > 1) A(dev_alloc(b, &l->ep_ctrl, 1, true));
+  if (c.ep_world > 1) {
+    A(dev_alloc(b, &l->ep_ctrl, 1, true));
+    A(dev_alloc(b, &l->act1_sf_rows, static_cast<size_t>(l->max_slots) * H / 16, true));
+  }
   // partial logits of the tensor-core router: largest splits * rows over the batch sizes this
   // workspace can see (splits * tiles <= SM count)
   l->logits_partial = nullptr;
@@ -608,10 +646,8 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_async(void* layer, glmrt_
     return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward: hidden and output must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
   const uint64_t before = launches_total();
-  mark(l, GLMRT_B200_STAGE_ROUTER, s);
-  GLMRT_RETURN_IF_ERROR(run_router(l, hidden_bf16.ptr, rows, s));
-  GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
-                                   static_cast<uint16_t*>(output_bf16.ptr), s));
+  GLMRT_RETURN_IF_ERROR(run_router_and_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                              static_cast<uint16_t*>(output_bf16.ptr), s));
   l->launches_last = static_cast<uint32_t>(launches_total() - before);
   cudaError_t err = cudaSuccess;
   if (topk_indices.ptr != nullptr)
@@ -640,12 +676,10 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_forward_residual_async(
       return fail(GLMRT_STATUS_INVALID_ARGUMENT, "forward_residual: buffers must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
   const uint64_t before = launches_total();
-  mark(l, GLMRT_B200_STAGE_ROUTER, s);
-  GLMRT_RETURN_IF_ERROR(run_router(l, hidden_bf16.ptr, rows, s));
-  GLMRT_RETURN_IF_ERROR(run_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
-                                   static_cast<uint16_t*>(output_bf16.ptr), s,
-                                   static_cast<const uint16_t*>(residual_bf16.ptr),
-                                   static_cast<const uint16_t*>(shared_delta_bf16.ptr)));
+  GLMRT_RETURN_IF_ERROR(run_router_and_routed(l, static_cast<const uint16_t*>(hidden_bf16.ptr), rows,
+                                              static_cast<uint16_t*>(output_bf16.ptr), s,
+                                              static_cast<const uint16_t*>(residual_bf16.ptr),
+                                              static_cast<const uint16_t*>(shared_delta_bf16.ptr)));
   l->launches_last = static_cast<uint32_t>(launches_total() - before);
   return ok();
 }
@@ -859,6 +893,7 @@ void local_ep_buffers(Layer* l, glmrt_b200_ep_buffers_t* out) {
   out->slot_out = l->slot_out;
   out->route_rows = l->route_rows;
   out->control = l->ep_ctrl;
+  out->act_sf_rows = l->act1_sf_rows;
 }
 
 glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t rows, uint16_t* out,
@@ -905,6 +940,9 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       FfnArgs f = ffn_args(l, chunk_tokens);
       mark(l, GLMRT_B200_STAGE_FC1, s);
       if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
+        if (chunk_tokens >= 128)
+          GLMRT_RETURN_IF_ERROR(launch_ep_retile_scales(a, l->act1_sf_rows, l->act1_sf, static_cast<int>(c.hidden_dim / 16),
+                                                        l->counters, l->counters + kCntError, l->counters + kCntChunks, s));
         GLMRT_RETURN_IF_ERROR(launch_ep_wait(ep_wait_dispatch(a), l->counters + kCntError, l->counters + kCntChunks, s));
         GLMRT_RETURN_IF_ERROR(launch_fc1_simt(f, s));
         mark(l, GLMRT_B200_STAGE_FC2, s);
@@ -914,6 +952,9 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       }
       f.wait = ep_wait_dispatch(a);
       f.signal = ep_signal_combine(a);
+      if (chunk_tokens >= 128)   // prefill-sized push: scale rows arrive row-major, re-tile what this rank owns
+        GLMRT_RETURN_IF_ERROR(launch_ep_retile_scales(a, l->act1_sf_rows, l->act1_sf, static_cast<int>(c.hidden_dim / 16),
+                                                      l->counters, l->counters + kCntError, l->counters + kCntChunks, s));
       if (!l->have_maps) GLMRT_RETURN_IF_ERROR(build_maps(l));
       const TensorMaps& maps = chunk_tokens == 32 ? l->maps32 : l->maps128;
       GLMRT_RETURN_IF_ERROR(chunk_tokens == 32 ? launch_fc1_tc(f, maps, l->sm_count, s)
@@ -967,12 +1008,12 @@ extern "C" glmrt_status_t glmrt_b200_ep_ipc_export(void* layer, void* out_handle
   Layer* l = static_cast<Layer*>(layer);
   GLMRT_RETURN_IF_ERROR(require_ep(l, false));
   if (out_handles == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_ipc_export: null output");
-  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_export: need 320 bytes");
+  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_export: need 384 bytes");
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle size");
   glmrt_b200_ep_buffers_t b;
   local_ep_buffers(l, &b);
-  void* ptrs[5] = {b.act_codes, b.act_sf, b.slot_out, b.route_rows, b.control};
-  for (int i = 0; i < 5; ++i) {
+  void* ptrs[6] = {b.act_codes, b.act_sf, b.slot_out, b.route_rows, b.control, b.act_sf_rows};
+  for (int i = 0; i < 6; ++i) {
     cudaIpcMemHandle_t h;
     cudaError_t err = cudaIpcGetMemHandle(&h, ptrs[i]);
     if (err != cudaSuccess) return fail_cuda(GLMRT_STATUS_INTERNAL_ERROR, "cudaIpcGetMemHandle", err);
@@ -986,9 +1027,9 @@ extern "C" glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handle
   Layer* l = static_cast<Layer*>(layer);
   GLMRT_RETURN_IF_ERROR(require_ep(l, false));
   if (handles == nullptr || out_mapped == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_ipc_open: null argument");
-  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_open: need 320 bytes");
-  void* ptrs[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-  for (int i = 0; i < 5; ++i) {
+  if (bytes < GLMRT_B200_EP_IPC_BYTES) return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "ep_ipc_open: need 384 bytes");
+  void* ptrs[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  for (int i = 0; i < 6; ++i) {
     cudaIpcMemHandle_t h;
     std::memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * i, 64);
     cudaError_t err = cudaIpcOpenMemHandle(&ptrs[i], h, cudaIpcMemLazyEnablePeerAccess);
@@ -1000,6 +1041,7 @@ extern "C" glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handle
   out_mapped->slot_out = ptrs[2];
   out_mapped->route_rows = ptrs[3];
   out_mapped->control = ptrs[4];
+  out_mapped->act_sf_rows = ptrs[5];
   return ok();
 }
 
@@ -1017,11 +1059,12 @@ extern "C" glmrt_status_t glmrt_b200_ep_attach(void* layer, const glmrt_b200_ep_
   a.counters = l->counters;
   for (size_t p = 0; p < world; ++p) {
     if (peers[p].act_codes == nullptr || peers[p].act_sf == nullptr || peers[p].slot_out == nullptr ||
-        peers[p].control == nullptr || my_rows_in_peer[p] == 0)
+        peers[p].control == nullptr || peers[p].act_sf_rows == nullptr || my_rows_in_peer[p] == 0)
       return fail(GLMRT_STATUS_INVALID_ARGUMENT, "ep_attach: a peer buffer is null");
     a.peer_ctrl[p] = static_cast<EpControl*>(peers[p].control);
     a.peer_act_codes[p] = static_cast<uint8_t*>(peers[p].act_codes);
     a.peer_act_sf[p] = static_cast<uint8_t*>(peers[p].act_sf);
+    a.peer_act_sf_rows[p] = static_cast<uint8_t*>(peers[p].act_sf_rows);
     a.peer_slot_out[p] = static_cast<uint16_t**>(peers[p].slot_out);
     a.my_rows_in_peer[p] = reinterpret_cast<uint16_t*>(static_cast<uintptr_t>(my_rows_in_peer[p]));
   }

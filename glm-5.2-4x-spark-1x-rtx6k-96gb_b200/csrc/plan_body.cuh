@@ -1,0 +1,112 @@
+// Route plan of one batch by ONE CTA: counting sort of the rows * top_k routes by expert (the
+// device-side form of plan_packed_w4a16_topk8_prefill_flat,
+// rust/crates/glmrt-daemon/src/commands/real_full/sparse_mlp/route.rs:3727-3828).  A device function
+// so that it can run as a kernel of its own or as the tail of the router's selection kernel (one
+// launch less on the decode path).  Called by every thread of the CTA; nthreads = its size
+// (a multiple of 32).  Uses 8 KB of static shared memory.
+#pragma once
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace glmrt {
+
+constexpr int kMaxLocalExperts = 1024;
+
+__device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads) {
+  __shared__ int cnt[kMaxLocalExperts];
+  __shared__ int base[kMaxLocalExperts];
+  __shared__ int s_error;
+  const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
+  for (int i = threadIdx.x; i < local_experts; i += nthreads) cnt[i] = 0;
+  if (threadIdx.x == 0) s_error = 0;
+  __syncthreads();
+  const int n = a.rows * a.top_k;
+  for (int r = threadIdx.x; r < n; r += nthreads) {
+    const uint32_t e = a.topk_indices[r];
+    int pos = -1;
+    if (e == kNoRoute) {
+      // nothing to do for this entry
+    } else if (e >= static_cast<uint32_t>(a.experts)) {
+      atomicOr(&s_error, static_cast<int>(kErrBadExpert));
+    } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
+      pos = atomicAdd(&cnt[e / a.ep_world], 1);
+    }
+    a.route_slot[r] = pos;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp 0: each lane owns a contiguous run of experts; exclusive scan of slots and chunks
+    const int lane = threadIdx.x;
+    const int per_lane = (local_experts + 31) / 32;
+    const int le0 = lane * per_lane, le1 = min(local_experts, le0 + per_lane);
+    int slots = 0, chunks = 0, distinct = 0, routes = 0;
+    for (int le = le0; le < le1; ++le) {
+      const int c = cnt[le];
+      slots += expert_slot_span(c, a.chunk_tokens);
+      chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
+      distinct += c != 0;
+      routes += c;
+    }
+    int slot_off = slots, chunk_off = chunks;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int s = __shfl_up_sync(0xffffffffu, slot_off, d);
+      const int c = __shfl_up_sync(0xffffffffu, chunk_off, d);
+      if (lane >= d) { slot_off += s; chunk_off += c; }
+    }
+    const int total_slots = __shfl_sync(0xffffffffu, slot_off, 31);
+    const int total_chunks = __shfl_sync(0xffffffffu, chunk_off, 31);
+    slot_off -= slots;    // inclusive -> exclusive
+    chunk_off -= chunks;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      distinct += __shfl_xor_sync(0xffffffffu, distinct, d);
+      routes += __shfl_xor_sync(0xffffffffu, routes, d);
+    }
+    int err = s_error;
+    if (total_slots > a.max_slots) err |= static_cast<int>(kErrSlotOverflow);
+    if (total_chunks > a.max_chunks) err |= static_cast<int>(kErrChunkOverflow);
+    for (int le = le0; le < le1; ++le) {
+      const int c = cnt[le];
+      base[le] = slot_off;
+      a.expert_counts[le] = c;
+      if (err == 0) {
+        for (int off = 0; off < c; off += a.chunk_tokens) {
+          Chunk ch;
+          ch.expert = le;
+          ch.slot_base = slot_off + slot_of_position(off, a.chunk_tokens);
+          ch.tokens = min(a.chunk_tokens, c - off);
+          ch.reserved = 0;
+          a.chunks[chunk_off++] = ch;
+        }
+      }
+      slot_off += expert_slot_span(c, a.chunk_tokens);
+    }
+    if (lane == 0) {
+      s_error = err;
+      // never launch expert work on an inconsistent plan
+      a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(total_chunks);
+      a.counters[kCntSlots] = static_cast<uint32_t>(total_slots);
+      a.counters[kCntError] = static_cast<uint32_t>(err);   // also clears the word for the kernels that follow
+      a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+      a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+    }
+  }
+  __syncthreads();
+  const bool bad = s_error != 0;
+  for (int r = threadIdx.x; r < n; r += nthreads) {
+    const int pos = a.route_slot[r];
+    if (pos < 0) continue;
+    const uint32_t e = a.topk_indices[r];
+    const int slot = base[e / a.ep_world] + slot_of_position(pos, a.chunk_tokens);
+    if (bad || slot >= a.max_slots) {
+      a.route_slot[r] = -1;
+    } else {
+      a.route_slot[r] = slot;
+      a.slot_route[slot] = r;
+    }
+  }
+}
+
+}  // namespace glmrt

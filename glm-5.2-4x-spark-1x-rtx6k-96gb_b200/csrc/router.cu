@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "internal.h"
+#include "plan_body.cuh"
 
 namespace glmrt {
 namespace {
@@ -259,9 +260,10 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     topk_weights[out + lane + 32] = my_score2 / sum * scaling;
   }
   }  // row < rows
-  if (tail.world == 0) return;
-  // Expert-parallel path: the last CTA to finish counts this rank's routes per expert and publishes
-  // the histogram to every rank (the first step of the exchange, otherwise a launch of its own).
+  if (tail.ticket == nullptr) return;
+  // The last CTA to finish does what would otherwise be a launch of its own: on the
+  // expert-parallel path it counts this rank's routes per expert and publishes the histogram to
+  // every rank (the first step of the exchange); on one GPU it builds the route plan.
   __shared__ int s_is_last;
   __threadfence();
   __syncthreads();
@@ -269,6 +271,11 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   __syncthreads();
   if (!s_is_last) return;
   __threadfence();
+  if (tail.do_plan) {
+    if (threadIdx.x == 0) *tail.ticket = 0;
+    route_plan_body(tail.plan, blockDim.x);
+    return;
+  }
   int* hist = reinterpret_cast<int*>(smem);   // 2 * experts floats per warp are free again
   for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
   __syncthreads();

@@ -20,10 +20,10 @@ from .layer import MoeLayer, _buf, _stream
 class EpBuffers(C.Structure):
     """glmrt_b200_ep_buffers_t."""
     _fields_ = [("act_codes", C.c_void_p), ("act_sf", C.c_void_p), ("slot_out", C.c_void_p),
-                ("route_rows", C.c_void_p), ("control", C.c_void_p)]
+                ("route_rows", C.c_void_p), ("control", C.c_void_p), ("act_sf_rows", C.c_void_p)]
 
 
-IPC_BYTES = 320
+IPC_BYTES = 384
 
 
 def partition_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:

@@ -575,8 +575,9 @@ typedef struct glmrt_b200_ep_buffers_t {
   void* slot_out;    /* [slots] result-row address per slot */
   void* route_rows;  /* bf16 [rows * top_k, H] result rows pushed by owners */
   void* control;     /* histograms and epoch flags */
+  void* act_sf_rows; /* [slots, H/16] row-major scale bytes of prefill-sized pushes (re-tiled by the owner) */
 } glmrt_b200_ep_buffers_t;
-#define GLMRT_B200_EP_IPC_BYTES 320 /* five 64-byte CUDA IPC handles */
+#define GLMRT_B200_EP_IPC_BYTES 384 /* six 64-byte CUDA IPC handles */
 glmrt_status_t glmrt_b200_ep_local_buffers(void* layer, glmrt_b200_ep_buffers_t* out);
 glmrt_status_t glmrt_b200_ep_ipc_export(void* layer, void* out_handles, size_t bytes);
 glmrt_status_t glmrt_b200_ep_ipc_open(void* layer, const void* handles, size_t bytes,
@@ -757,6 +758,14 @@ typedef enum glmrt_b200_stage_t {
 glmrt_status_t glmrt_b200_moe_layer_set_profiling(void* layer, int enable);
 /* out_ms receives GLMRT_B200_STAGE_COUNT floats; waits for the last forward to finish. */
 glmrt_status_t glmrt_b200_moe_layer_stage_times(void* layer, float* out_ms, size_t count);
+
+/* Measurement aid (no counterpart in the reference): the rate at which all SMs together can bring
+ * operand tiles into shared memory with the copy shapes of the prefill FC1 kernel (per stage three
+ * 128-row x 128-byte TMA boxes and three 2 KB scale copies, `stages` stages of 54 KB in flight per
+ * SM, nothing consumed).  working_set_bytes well below the L2 size measures L2 -> shared memory,
+ * far above it HBM -> shared memory.  Allocates and frees its own buffers; synchronises the stream. */
+glmrt_status_t glmrt_b200_probe_operand_delivery(size_t working_set_bytes, uint32_t stages, uint32_t tiles_per_cta,
+                                                 float* out_gb_per_s, float* out_ms, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -725,3 +725,32 @@ def test_stacked_layers_share_one_workspace(pkg):
     np.testing.assert_array_equal(to_bits(y), expect)
     for l in reversed(stack):
         l.close()
+
+
+def test_dense_shared_expert_beside_the_routed_path(pkg, small_layer):
+    """hidden + routed + shared with the reference's DENSE shared expert (expert_forward in float32
+    on unquantised weights, glm_moe_dsa_layer_ref.py:157-206): the shared rows against the
+    oracle's float32 expert_forward, and the whole layer output against the oracle's composition
+    (routed part in mode O1, residual step exact)."""
+    from glmrt_b200.shared_expert import DenseSharedExpert, sparse_layer_forward
+    K, T, H, I = 4, 40, 512, 256
+    rng = np.random.default_rng(88)
+    wg, wu = (O.bf16_to_f32(O.bf16_round(rng.standard_normal((I, H), np.float32) * np.float32(0.05))) for _ in range(2))
+    wd = O.bf16_to_f32(O.bf16_round(rng.standard_normal((H, I), np.float32) * np.float32(0.05)))
+    hid = O.make_hidden(901, T, H)
+    resid = O.bf16_round(rng.standard_normal((T, H), np.float32))
+    shared = DenseSharedExpert(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd))
+    delta = to_bits(shared.delta(to_dev(hid)))
+    want_delta = O.bf16_round(O.expert_forward(O.bf16_to_f32(hid), O.ExpertWeights(wg, wu, wd)))
+    err = O.rel_l2_per_token(delta, want_delta)
+    assert err.max() <= 2e-3, f"dense shared expert vs float32 expert_forward: {err.max():.3e}"
+    routed = make(pkg, small_layer, K, 64, "tc")
+    got = to_bits(sparse_layer_forward(routed, shared, to_dev(resid), to_dev(hid)))
+    routed.check()
+    _, _, routed_ref = O.layer_forward(small_layer, hid, K, mode="O1")
+    want = O.residual_add_shared_f32_delta_bf16(resid, want_delta, O.bf16_to_f32(routed_ref))
+    assert O.rel_l2_per_token(got, want).max() <= TOL
+    # the fold itself is exact: same routed rows and the same delta give the same bits
+    routed_rows = to_bits(routed.forward(to_dev(hid)))
+    np.testing.assert_array_equal(got, O.residual_add_shared_f32_delta_bf16(resid, delta, O.bf16_to_f32(routed_rows)))
+    routed.close()
