@@ -1023,10 +1023,10 @@ def run_zipf(args, torch, dist, rank, world, layer, sampler, timer):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one FC1 launch from the ncu captures summarised
-# under profiles/, per expert touched: decode kernel (820.55 MB, 57 experts touched) and prefill
-# kernel (1003.59 MB, 64 experts).
-NCU_FC1_TRAFFIC_PER_EXPERT = 820.55e6 / 57
-NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT = 1003.59e6 / 64
+# under profiles/, per expert touched: decode kernel (862.55 MB, 60 experts touched) and prefill
+# kernel (998.81 MB, 64 experts).
+NCU_FC1_TRAFFIC_PER_EXPERT = 862.55e6 / 60
+NCU_FC1_PREFILL_TRAFFIC_PER_EXPERT = 998.81e6 / 64
 
 
 def main():

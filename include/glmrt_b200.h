@@ -150,6 +150,8 @@ glmrt_status_t glmrt_b200_router_topk_bf16_f32w_async(
  * the process exits), so rows * experts must not exceed 262144; larger problems are rejected
  * with GLMRT_STATUS_BUFFER_TOO_SMALL.  The entry point calls no allocator.  The first call on a
  * device looks up the array's device address; make that first call outside any stream capture.
+ * The address is cached per device for the life of the process, which assumes that the device's
+ * primary context is not reset in between.
  * All calls on one device share the array: calls that may overlap on the GPU (different streams)
  * race on it and must be ordered by the caller. */
 glmrt_status_t glmrt_b200_router_topk_bf16_f32w_static_async(
