@@ -173,6 +173,8 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
         }
       }
     }
+    if (p.fc_sync != nullptr && plan_ok)   // hand-over words of the decode GEMMs (FfnArgs::fc_sync)
+      for (int i = threadIdx.x; i < kFcSyncHeader + s_chunk_total; i += kPushThreads) p.fc_sync[i] = 0u;
     if (threadIdx.x == 0) {
       // never start expert work on an inconsistent plan
       p.counters[kCntChunks] = plan_ok ? static_cast<uint32_t>(s_chunk_total) : 0u;

@@ -25,6 +25,8 @@
 // copies land, releases tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ep_flags.cuh"
 #include "epilogue.cuh"
@@ -54,16 +56,48 @@ struct Cfg {
                                    : kColsUsed <= 256 ? 256 : 512;
   static constexpr uint32_t kTxBytes = kStageBytes;
   static constexpr int kChunkCache = 256;  // work items of this CTA's first tiles, staged in shared memory
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ +
+  static constexpr int kBarrierBytes = 768; // mbarriers, the tensor-memory slot, the abort word and the tile ring
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + kBarrierBytes +
                                        kChunkCache * sizeof(Chunk);
 };
 
-template <bool kFC1, int kBN>
-__global__ void __launch_bounds__(kThreadsTC, 1)
+// One entry of the tile ring of the overlapped FC2 kernel: a scheduling warp draws tiles from a
+// global counter and hands each one, with its work item and once its operand rows are there, to the
+// producer, the issuing warp and the epilogue warps.
+struct TileSlot {
+  Chunk ch;
+  int32_t tile;      // -1: no more tiles
+  int32_t pad[3];
+};
+constexpr int kTileRing = 8;
+constexpr int kThreadsOverlapFc2 = kThreadsTC + 32;   // the six warps of every instance + the scheduling warp
+
+// Destination-row pointers are written by an earlier kernel (or by a peer rank); the overlapped
+// FC2 may share an SM's L1 with that earlier kernel's traffic, so it reads them from the L2.
+__device__ __forceinline__ uint16_t* load_row_pointer(uint16_t* const* p) {
+  return reinterpret_cast<uint16_t*>(__ldcg(reinterpret_cast<const unsigned long long*>(p)));
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// kOverlap: FC1 and FC2 of a decode-sized step run as one pipeline over two launches.  FC1 lets its
+// successor start once FC1 itself may run (griddepcontrol.launch_dependents after its own
+// griddepcontrol.wait, so everything older than FC1 is complete when FC2 begins) and counts, per work
+// item, the epilogue warps that have stored intermediate rows.  FC2 does not wait for FC1 to
+// complete: its CTAs take the SMs FC1's CTAs have left, draw tiles from a global counter (the CTAs
+// that start early take more) and wait, per tile, until the work item's intermediate rows are all
+// there.  On an expert-parallel shard with 28 experts FC1 is 448 tiles on 148 SMs: during its
+// fourth wave 144 SMs would otherwise idle.
+template <bool kFC1, int kBN, bool kOverlap>
+__global__ void __launch_bounds__(kOverlap && !kFC1 ? kThreadsOverlapFc2 : kThreadsTC, 1)
 expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                    const __grid_constant__ CUtensorMap map_b) {
   using C = Cfg<kFC1, kBN>;
-  pdl_launch_dependents();
+  constexpr bool kDynamic = kOverlap && !kFC1;   // tiles drawn from a counter instead of a fixed stride
+  if (!(kOverlap && kFC1)) pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -72,9 +106,12 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   uint64_t* empty_bar = bars + C::kStages;
   uint64_t* acc_full = bars + 2 * C::kStages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* ring_full = acc_empty + 2;
+  uint64_t* ring_empty = ring_full + kTileRing;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ring_empty + kTileRing);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  Chunk* chunk_cache = reinterpret_cast<Chunk*>(reinterpret_cast<uint8_t*>(bars) + 256);
+  TileSlot* ring = reinterpret_cast<TileSlot*>(reinterpret_cast<uint8_t*>(bars) + 384);   // 8 x 32 bytes
+  Chunk* chunk_cache = reinterpret_cast<Chunk*>(reinterpret_cast<uint8_t*>(bars) + C::kBarrierBytes);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -94,6 +131,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);
     }
+    for (int r = 0; r < kTileRing; ++r) {
+      mbar_init(&ring_full[r], 1);
+      mbar_init(&ring_empty[r], 6);   // the producer, the issuing warp and four epilogue warps have read the entry
+    }
     *abort_flag = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -105,21 +146,39 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   const uint32_t tmem_base = *tmem_slot;
 
   // Everything above (barriers, tensor memory) ran while the previous kernel was finishing; from
-  // here on this kernel reads what that kernel wrote.
-  pdl_wait();
+  // here on this kernel reads what earlier kernels wrote.  The overlapped FC2 does not wait for
+  // FC1's completion (FC1 raised launch_dependents only after everything older than itself was
+  // complete); it reads what it needs of FC1 tile by tile, below.
+  if (!kDynamic) pdl_wait();
+  if (kOverlap && kFC1) pdl_launch_dependents();
   // a step that has already reported an error runs no expert work (and tells no peer it did)
   const bool step_failed = *reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u;
-  const int num_chunks = step_failed ? 0 : static_cast<int>(a.counters[kCntChunks]);
+  const int num_chunks = step_failed ? 0 : static_cast<int>(__ldcg(a.counters + kCntChunks));
   const int num_tiles = num_chunks * feat_tiles;
-  // The work items of this CTA's tiles are fetched once, up front: a global load at the head of
-  // every tile would stall each role for a memory round trip and drain the TMA pipeline.
-  for (int i = threadIdx.x; i < C::kChunkCache; i += kThreadsTC) {
-    const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
-    if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
+  if (!kDynamic) {
+    // The work items of this CTA's tiles are fetched once, up front: a global load at the head of
+    // every tile would stall each role for a memory round trip and drain the TMA pipeline.
+    for (int i = threadIdx.x; i < C::kChunkCache; i += blockDim.x) {
+      const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
+      if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  auto chunk_of = [&](int it, int tile) -> Chunk {
-    return it < C::kChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
+  // Tile sequence of a consumer role (every lane of the warp calls it; the warp stays converged).
+  auto next_tile = [&](int it, TileSlot& ts) -> bool {
+    if (!kDynamic) {
+      const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(it) * gridDim.x;
+      if (tile >= num_tiles) return false;
+      ts.tile = static_cast<int32_t>(tile);
+      ts.ch = it < C::kChunkCache ? chunk_cache[it] : a.chunks[tile / feat_tiles];
+      return true;
+    }
+    const int r = it % kTileRing;
+    if (!mbar_wait_warp(&ring_full[r], static_cast<uint32_t>(it / kTileRing) & 1u, abort_flag)) return false;
+    ts = ring[r];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ring_empty[r]);
+    return ts.tile >= 0;
   };
 
   if (warp == 0) {
@@ -133,7 +192,6 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      int it = 0;
       if (kFC1 && a.wait.flags != nullptr && (blockIdx.x == 0 || static_cast<int>(blockIdx.x) < num_tiles)) {
         // expert-parallel path: the rows this kernel reads are pushed by the peers (CTA 0 waits even
         // without work, so that no rank ever runs a step ahead of a peer that is still pushing)
@@ -144,8 +202,21 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         }
         asm volatile("fence.proxy.async;" ::: "memory");
       }
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
-        const Chunk ch = chunk_of(it, tile);
+      for (int it = 0; alive; ++it) {
+        TileSlot ts;
+        if (kDynamic) {
+          // the scheduling warp hands over tiles whose operand rows are complete
+          const int r = it % kTileRing;
+          if (!mbar_wait(&ring_full[r], static_cast<uint32_t>(it / kTileRing) & 1u, abort_flag)) { alive = false; break; }
+          ts = ring[r];
+          mbar_arrive(&ring_empty[r]);
+          if (ts.tile < 0) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // FC1 wrote the rows with ordinary stores; TMA reads them
+        } else if (!next_tile(it, ts)) {
+          break;
+        }
+        const Chunk ch = ts.ch;
+        const int tile = ts.tile;
         const int ft = tile % feat_tiles;
         const int w_row = ch.expert * out_rows + ft * kTileRows;
         const size_t sfa_tile0 = static_cast<size_t>(w_row / 128) * k_tiles64;
@@ -184,9 +255,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       bool alive = true;
       const uint32_t t_sfa0 = tmem_base + C::kSfCol;
       const uint32_t t_sfb = t_sfa0 + 16 * C::kNumA;
-      int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
-        const Chunk ch = chunk_of(it, tile);
+      TileSlot ts;
+      for (int it = 0; alive && next_tile(it, ts); ++it) {
+        const Chunk ch = ts.ch;
         const uint32_t n_mma = static_cast<uint32_t>(max(16, (ch.tokens + 15) & ~15));
         const uint32_t idesc = idesc_nvf4(n_mma);
         const uint32_t sfb_q = static_cast<uint32_t>((ch.slot_base & 127) >> 5);  // 32-row quadrant inside the scale tile
@@ -232,6 +303,54 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
       }
     }
+  } else if (warp >= 6) {
+    // ================= tile scheduler (overlapped FC2 only) =================
+    // Draws tiles from the global counter (the CTAs that start early, on SMs FC1 has already left,
+    // take more), waits until every FC1 epilogue warp has stored its share of the tile's work item
+    // (bounded; a step that has reported an error ends the wait), and hands the tile to the ring.
+    if (kDynamic && lane == 0) {
+      const uint32_t need = 4u * static_cast<uint32_t>(a.inter / kTileRows);
+      int ready_chunk = -1;
+      Chunk ch = Chunk{0, 0, 0, 0};
+      bool alive = true;
+      for (int it = 0; alive; ++it) {
+        TileSlot ts;
+        ts.pad[0] = ts.pad[1] = ts.pad[2] = 0;
+        const int t = static_cast<int>(atomicAdd(a.fc_sync, 1u));
+        if (t >= num_tiles) {
+          ts.tile = -1;
+          ts.ch = Chunk{0, 0, 0, 0};
+        } else {
+          const int ci = t / feat_tiles;
+          if (ci != ready_chunk) {
+            const int4 c4 = __ldcg(reinterpret_cast<const int4*>(a.chunks + ci));   // from L2: written by an earlier kernel
+            ch = Chunk{c4.x, c4.y, c4.z, c4.w};
+            const uint32_t* done = a.fc_sync + kFcSyncHeader + ci;
+            if (ld_acquire_gpu(done) < need) {
+              const uint64_t t0 = global_timer_ns();
+              while (ld_acquire_gpu(done) < need) {
+                if (*reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u || *abort_flag != 0u ||
+                    global_timer_ns() - t0 > kWaitLimitNs) {
+                  *abort_flag = 1u;
+                  alive = false;
+                  break;
+                }
+                __nanosleep(64);
+              }
+              if (!alive) break;
+            }
+            ready_chunk = ci;
+          }
+          ts.tile = t;
+          ts.ch = ch;
+        }
+        const int r = it % kTileRing;
+        if (!mbar_wait(&ring_empty[r], (static_cast<uint32_t>(it / kTileRing) & 1u) ^ 1u, abort_flag)) break;
+        ring[r] = ts;
+        mbar_arrive(&ring_full[r]);     // release: the entry is visible to the roles that wait on it
+        if (ts.tile < 0) break;
+      }
+    }
   } else {
     // ================= epilogue (warps 2..5) =================
     const int quad = warp & 3;                       // tensor-memory lanes 32*quad .. 32*quad+31
@@ -239,9 +358,10 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
     int abuf = 0;
     uint32_t aphase = 0;
     bool alive = true;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++it) {
-      const Chunk ch = chunk_of(it, tile);
+    TileSlot ts;
+    for (int it = 0; alive && next_tile(it, ts); ++it) {
+      const Chunk ch = ts.ch;
+      const int tile = ts.tile;
       const int ft = tile % feat_tiles;
       const int feature = ft * kTileRows + quad * 32 + lane;   // output row of this lane inside the expert
       // everything the epilogue needs from global memory is fetched before the accumulators are
@@ -249,7 +369,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
       const float s2a = a.scale2[ch.expert * 3 + (kFC1 ? 0 : 2)];
       const float s2b = kFC1 ? a.scale2[ch.expert * 3 + 1] : 0.0f;
       uint16_t* dst_lane = nullptr;   // FC2: lane j holds the destination row of token column j (of the current 32)
-      if (!kFC1 && lane < ch.tokens) dst_lane = a.slot_out[ch.slot_base + lane];
+      if (!kFC1 && lane < ch.tokens) dst_lane = load_row_pointer(a.slot_out + ch.slot_base + lane);
       // lane 0 waits (bounded) and the warp takes one common decision, so that the full-mask
       // shuffles of the epilogue can never run with part of the warp gone
       uint32_t ready = lane == 0 ? (mbar_wait(&acc_full[abuf], aphase, abort_flag) ? 1u : 0u) : 0u;
@@ -272,10 +392,17 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
                                    a.act2_sf);
           }
         }
+        if (kOverlap) {
+          // this warp's share of the work item's intermediate rows is stored: count it for FC2
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(a.fc_sync + kFcSyncHeader + tile / feat_tiles, 1u);
+        }
       } else {
         for (int c0 = 0; c0 < ch.tokens; c0 += 8) {
           if (c0 != 0 && (c0 & 31) == 0)
-            dst_lane = (c0 + lane < ch.tokens) ? a.slot_out[ch.slot_base + c0 + lane] : nullptr;
+            dst_lane = (c0 + lane < ch.tokens) ? load_row_pointer(a.slot_out + ch.slot_base + c0 + lane) : nullptr;
           uint32_t y[8];
           tc_load8(t_acc + c0, y);
           tc_wait_ld();
@@ -326,15 +453,26 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <bool kFC1, int kBN>
+template <bool kFC1, int kBN, bool kOverlap>
 glmrt_status_t launch_one(const FfnArgs& a, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b,
                           int sm_count, cudaStream_t stream) {
   using C = Cfg<kFC1, kBN>;
   static std::atomic<uint64_t> configured{0};
-  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_kernel<kFC1, kBN>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_kernel)"));
-  launch_pdl(expert_gemm_kernel<kFC1, kBN>, dim3(sm_count), dim3(kThreadsTC), C::kSmemBytes, stream, a, a0, a1, b);
+  GLMRT_RETURN_IF_ERROR(ensure_smem_limit(configured, expert_gemm_kernel<kFC1, kBN, kOverlap>, C::kSmemBytes, "cudaFuncSetAttribute(expert_gemm_kernel)"));
+  launch_pdl(expert_gemm_kernel<kFC1, kBN, kOverlap>, dim3(sm_count), dim3(kOverlap && !kFC1 ? kThreadsOverlapFc2 : kThreadsTC),
+             C::kSmemBytes, stream, a, a0, a1, b);
   GLMRT_LAUNCH_CHECK("expert_gemm_kernel");
   return GLMRT_STATUS_OK;
+}
+
+// FC2 may start under FC1's tail only when the two are launched with the programmatic launch
+// attribute (otherwise FC2 starts after FC1 has completed anyway and the plain pair is used).
+bool fc_overlap(const FfnArgs& a) {
+  static const bool off = []() {
+    const char* v = std::getenv("GLMRT_B200_NO_FC_OVERLAP");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return a.fc_sync != nullptr && !off && pdl_enabled();
 }
 
 }  // namespace
@@ -373,12 +511,16 @@ glmrt_status_t make_scale_tensor_map(CUtensorMap* out, const void* base, uint64_
 }
 
 glmrt_status_t launch_fc1_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  if (a.chunk_tokens == 32) return launch_one<true, 32>(a, m.gate, m.up, m.act1, sm_count, stream);
+  if (a.chunk_tokens == 32)
+    return fc_overlap(a) ? launch_one<true, 32, true>(a, m.gate, m.up, m.act1, sm_count, stream)
+                         : launch_one<true, 32, false>(a, m.gate, m.up, m.act1, sm_count, stream);
   return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
 }
 
 glmrt_status_t launch_fc2_tc(const FfnArgs& a, const TensorMaps& m, int sm_count, cudaStream_t stream) {
-  if (a.chunk_tokens == 32) return launch_one<false, 32>(a, m.down, m.down, m.act2, sm_count, stream);
+  if (a.chunk_tokens == 32)
+    return fc_overlap(a) ? launch_one<false, 32, true>(a, m.down, m.down, m.act2, sm_count, stream)
+                         : launch_one<false, 32, false>(a, m.down, m.down, m.act2, sm_count, stream);
   return fail(GLMRT_STATUS_INTERNAL_ERROR, "tensor-core engine: unsupported chunk size");
 }
 

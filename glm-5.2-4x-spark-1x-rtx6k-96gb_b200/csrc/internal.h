@@ -103,6 +103,7 @@ struct PlanArgs {
   int32_t* block_hist;           // [ceil(routes / 256)][local experts] per-block counts, then prefixes
   Chunk* chunks;                 // [max_chunks]
   uint32_t* counters;            // [kCntWords]
+  uint32_t* fc_sync = nullptr;   // [kFcSyncHeader + max_chunks] cleared by the plan: see FfnArgs::fc_sync
 };
 // Optional tails of the router's selection kernel, run by the last CTA of its grid to finish.
 //   expert-parallel path (world > 0): count this rank's routes per expert, store the histogram into
@@ -248,7 +249,13 @@ struct FfnArgs {
   // result rows have been stored
   EpWait wait;
   EpSignal signal;
+  // Decode kernels: FC2 starts on the SMs FC1 has left while FC1's last tiles still run.  Word 0 is
+  // FC2's next-tile counter, words kFcSyncHeader + c count the FC1 epilogue warps that have stored
+  // work item c's intermediate rows (4 per feature tile); both are cleared by the route plan.
+  // nullptr: FC2 starts when FC1 has completed, as every other kernel pair does.
+  uint32_t* fc_sync = nullptr;
 };
+constexpr int kFcSyncHeader = 8;
 glmrt_status_t launch_fc1_simt(const FfnArgs& a, cudaStream_t stream);
 glmrt_status_t launch_fc2_simt(const FfnArgs& a, cudaStream_t stream);
 

@@ -80,6 +80,7 @@ struct Layer {
   uint16_t* route_rows = nullptr;
   uint16_t** slot_out = nullptr;
   uint32_t* slot_weight = nullptr;   // route weight per slot (fused combine of large batches)
+  uint32_t* fc_sync = nullptr;       // hand-over words between the decode FC1 and FC2 kernels
   uint16_t *hidden_stage = nullptr, *out_stage = nullptr;
   // scratch for weight loading
   float* wtmp = nullptr;
@@ -182,7 +183,10 @@ glmrt_status_t build_maps(Layer* l) {
   return GLMRT_STATUS_OK;
 }
 
-FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
+// batch_rows: rows of the whole batch (over all ranks where known).  The FC1 -> FC2 overlap of the
+// decode kernels pays from about eight rows on (64 routes); below that FC2's tile scheduling costs
+// more than the overlap saves (measured at one row: +1.3 us on 67), so tiny batches run the plain pair.
+FfnArgs ffn_args(const Layer* l, int chunk_tokens, size_t batch_rows) {
   FfnArgs a{};
   a.gate_codes = l->gate_codes; a.up_codes = l->up_codes; a.down_codes = l->down_codes;
   a.gate_sf = l->gate_sf; a.up_sf = l->up_sf; a.down_sf = l->down_sf;
@@ -194,6 +198,8 @@ FfnArgs ffn_args(const Layer* l, int chunk_tokens) {
   a.hidden = static_cast<int>(l->cfg.hidden_dim); a.inter = static_cast<int>(l->cfg.intermediate_dim);
   a.max_chunks = l->max_chunks; a.chunk_tokens = chunk_tokens;
   a.error_word = l->counters + kCntError;
+  a.fc_sync = chunk_tokens == 32 && batch_rows * l->cfg.top_k >= 64 && !(l->cfg.flags & GLMRT_B200_LAYER_ENGINE_SIMT)
+                  ? l->fc_sync : nullptr;
   return a;
 }
 
@@ -225,6 +231,7 @@ PlanArgs plan_args(const Layer* l, size_t rows, int chunk_tokens) {
   p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
   p.expert_base = l->expert_base; p.block_hist = l->block_hist;
   p.chunks = l->chunks; p.counters = l->counters;
+  p.fc_sync = chunk_tokens == 32 ? l->fc_sync : nullptr;
   return p;
 }
 
@@ -294,7 +301,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   if (!plan_done) GLMRT_RETURN_IF_ERROR(launch_route_plan(plan_args(l, rows, chunk_tokens), stream));
   mark(l, GLMRT_B200_STAGE_DISPATCH, stream);
   GLMRT_RETURN_IF_ERROR(fused ? launch_quantize_dispatch(hidden, d, stream) : launch_dispatch(d, stream));
-  FfnArgs f = ffn_args(l, chunk_tokens);
+  FfnArgs f = ffn_args(l, chunk_tokens, rows);
   if (fused_combine) f.slot_weight = l->slot_weight;
   mark(l, GLMRT_B200_STAGE_FC1, stream);
   if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
@@ -424,6 +431,7 @@ glmrt_status_t alloc_workspace(Layer* l) {
   A(dev_alloc(b, &l->block_hist, ((routes + 255) / 256 + 1) * E));
   A(dev_alloc(b, &l->chunks, static_cast<size_t>(l->max_chunks)));
   A(dev_alloc(b, &l->counters, kCntWords, true));
+  A(dev_alloc(b, &l->fc_sync, static_cast<size_t>(kFcSyncHeader) + l->max_chunks, true));
   // slot-ordered operands; zero-filled once so that padding slots hold finite values
   A(dev_alloc(b, &l->act1_codes, static_cast<size_t>(l->max_slots) * H / 2, true));
   A(dev_alloc(b, &l->act1_sf, static_cast<size_t>(l->max_slots) * H / 16, true));
@@ -930,6 +938,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
       p.expert_base = l->expert_base; p.block_hist = l->block_hist;
       p.chunks = l->chunks; p.counters = l->counters;
+      p.fc_sync = chunk_tokens == 32 ? l->fc_sync : nullptr;
       mark(l, GLMRT_B200_STAGE_DISPATCH, s);
       return launch_ep_plan_dispatch(a, p, hidden, l->payload, static_cast<int>(rows), static_cast<int>(c.top_k),
                                      static_cast<int>(c.hidden_dim), s);
@@ -937,7 +946,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
     case 2: {
       // expert FFN on what arrived: FC1 waits for the peers' rows, FC2 stores each result row into
       // its home rank and raises the "combine" flag when the last CTA is done
-      FfnArgs f = ffn_args(l, chunk_tokens);
+      FfnArgs f = ffn_args(l, chunk_tokens, batch);
       mark(l, GLMRT_B200_STAGE_FC1, s);
       if (c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) {
         if (chunk_tokens >= 128)

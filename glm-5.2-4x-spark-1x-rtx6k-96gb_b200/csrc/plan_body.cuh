@@ -17,6 +17,7 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
   __shared__ int cnt[kMaxLocalExperts];
   __shared__ int base[kMaxLocalExperts];
   __shared__ int s_error;
+  __shared__ int s_total_chunks;
   const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
   for (int i = threadIdx.x; i < local_experts; i += nthreads) cnt[i] = 0;
   if (threadIdx.x == 0) s_error = 0;
@@ -84,6 +85,7 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
       slot_off += expert_slot_span(c, a.chunk_tokens);
     }
     if (lane == 0) {
+      s_total_chunks = err != 0 ? 0 : total_chunks;
       s_error = err;
       // never launch expert work on an inconsistent plan
       a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(total_chunks);
@@ -94,6 +96,10 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
     }
   }
   __syncthreads();
+  if (a.fc_sync != nullptr) {
+    // the decode GEMMs' hand-over words: FC2's tile counter and one "rows stored" count per work item
+    for (int i = threadIdx.x; i < kFcSyncHeader + s_total_chunks; i += nthreads) a.fc_sync[i] = 0u;
+  }
   const bool bad = s_error != 0;
   for (int r = threadIdx.x; r < n; r += nthreads) {
     const int pos = a.route_slot[r];
