@@ -223,6 +223,8 @@ glmrt_status_t launch_bf16_rows_to_fp8_row_scaled(const uint16_t* src, uint8_t* 
 // ---- layer.cu: entry used by the ExpertProtocolV2 executor (protocol_v2.cu) ----
 struct LayerDims { uint32_t hidden, experts, top_k, max_tokens, ep_world, ep_rank; };
 glmrt_status_t layer_dims(void* layer, LayerDims* out);
+// Forgets a streamed request that is still pending on this layer handle (called when the handle dies).
+void drop_stream_session(void* layer);
 // Runs `rows` host rows (bf16, or NVFP4 payload rows when hidden_is_payload) with host route tables
 // [rows, top_k] (expert kNoRoute = none) through the layer and writes bf16 rows, or NVFP4 payload
 // rows in the native rounding rule (out_kind 1) or row-scaled FP8 rows (out_kind 2), to host memory.

@@ -557,6 +557,7 @@ extern "C" glmrt_status_t glmrt_b200_moe_layer_create_stacked(const glmrt_b200_m
 extern "C" glmrt_status_t glmrt_b200_moe_layer_destroy(void* layer) {
   if (layer == nullptr) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "layer is null");
   cudaDeviceSynchronize();
+  drop_stream_session(layer);
   destroy(static_cast<Layer*>(layer));
   return ok();
 }

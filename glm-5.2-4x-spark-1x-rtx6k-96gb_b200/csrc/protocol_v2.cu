@@ -28,6 +28,8 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -573,34 +575,20 @@ extern "C" glmrt_status_t glmrt_b200_pv2_verify_response_checksum(const void* fr
 }
 
 // ---- executor ------------------------------------------------------------------------------
-extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* request_frame, size_t request_bytes,
-                                                 void* response_out, size_t response_capacity, size_t* response_len,
-                                                 void* cuda_stream) {
-  if (layer == nullptr || request_frame == nullptr || response_len == nullptr)
-    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "pv2_execute: null pointer argument");
-  const uint8_t* b = static_cast<const uint8_t*>(request_frame);
-  glmrt_b200_pv2_request_header_t h;
-  glmrt_b200_pv2_sections_t sec;
-  GLMRT_RETURN_IF_ERROR(parse_request(b, request_bytes, &h, &sec));
-  if (h.flags & (GLMRT_B200_PV2_FLAG_STREAM_PLAN | GLMRT_B200_PV2_FLAG_STREAM_DATA | GLMRT_B200_PV2_FLAG_LAYER_BLOCK))
-    return bad("executor: streamed-ingress and layer-block frames are not supported, only regular requests");
-  // the reference's executors check the checksum of a frame that carries one (synthetic.rs:124)
-  GLMRT_RETURN_IF_ERROR(glmrt_b200_pv2_verify_request_checksum(request_frame, request_bytes));
-  LayerDims d;
-  GLMRT_RETURN_IF_ERROR(layer_dims(layer, &d));
-  if (h.hidden_dim != d.hidden)
-    return bad("executor: request hidden_dim " + std::to_string(h.hidden_dim) + " does not match the layer's " + std::to_string(d.hidden));
-  const bool in_payload = h.hidden_dtype == GLMRT_B200_PV2_DTYPE_NVFP4_E2M1_FP8_E4M3;
-  if (!in_payload && h.hidden_dtype != GLMRT_B200_PV2_DTYPE_BF16)
-    return bad("executor: hidden dtype must be bf16 or NVFP4 E2M1 + FP8 E4M3, got " + std::to_string(h.hidden_dtype));
-  if (h.row_count == 0) return bad("executor: request has no rows");
-  if (h.row_count > d.max_tokens)
-    return bad("executor: " + std::to_string(h.row_count) + " rows exceed the layer's max_tokens " + std::to_string(d.max_tokens));
+namespace glmrt {
+namespace {
 
-  // (row, expert, weight) route ranges -> [rows, top_k] tables; unused entries carry kNoRoute
+// The layer's view of a request: [rows, top_k] route tables (unused entries kNoRoute).
+struct RouteTables {
+  std::vector<uint32_t> idx;
+  std::vector<float> w;
+};
+
+glmrt_status_t build_route_tables(const uint8_t* b, const glmrt_b200_pv2_request_header_t& h,
+                                  const glmrt_b200_pv2_sections_t& sec, const LayerDims& d, RouteTables* t) {
   const size_t rows = h.row_count;
-  std::vector<uint32_t> idx(rows * d.top_k, kNoRoute);
-  std::vector<float> w(rows * d.top_k, 0.0f);
+  t->idx.assign(rows * d.top_k, kNoRoute);
+  t->w.assign(rows * d.top_k, 0.0f);
   for (size_t i = 0; i < rows; ++i) {
     glmrt_b200_pv2_row_t row;
     GLMRT_RETURN_IF_ERROR(decode_row(b + sec.rows_offset + i * GLMRT_B200_PV2_ROW_DESCRIPTOR_LEN, &row));
@@ -614,14 +602,33 @@ extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* reques
         return bad("executor: route row_index " + std::to_string(r.row_index) + " did not match row " + std::to_string(i));
       if (r.expert_id >= d.experts || r.expert_id % d.ep_world != d.ep_rank)
         return bad("executor: expert " + std::to_string(r.expert_id) + " does not live on this shard");
-      idx[i * d.top_k + k] = r.expert_id;
-      w[i * d.top_k + k] = r.gate_weight;
+      t->idx[i * d.top_k + k] = r.expert_id;
+      t->w[i * d.top_k + k] = r.gate_weight;
     }
   }
+  return GLMRT_STATUS_OK;
+}
 
+glmrt_status_t check_request_against_layer(const glmrt_b200_pv2_request_header_t& h, const LayerDims& d, uint32_t total_rows,
+                                           bool* in_payload) {
+  if (h.hidden_dim != d.hidden)
+    return bad("executor: request hidden_dim " + std::to_string(h.hidden_dim) + " does not match the layer's " + std::to_string(d.hidden));
+  *in_payload = h.hidden_dtype == GLMRT_B200_PV2_DTYPE_NVFP4_E2M1_FP8_E4M3;
+  if (!*in_payload && h.hidden_dtype != GLMRT_B200_PV2_DTYPE_BF16)
+    return bad("executor: hidden dtype must be bf16 or NVFP4 E2M1 + FP8 E4M3, got " + std::to_string(h.hidden_dtype));
+  if (total_rows == 0) return bad("executor: request has no rows");
+  if (total_rows > d.max_tokens)
+    return bad("executor: " + std::to_string(total_rows) + " rows exceed the layer's max_tokens " + std::to_string(d.max_tokens));
+  return GLMRT_STATUS_OK;
+}
+
+// Runs `rows` hidden rows (host memory, `stride` bytes apart) with their route tables and frames the response.
+glmrt_status_t run_and_frame(void* layer, const glmrt_b200_pv2_request_header_t& h, uint32_t rows, const uint8_t* hidden,
+                             size_t stride, bool in_payload, const RouteTables& t, void* response_out, size_t response_capacity,
+                             size_t* response_len, cudaStream_t stream) {
   glmrt_b200_pv2_response_header_t rh{};
   rh.request_id = h.request_id; rh.placement_version = h.placement_version; rh.layer_id = h.layer_id;
-  rh.row_count = h.row_count; rh.output_dim = h.hidden_dim;
+  rh.row_count = rows; rh.output_dim = h.hidden_dim;
   // response dtype negotiated by the request's flags (view.rs:258-264)
   const int out_kind = (h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_NVFP4_E2M1_FP8_E4M3)   ? kOutNvfp4Payload
                        : (h.flags & GLMRT_B200_PV2_FLAG_RESPONSE_FP8_E4M3_ROW_SCALED) ? kOutFp8RowScaled
@@ -636,14 +643,172 @@ extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* reques
   // a response to a checksummed request carries a checksum too (synthetic.rs with_matching_debug_checksum)
   rh.flags = h.flags & GLMRT_B200_PV2_FLAG_DEBUG_CHECKSUM;
   GLMRT_RETURN_IF_ERROR(glmrt_b200_pv2_compact_id(kExecutorName, &rh.executor_id));
-  const size_t header_len = header_len_for(rh.flags), payload_bytes = rows * out_row, wire = header_len + payload_bytes;
+  const size_t header_len = header_len_for(rh.flags), payload_bytes = size_t(rows) * out_row, wire = header_len + payload_bytes;
   *response_len = wire;
   if (response_out == nullptr || response_capacity < wire)
     return fail(GLMRT_STATUS_BUFFER_TOO_SMALL, "pv2_execute: response buffer too small for " + std::to_string(wire) + " bytes");
   uint8_t* out = static_cast<uint8_t*>(response_out);
   // the partial output rows land directly behind the header
-  GLMRT_RETURN_IF_ERROR(layer_execute_host_rows(layer, b + sec.payload_offset, in_payload, h.hidden_row_stride_bytes, rows,
-                                                idx.data(), w.data(), out_kind, out + header_len, out_row,
-                                                static_cast<cudaStream_t>(cuda_stream)));
+  GLMRT_RETURN_IF_ERROR(layer_execute_host_rows(layer, hidden, in_payload, stride, rows, t.idx.data(), t.w.data(), out_kind,
+                                                out + header_len, out_row, stream));
   return glmrt_b200_pv2_encode_response(&rh, nullptr, out + header_len, payload_bytes, out, response_capacity, response_len);
+}
+
+// ---- streamed ingress (protocol_v2/stream.rs:9-27; executor side: protocol_v2_executor.rs:1936-1945) ----
+// A stream-plan frame carries the request's rows and routes and, as its payload, a "GLMSTRM2" plan:
+// the order in which the hidden rows will arrive and, for the sender's benefit, groups of routes that
+// become ready after so many rows.  Stream-data frames follow, each with a run of hidden rows in that
+// order (their route_count field is the position of the first row); the last one carries the
+// stream-final flag.  The reference starts expert work group by group while rows are still arriving;
+// this executor stages the rows as they come and runs the request when the final frame is in, which
+// gives the same response as the regular request (the reference tests exactly that equality).
+struct StreamSession {
+  glmrt_b200_pv2_request_header_t head{};
+  RouteTables tables;
+  std::vector<uint32_t> order;      // activation_row_order
+  std::vector<uint8_t> hidden;      // staged rows, request order, `stride` bytes each
+  std::vector<uint8_t> have;
+  size_t stride = 0, received = 0;
+  bool in_payload = false;
+};
+std::mutex g_stream_mutex;
+std::map<void*, StreamSession> g_streams;    // one pending streamed request per layer handle (lane)
+
+constexpr size_t kStreamPlanHeaderLen = 40, kStreamPlanGroupLen = 20;
+
+glmrt_status_t parse_stream_plan(const uint8_t* p, size_t n, uint32_t rows, uint32_t routes, std::vector<uint32_t>* order) {
+  if (n < kStreamPlanHeaderLen) return bad("stream plan frame too short: " + std::to_string(n));
+  if (std::memcmp(p, "GLMSTRM2", 8) != 0) return bad("stream plan magic mismatch");
+  if (get16(p + 8) != 1) return bad("unsupported stream plan version " + std::to_string(get16(p + 8)));
+  if (get16(p + 10) != kStreamPlanHeaderLen) return bad("stream plan header length did not match 40");
+  if (get32(p + 12) != n) return bad("stream plan wire bytes " + std::to_string(get32(p + 12)) + " did not match " + std::to_string(n));
+  const uint32_t row_count = get32(p + 16), route_count = get32(p + 20), activation = get32(p + 24), groups = get32(p + 28),
+                 route_indices = get32(p + 32), completed = get32(p + 36);
+  const uint64_t expect = kStreamPlanHeaderLen + uint64_t(groups) * kStreamPlanGroupLen +
+                          4ull * (uint64_t(activation) + route_indices + completed);
+  if (expect != n) return bad("stream plan section bytes " + std::to_string(expect) + " did not match " + std::to_string(n));
+  if (row_count != rows) return bad("stream plan rows " + std::to_string(row_count) + " did not match request rows " + std::to_string(rows));
+  if (route_count != routes)
+    return bad("stream plan routes " + std::to_string(route_count) + " did not match request routes " + std::to_string(routes));
+  if (activation != rows) return bad("stream plan activation order must name every row once");
+  const uint8_t* act = p + kStreamPlanHeaderLen + size_t(groups) * kStreamPlanGroupLen;
+  const uint8_t* rts = act + 4ull * activation;
+  const uint8_t* done = rts + 4ull * route_indices;
+  order->resize(activation);
+  std::vector<uint8_t> seen(rows, 0);
+  for (uint32_t i = 0; i < activation; ++i) {
+    const uint32_t r = get32(act + 4ull * i);
+    if (r >= rows || seen[r]) return bad("stream plan activation order is not a permutation of the rows");
+    seen[r] = 1;
+    (*order)[i] = r;
+  }
+  for (uint32_t g = 0; g < groups; ++g) {
+    const uint8_t* q = p + kStreamPlanHeaderLen + size_t(g) * kStreamPlanGroupLen;
+    const uint64_t ready = get32(q), r_off = get32(q + 4), r_cnt = get32(q + 8), c_off = get32(q + 12), c_cnt = get32(q + 16);
+    if (ready == 0 || ready > rows) return bad("stream group " + std::to_string(g) + " ready-after row count is out of range");
+    if (r_off + r_cnt > route_indices) return bad("stream group " + std::to_string(g) + " route range is invalid");
+    if (c_off + c_cnt > completed) return bad("stream group " + std::to_string(g) + " completion range is invalid");
+    for (uint64_t i = 0; i < r_cnt; ++i)
+      if (get32(rts + 4 * (r_off + i)) >= routes) return bad("stream group " + std::to_string(g) + " names a route outside the request");
+    for (uint64_t i = 0; i < c_cnt; ++i)
+      if (get32(done + 4 * (c_off + i)) >= rows) return bad("stream group " + std::to_string(g) + " names a row outside the request");
+  }
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t begin_stream(void* layer, const uint8_t* b, const glmrt_b200_pv2_request_header_t& h,
+                            const glmrt_b200_pv2_sections_t& sec, const LayerDims& d) {
+  StreamSession s;
+  s.head = h;
+  GLMRT_RETURN_IF_ERROR(check_request_against_layer(h, d, h.row_count, &s.in_payload));
+  GLMRT_RETURN_IF_ERROR(build_route_tables(b, h, sec, d, &s.tables));
+  GLMRT_RETURN_IF_ERROR(parse_stream_plan(b + sec.payload_offset, sec.payload_bytes, h.row_count, h.route_count, &s.order));
+  s.stride = h.hidden_row_stride_bytes;
+  s.hidden.assign(size_t(h.row_count) * s.stride, 0);
+  s.have.assign(h.row_count, 0);
+  std::lock_guard<std::mutex> lock(g_stream_mutex);
+  g_streams[layer] = std::move(s);      // a plan replaces an unfinished stream on the same handle
+  return GLMRT_STATUS_OK;
+}
+
+glmrt_status_t continue_stream(void* layer, const uint8_t* b, const glmrt_b200_pv2_request_header_t& h,
+                               const glmrt_b200_pv2_sections_t& sec, void* response_out, size_t response_capacity,
+                               size_t* response_len, cudaStream_t stream) {
+  StreamSession done;
+  {
+    std::lock_guard<std::mutex> lock(g_stream_mutex);
+    auto it = g_streams.find(layer);
+    if (it == g_streams.end()) return bad("executor: stream data frame without a stream plan on this handle");
+    StreamSession& s = it->second;
+    if (h.request_id != s.head.request_id || h.layer_id != s.head.layer_id || h.placement_version != s.head.placement_version)
+      return bad("executor: stream data frame does not belong to the pending stream plan");
+    if (h.hidden_dim != s.head.hidden_dim || h.hidden_dtype != s.head.hidden_dtype || h.hidden_row_stride_bytes != s.stride)
+      return bad("executor: stream data frame rows differ in shape from the stream plan");
+    const uint64_t first = h.route_count;     // position of the first row in the plan's activation order
+    if (first + h.row_count > s.order.size())
+      return bad("executor: stream data rows " + std::to_string(first) + ".." + std::to_string(first + h.row_count) +
+                 " exceed the plan's " + std::to_string(s.order.size()) + " rows");
+    for (uint32_t i = 0; i < h.row_count; ++i) {
+      const uint32_t row = s.order[first + i];
+      if (s.have[row]) return bad("executor: stream data row " + std::to_string(row) + " arrived twice");
+      std::memcpy(s.hidden.data() + size_t(row) * s.stride, b + sec.payload_offset + size_t(i) * s.stride, s.stride);
+      s.have[row] = 1;
+      ++s.received;
+    }
+    if (!(h.flags & GLMRT_B200_PV2_FLAG_STREAM_FINAL)) {
+      *response_len = 0;      // nothing to send back yet
+      return GLMRT_STATUS_OK;
+    }
+    if (s.received != s.order.size()) {
+      const size_t got = s.received, want = s.order.size();
+      g_streams.erase(it);
+      return bad("executor: final stream data frame after " + std::to_string(got) + " of " + std::to_string(want) + " rows");
+    }
+    done = std::move(s);
+    g_streams.erase(it);
+  }
+  return run_and_frame(layer, done.head, done.head.row_count, done.hidden.data(), done.stride, done.in_payload, done.tables,
+                       response_out, response_capacity, response_len, stream);
+}
+
+}  // namespace
+
+void drop_stream_session(void* layer) {
+  std::lock_guard<std::mutex> lock(g_stream_mutex);
+  g_streams.erase(layer);
+}
+
+}  // namespace glmrt
+
+extern "C" glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* request_frame, size_t request_bytes,
+                                                 void* response_out, size_t response_capacity, size_t* response_len,
+                                                 void* cuda_stream) {
+  if (layer == nullptr || request_frame == nullptr || response_len == nullptr)
+    return fail(GLMRT_STATUS_INVALID_ARGUMENT, "pv2_execute: null pointer argument");
+  const uint8_t* b = static_cast<const uint8_t*>(request_frame);
+  glmrt_b200_pv2_request_header_t h;
+  glmrt_b200_pv2_sections_t sec;
+  GLMRT_RETURN_IF_ERROR(parse_request(b, request_bytes, &h, &sec));
+  if (h.flags & GLMRT_B200_PV2_FLAG_LAYER_BLOCK)
+    return bad("executor: layer-block requests (attention blocks on the expert hosts) are not supported, only routed-expert requests");
+  // the reference's executors check the checksum of a frame that carries one (synthetic.rs:124)
+  GLMRT_RETURN_IF_ERROR(glmrt_b200_pv2_verify_request_checksum(request_frame, request_bytes));
+  LayerDims d;
+  GLMRT_RETURN_IF_ERROR(layer_dims(layer, &d));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (h.flags & GLMRT_B200_PV2_FLAG_STREAM_PLAN) {
+    GLMRT_RETURN_IF_ERROR(begin_stream(layer, b, h, sec, d));
+    *response_len = 0;
+    return ok();
+  }
+  if (h.flags & GLMRT_B200_PV2_FLAG_STREAM_DATA) {
+    const glmrt_status_t st = continue_stream(layer, b, h, sec, response_out, response_capacity, response_len, stream);
+    return st == GLMRT_STATUS_OK ? ok() : st;
+  }
+  bool in_payload = false;
+  GLMRT_RETURN_IF_ERROR(check_request_against_layer(h, d, h.row_count, &in_payload));
+  RouteTables t;
+  GLMRT_RETURN_IF_ERROR(build_route_tables(b, h, sec, d, &t));
+  return run_and_frame(layer, h, h.row_count, b + sec.payload_offset, h.hidden_row_stride_bytes, in_payload, t, response_out,
+                       response_capacity, response_len, stream);
 }

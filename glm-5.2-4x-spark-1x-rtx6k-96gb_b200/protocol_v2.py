@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 import enum
+import struct
 from dataclasses import dataclass, field
 
 from . import native as N
@@ -171,6 +172,70 @@ class ExpertProtocolV2Request:
                    [view.row(i) for i in range(view.row_descriptor_count)],
                    [view.route(i) for i in range(view.route_entry_count)],
                    view.hidden_payload(), h.hidden_row_stride_bytes, h.flags)
+
+
+@dataclass
+class ExpertProtocolV2StreamRouteGroup:
+    """protocol_v2/stream.rs:14-19: routes that can run once ``ready_after_rows`` rows have arrived."""
+    ready_after_rows: int
+    route_indices: list
+    completed_rows: list
+
+
+@dataclass
+class ExpertProtocolV2StreamPlan:
+    """The "GLMSTRM2" payload of a stream-plan frame (protocol_v2/stream.rs:21-27, encode :86-150):
+    the order in which the hidden rows will arrive and the completion-first route groups.  This is
+    the sender's side of streamed ingress; the library parses it in ``glmrt_b200_pv2_execute``."""
+    row_count: int
+    route_count: int
+    activation_row_order: list
+    groups: list = field(default_factory=list)
+
+    def encode(self) -> bytes:
+        route_indices = [r for g in self.groups for r in g.route_indices]
+        completed = [r for g in self.groups for r in g.completed_rows]
+        wire = 40 + 20 * len(self.groups) + 4 * (len(self.activation_row_order) + len(route_indices) + len(completed))
+        out = b"GLMSTRM2" + struct.pack("<HHIIIIIII", 1, 40, wire, self.row_count, self.route_count,
+                                        len(self.activation_row_order), len(self.groups), len(route_indices),
+                                        len(completed))
+        r_off = c_off = 0
+        for g in self.groups:
+            out += struct.pack("<IIIII", g.ready_after_rows, r_off, len(g.route_indices), c_off, len(g.completed_rows))
+            r_off += len(g.route_indices)
+            c_off += len(g.completed_rows)
+        for seq in (self.activation_row_order, route_indices, completed):
+            out += struct.pack(f"<{len(seq)}I", *seq)
+        assert len(out) == wire
+        return out
+
+
+def streamed_request_frames(request: "ExpertProtocolV2Request", plan: ExpertProtocolV2StreamPlan, rows_per_frame: int,
+                            lib: N.NativeLibrary | None = None) -> list:
+    """The frames of a streamed request: the stream-plan frame (the request's rows and routes, the
+    plan as payload), then stream-data frames with runs of hidden rows in the plan's activation
+    order, the last one flagged final (protocol_v2/request.rs:183-230, 521-531: a data frame has
+    no descriptors and its route_count field is the position of its first row)."""
+    stride = request.hidden_row_stride_bytes or request.hidden_dtype.row_bytes(request.hidden_dim, lib)
+    base_flags = request.flags & ~(EXPERT_PROTOCOL_V2_FLAG_STREAM_PLAN | EXPERT_PROTOCOL_V2_FLAG_STREAM_DATA |
+                                   EXPERT_PROTOCOL_V2_FLAG_STREAM_FINAL | EXPERT_PROTOCOL_V2_FLAG_DEBUG_CHECKSUM)
+    head = ExpertProtocolV2Request(request.request_id, request.placement_version, request.layer_id, request.hidden_dim,
+                                   request.hidden_dtype, request.rows, request.routes, plan.encode(), stride,
+                                   base_flags | EXPERT_PROTOCOL_V2_FLAG_STREAM_PLAN)
+    frames = [head.encode(lib)]
+    order = plan.activation_row_order
+    for first in range(0, len(order), rows_per_frame):
+        run = order[first:first + rows_per_frame]
+        payload = b"".join(request.hidden_payload[r * stride:(r + 1) * stride] for r in run)
+        flags = base_flags | EXPERT_PROTOCOL_V2_FLAG_STREAM_DATA
+        if first + rows_per_frame >= len(order):
+            flags |= EXPERT_PROTOCOL_V2_FLAG_STREAM_FINAL
+        h = b"GLMRTE2\0" + struct.pack("<HHI", 2, 1, EXPERT_PROTOCOL_V2_REQUEST_HEADER_LEN)
+        h += struct.pack("<QQIIIHHIIIQQQII", request.request_id, request.placement_version, request.layer_id, len(run),
+                         request.hidden_dim, int(request.hidden_dtype), 0, first, 0, 0, len(payload), len(payload),
+                         EXPERT_PROTOCOL_V2_REQUEST_HEADER_LEN + len(payload), flags, stride) + b"\0" * 4
+        frames.append(h + payload)
+    return frames
 
 
 class ExpertProtocolV2RequestView:
@@ -348,7 +413,8 @@ class B200MoeExecutor(ProtocolV2ExpertExecutor):
         return B200_EXECUTOR_NAME
 
     def execute_frame(self, frame: bytes) -> bytes:
-        """Request frame in, response frame out."""
+        """Request frame in, response frame out (empty for a stream-plan frame and for every
+        stream-data frame but the final one: their rows are staged, nothing is sent back yet)."""
         frame = bytes(frame)
         cap = EXPERT_PROTOCOL_V2_REQUEST_DEBUG_HEADER_LEN + self.layer.max_tokens * self.layer.hidden * 2
         out = C.create_string_buffer(cap)

@@ -613,9 +613,10 @@ glmrt_status_t glmrt_b200_moe_layer_forward_ep_host(void* layer, const void* hid
 /* (128 with the debug checksum), 40-byte row descriptors, 10-byte route       */
 /* entries (row, expert, bf16 gate weight), then the row payload.  Regular     */
 /* request and response frames are encoded, parsed and validated with the      */
-/* reference's rules; stream-plan, stream-data and layer-block frames are      */
-/* recognised and refused by the executor.  All functions are host-only and    */
-/* need no GPU except glmrt_b200_pv2_execute.                                  */
+/* reference's rules; the executor also takes streamed ingress (a stream-plan  */
+/* frame followed by stream-data frames); layer-block frames are recognised    */
+/* and refused.  All functions are host-only and need no GPU except            */
+/* glmrt_b200_pv2_execute.                                                     */
 /* ------------------------------------------------------------------------ */
 enum {                                     /* protocol_v2.rs:10-34 */
   GLMRT_B200_PV2_REQUEST_HEADER_LEN = 96,
@@ -739,7 +740,15 @@ glmrt_status_t glmrt_b200_pv2_parse_response(const void* frame, size_t frame_byt
  * do not live on this layer's shard are refused) and writes a response frame with one partial
  * output row per request row: bf16, or NVFP4 payload rows (native rounding rule) or row-scaled
  * FP8 rows when the request's flags negotiate them.  The executor id is the compact
- * id of "b200-nvfp4-tcgen05-executor".  Synchronises `cuda_stream`. */
+ * id of "b200-nvfp4-tcgen05-executor".  Synchronises `cuda_stream`.
+ * Streamed ingress (protocol_v2/stream.rs:9-27, protocol_v2_executor.rs:1936-1945): a frame with
+ * GLMRT_B200_PV2_FLAG_STREAM_PLAN carries the request's rows and routes and a "GLMSTRM2" plan
+ * (an ordering of the rows in route groups) as its payload and opens a stream on `layer`; the
+ * frames with GLMRT_B200_PV2_FLAG_STREAM_DATA that follow carry the payload rows named in their
+ * row table.  Those calls return OK with *response_len = 0; the call that brings the frame with
+ * GLMRT_B200_PV2_FLAG_STREAM_FINAL runs the request and writes the response a regular request
+ * with the same rows would get.  One stream per layer handle at a time: a new plan frame replaces
+ * the stream in progress, and a final frame that comes before every row has arrived ends it. */
 glmrt_status_t glmrt_b200_pv2_execute(void* layer, const void* request_frame, size_t request_bytes,
                                       void* response_out, size_t response_capacity,
                                       size_t* response_len, void* cuda_stream);

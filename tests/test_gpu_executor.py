@@ -189,3 +189,59 @@ def test_executor_output_against_both_oracle_modes(pkg, ref_layer):
     assert e1 <= 2e-2
     assert 2e-2 < e0 < 0.35      # the W4A4 / W4A16 gap: real, and bounded
     layer.close()
+
+
+def test_streamed_ingress_gives_the_regular_response(pkg, ref_layer):
+    """Streamed ingress (protocol_v2/stream.rs; the reference tests that a streamed request and the
+    regular request give the same response, protocol_v2_executor.rs:3430-3503): a stream-plan frame
+    with the rows, the routes and the order of arrival, then stream-data frames with runs of hidden
+    rows in that order.  Nothing is answered until the final data frame; the answer then equals the
+    regular request's, bit for bit.  Malformed streams are refused without touching the stream's
+    state or the GPU context."""
+    from glmrt_b200 import native as N
+    from glmrt_b200 import protocol_v2 as P
+    from glmrt_b200.layer import MoeLayer
+    H, I, E, K, T = 512, 256, 16, 4, 11
+    layer = MoeLayer(H, I, E, K, max_tokens=16)
+    layer.load_quantized_layer(ref_layer)
+    ex = P.B200MoeExecutor(layer)
+    hid = O.make_hidden(35, T, H)
+    _, idx, w = layer.forward(to_dev(hid), want_routes=True)
+    idx, w = idx.cpu().numpy(), w.cpu().numpy()
+    req = build_request(P, hid, idx, w, request_id=901)
+    regular = ex.execute_frame(req.encode())
+    rng = np.random.default_rng(5)
+    order = [int(r) for r in rng.permutation(T)]
+    # completion-first groups as a coordinator would send them: routes of the rows staged so far
+    groups, staged = [], set()
+    for n_ready in (4, 8, T):
+        new_rows = [r for r in order[:n_ready] if r not in staged]
+        staged.update(new_rows)
+        groups.append(P.ExpertProtocolV2StreamRouteGroup(n_ready, [r * K + k for r in new_rows for k in range(K)], new_rows))
+    plan = P.ExpertProtocolV2StreamPlan(T, T * K, order, groups)
+    for rows_per_frame in (3, T, 1):
+        frames = P.streamed_request_frames(req, plan, rows_per_frame)
+        assert len(frames) == 1 + -(-T // rows_per_frame)
+        answers = [ex.execute_frame(f) for f in frames]
+        assert all(a == b"" for a in answers[:-1])
+        assert answers[-1] == regular
+    # a data frame without a plan, a plan that is not a permutation, a row that arrives twice, an early final frame
+    frames = P.streamed_request_frames(req, plan, 4)
+    with pytest.raises(N.GlmrtError, match="without a stream plan"):
+        ex.execute_frame(frames[1])
+    bad_plan = P.ExpertProtocolV2StreamPlan(T, T * K, [0] + order[1:] if order[0] != 0 else [1] + order[1:], [])
+    with pytest.raises(N.GlmrtError, match="not a permutation"):
+        ex.execute_frame(P.streamed_request_frames(req, bad_plan, 4)[0])
+    ex.execute_frame(frames[0])
+    ex.execute_frame(frames[1])
+    with pytest.raises(N.GlmrtError, match="arrived twice"):
+        ex.execute_frame(frames[1])
+    with pytest.raises(N.GlmrtError, match="of 11 rows"):
+        ex.execute_frame(frames[-1])                      # final frame while rows are missing: the stream is dropped
+    with pytest.raises(N.GlmrtError, match="without a stream plan"):
+        ex.execute_frame(frames[2])
+    # and a complete stream still works afterwards
+    answers = [ex.execute_frame(f) for f in frames]
+    assert answers[-1] == regular
+    layer.check()
+    layer.close()
