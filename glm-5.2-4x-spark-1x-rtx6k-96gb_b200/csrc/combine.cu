@@ -11,6 +11,8 @@
 #include "ep_flags.cuh"
 #include "internal.h"
 
+GLMRT_CHAIN_TRACE_TU(combine)
+
 namespace glmrt {
 namespace {
 
@@ -36,8 +38,10 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
                       const int32_t* __restrict__ route_slot, uint16_t* __restrict__ out, int rows, int top_k,
                       int hidden, const uint16_t* __restrict__ residual, const uint16_t* __restrict__ shared,
                       EpWait wait, uint32_t* error_word) {
+  GLMRT_CHAIN_SCOPE(kChainCombine);
   pdl_launch_dependents();
   pdl_wait();
+  GLMRT_CHAIN_READY();
   if (wait.flags != nullptr) {
     // expert-parallel path: the route rows are stored by the owners of the experts; their flags say when
     __shared__ uint32_t s_wait_err;
@@ -48,6 +52,7 @@ combine_routes_kernel(const uint16_t* __restrict__ route_rows, const float* __re
     __syncthreads();
     if (s_wait_err != 0u) return;
   }
+  GLMRT_CHAIN_MARK(0);
   const int vec_per_row = hidden / 8;
   const size_t gid = blockIdx.x * static_cast<size_t>(kThreads) + threadIdx.x;
   if (gid >= static_cast<size_t>(rows) * vec_per_row) return;

@@ -92,6 +92,88 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #endif
 
+// ---- optional timeline of the kernels of a forward pass (trace builds only) ----
+// A library built with -DGLMRT_B200_TRACE (build.py --trace) stamps, per kernel of the chain and
+// per launch, the global timer when the first and the last CTA start, when the first CTA is past
+// its pdl_wait(), and when the last warp leaves.  A kernel never overlaps its own next launch
+// (the other kernels of the pass lie between, each waiting for its predecessor to complete), so
+// the launch number is the count of CTA arrivals divided by the grid size.  Every translation unit
+// with chain kernels keeps its own table (GLMRT_CHAIN_TRACE_TU defines it and a C accessor);
+// trace_chain.py merges them.  The product library has none of this.
+enum ChainKernel : int {
+  kChainLogits = 0, kChainSelect, kChainQuantDispatch, kChainFc1, kChainFc2, kChainCombine,
+  kChainEpPlanDispatch, kChainEpCount, kChainEpRetile, kChainPlan, kChainKernels
+};
+#if defined(GLMRT_B200_TRACE) && defined(__CUDACC__)
+constexpr int kChainLaunches = 16;   // ring over launches
+constexpr int kChainStamps = 12;     // first CTA start, last CTA start, first CTA past its wait, last warp out, 8 marks
+#define GLMRT_CHAIN_TRACE_TU(name)                                                                              \
+  namespace glmrt { namespace {                                                                                \
+  __device__ unsigned long long g_chain_table[kChainLaunches * kChainKernels * kChainStamps];                   \
+  __device__ unsigned int g_chain_arrivals[kChainKernels];                                                      \
+  } }                                                                                                           \
+  extern "C" int glmrt_b200_trace_chain_##name(unsigned long long* out, int reset) {                            \
+    if (out != nullptr &&                                                                                       \
+        cudaMemcpyFromSymbol(out, glmrt::g_chain_table, sizeof(glmrt::g_chain_table)) != cudaSuccess) return 1; \
+    if (reset) {                                                                                                \
+      static unsigned long long init[glmrt::kChainLaunches * glmrt::kChainKernels * glmrt::kChainStamps];       \
+      for (int i = 0; i < glmrt::kChainLaunches * glmrt::kChainKernels; ++i) {                                  \
+        unsigned long long* r = init + i * glmrt::kChainStamps;                                                 \
+        for (int j = 0; j < glmrt::kChainStamps; ++j) r[j] = 0ull;                                              \
+        r[0] = ~0ull; r[2] = ~0ull;                                                                             \
+      }                                                                                                         \
+      static unsigned int zeros[glmrt::kChainKernels];                                                          \
+      if (cudaMemcpyToSymbol(glmrt::g_chain_table, init, sizeof(init)) != cudaSuccess) return 1;                \
+      if (cudaMemcpyToSymbol(glmrt::g_chain_arrivals, zeros, sizeof(zeros)) != cudaSuccess) return 1;           \
+    }                                                                                                           \
+    return 0;                                                                                                   \
+  }
+#define GLMRT_CHAIN_SCOPE(id) ChainScope chain_scope__(id, g_chain_table, g_chain_arrivals)
+#define GLMRT_CHAIN_READY() chain_scope__.ready()
+#define GLMRT_CHAIN_MARK(i) chain_mark(i)   /* latest time any CTA's thread 0 passed mark i (0..7) */
+#define GLMRT_CHAIN_MARK_HERE(i) chain_mark_here(i)   /* the same, stamped by the calling thread */
+static __shared__ unsigned long long* s_chain_row;   // set by the kernel's ChainScope; device functions mark through it
+struct ChainScope {
+  unsigned long long* row;
+  __device__ __forceinline__ static unsigned long long now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+  }
+  __device__ __forceinline__ ChainScope(int id, unsigned long long* table, unsigned int* arrivals) {
+    __shared__ unsigned int launch_index;
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+      const unsigned int ctas = gridDim.x * gridDim.y * gridDim.z;
+      launch_index = atomicAdd(&arrivals[id], 1u) / ctas;
+    }
+    __syncthreads();
+    row = table + (static_cast<size_t>(launch_index % kChainLaunches) * kChainKernels + id) * kChainStamps;
+    s_chain_row = row;   // every thread stores the same value
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+      const unsigned long long t = now();
+      atomicMin(row + 0, t);
+      atomicMax(row + 1, t);
+    }
+  }
+  __device__ __forceinline__ void ready() const {
+    if (threadIdx.x == 0 && threadIdx.y == 0) atomicMin(row + 2, now());
+  }
+  __device__ __forceinline__ ~ChainScope() {
+    if ((threadIdx.x & 31) == 0) atomicMax(row + 3, now());
+  }
+};
+__device__ __forceinline__ void chain_mark(int i) {
+  if (threadIdx.x == 0 && threadIdx.y == 0) atomicMax(s_chain_row + 4 + i, ChainScope::now());
+}
+__device__ __forceinline__ void chain_mark_here(int i) { atomicMax(s_chain_row + 4 + i, ChainScope::now()); }
+#else
+#define GLMRT_CHAIN_TRACE_TU(name)
+#define GLMRT_CHAIN_SCOPE(id) do { } while (0)
+#define GLMRT_CHAIN_READY() do { } while (0)
+#define GLMRT_CHAIN_MARK(i) do { } while (0)
+#define GLMRT_CHAIN_MARK_HERE(i) do { } while (0)
+#endif
+
 // ---- device-side formats ----
 #ifdef __CUDACC__
 
@@ -162,6 +244,20 @@ __device__ __forceinline__ float sigmoid_f32(float v) {
   }
   const float e = expf(v);
   return e / (1.0f + e);
+}
+
+// The weights of one 128-row tile of a projection (codes and tiled scales) are asked into the L2,
+// one 128-byte line per thread and pass, by all `threads` threads of a CTA; nothing waits for them.
+__device__ __forceinline__ void l2_prefetch_lines(const uint8_t* p, size_t bytes, int threads) {
+  for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < bytes; off += static_cast<size_t>(threads) * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off) : "memory");
+}
+__device__ __forceinline__ void l2_prefetch_weight_tile(const uint8_t* codes, const uint8_t* sf, size_t first_row,
+                                                        int row_bytes, int threads) {
+  l2_prefetch_lines(codes + first_row * static_cast<size_t>(row_bytes), 128 * static_cast<size_t>(row_bytes), threads);
+  // scale tiles: 512 bytes per (128 rows, 64 elements of K)
+  l2_prefetch_lines(sf + (first_row / 128) * static_cast<size_t>(row_bytes / 32) * 512,
+                    static_cast<size_t>(row_bytes / 32) * 512, threads);
 }
 
 // Byte offset of the scale of (row r, 16-element block j) in the tiled scale layout the

@@ -26,6 +26,8 @@
 #include "internal.h"
 #include "quant_block.cuh"
 
+GLMRT_CHAIN_TRACE_TU(ep)
+
 namespace glmrt {
 namespace {
 
@@ -51,8 +53,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_count_kernel(EpArgs a, const ui
     a.ctrl->cursor[e] = 0;
   }
   if (threadIdx.x == 0) a.counters[kCntError] = static_cast<uint32_t>(s_err);  // also clears the word
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // the release below is cumulative over what the barrier ordered before it
   if (threadIdx.x < a.world) st_release_sys(&a.peer_ctrl[threadIdx.x]->flag_counts[a.rank], a.epoch);
 }
 
@@ -73,15 +74,19 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   __shared__ int s_err;
   __shared__ int s_owner_slots[kEpMaxWorld];
   __shared__ int s_pos[64];
+  __shared__ int s_expert[64];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
+  GLMRT_CHAIN_SCOPE(kChainEpPlanDispatch);
   pdl_launch_dependents();
   if (threadIdx.x == 0) s_err = 0;
   __syncthreads();
   pdl_wait();   // the routes (and the cleared cursors) come from the router's kernels
+  GLMRT_CHAIN_READY();
   if (threadIdx.x < a.world && !wait_flag(&a.ctrl->flag_counts[threadIdx.x], a.epoch))
     atomicOr(&s_err, static_cast<int>(kErrWaitTimeout));
   __syncthreads();
+  GLMRT_CHAIN_MARK(0);
   const bool have_counts = s_err == 0;
   for (int e = threadIdx.x; e < a.experts; e += kPushThreads) {
     int tot = 0, mine = 0;
@@ -118,6 +123,7 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
     }
   }
   __syncthreads();
+  GLMRT_CHAIN_MARK(1);
 
   if (blockIdx.x == 0) {
     // this rank's own work items: chunk offsets by a scan over its experts (warp 0), then every
@@ -188,22 +194,53 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
     atomicOr(&a.ctrl->plan_failed, 1);   // read by the last CTA: one failing CTA poisons the whole push
   }
 
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  const int push_ctas = static_cast<int>(gridDim.x) - p.prefetch.tiles;
+  if (static_cast<int>(blockIdx.x) >= push_ctas && plan_ok) {
+    // an extra CTA: asks the L2 for the gate and up weights of one (work item, 128-row tile) pair of
+    // this rank's FC1, in FC1's tile order, while the rows travel
+    __shared__ int s_pf_expert;
+    if (threadIdx.x == 0) {
+      const int feat_tiles = p.prefetch.rows_per_expert / 128;
+      const int want = (static_cast<int>(blockIdx.x) - push_ctas) / feat_tiles;   // work item number
+      const int n_local = (a.experts - a.rank + a.world - 1) / a.world;
+      int seen = 0, found = -1;
+      for (int i = 0; i < n_local && found < 0; ++i) {
+        const int items = (s_tot[a.rank + i * a.world] + p.chunk_tokens - 1) / p.chunk_tokens;
+        if (want < seen + items) found = i;
+        seen += items;
+      }
+      s_pf_expert = found;
+    }
+    __syncthreads();
+    if (s_pf_expert >= 0) {
+      const int feat_tiles = p.prefetch.rows_per_expert / 128;
+      const size_t first_row = static_cast<size_t>(s_pf_expert) * p.prefetch.rows_per_expert +
+                               static_cast<size_t>((static_cast<int>(blockIdx.x) - push_ctas) % feat_tiles) * 128;
+      l2_prefetch_weight_tile(p.prefetch.w0, p.prefetch.sf0, first_row, p.prefetch.row_bytes, kPushThreads);
+      l2_prefetch_weight_tile(p.prefetch.w1, p.prefetch.sf1, first_row, p.prefetch.row_bytes, kPushThreads);
+    }
+  }
+  for (int row = blockIdx.x; row < rows && static_cast<int>(blockIdx.x) < push_ctas; row += push_ctas) {
     const int code_bytes = hidden_dim / 2, kblocks = hidden_dim / 16;
     __syncthreads();   // the previous row's image and positions have been read
     const size_t row_bytes = static_cast<size_t>(code_bytes + kblocks);
     if (plan_ok) {
+      // positions of the row's routes among this rank's routes of each expert: asked for first, the
+      // round trips of the id load and of the counter run under the quantisation of the row
+      if (threadIdx.x < top_k) {
+        const uint32_t e = p.topk_indices[row * top_k + threadIdx.x];
+        s_expert[threadIdx.x] = static_cast<int>(e);
+        s_pos[threadIdx.x] = e < static_cast<uint32_t>(a.experts) ? atomicAdd(&a.ctrl->cursor[e], 1) : -1;
+      }
       if (hidden != nullptr) {
-        quantize_row_to_image(hidden + static_cast<size_t>(row) * hidden_dim, img, hidden_dim, kPushThreads);
+        if (a.chunk_tokens < 128)   // decode-sized step
+          quantize_row_to_image<true>(hidden + static_cast<size_t>(row) * hidden_dim, img, hidden_dim, kPushThreads);
+        else
+          quantize_row_to_image<false>(hidden + static_cast<size_t>(row) * hidden_dim, img, hidden_dim, kPushThreads);
       } else {
         const uint4* src = reinterpret_cast<const uint4*>(payload + row * row_bytes);
         for (int i = threadIdx.x; i < static_cast<int>(row_bytes / 16); i += kPushThreads)
           reinterpret_cast<uint4*>(img)[i] = src[i];
-      }
-      // positions of the row's routes among this rank's routes of each expert
-      if (threadIdx.x < top_k) {
-        const uint32_t e = p.topk_indices[row * top_k + threadIdx.x];
-        s_pos[threadIdx.x] = e < static_cast<uint32_t>(a.experts) ? atomicAdd(&a.ctrl->cursor[e], 1) : -1;
       }
       __syncthreads();
       if (hidden != nullptr) {
@@ -219,7 +256,7 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
           if (threadIdx.x == 0) p.route_slot[route] = -1;
           continue;
         }
-        const int e = static_cast<int>(p.topk_indices[route]);
+        const int e = s_expert[k];
         const int owner = e % a.world;
         const int slot = s_base[e] + slot_of_position(s_mine[e] + pos, a.chunk_tokens);
         uint4* dst4 = reinterpret_cast<uint4*>(a.peer_act_codes[owner] + static_cast<size_t>(slot) * code_bytes);
@@ -247,13 +284,17 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   }
 
   // last CTA to finish tells every owner that this rank's rows have landed -- or that none will
-  __threadfence_system();
+  // (one thread fences for the CTA: the barrier orders every thread's stores before its fence)
   __syncthreads();
+  GLMRT_CHAIN_MARK(2);
   __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == static_cast<int>(gridDim.x) - 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == static_cast<int>(gridDim.x) - 1;
+    if (s_last) __threadfence_system();
+  }
   __syncthreads();
   if (s_last) {
-    __threadfence_system();
     const bool failed = *reinterpret_cast<volatile int32_t*>(&a.ctrl->plan_failed) != 0;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -276,8 +317,10 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
 __global__ void __launch_bounds__(256)
 ep_retile_scales_kernel(EpWait w, const uint8_t* __restrict__ sf_rows, uint8_t* __restrict__ sf_tiled, int kblocks,
                         const uint32_t* counters, uint32_t* error_word, uint32_t* chunk_count) {
+  GLMRT_CHAIN_SCOPE(kChainEpRetile);
   pdl_launch_dependents();
   pdl_wait();
+  GLMRT_CHAIN_READY();
   __shared__ uint32_t s_err;
   if (threadIdx.x == 0) {
     s_err = ep_wait_all_serial(w);
@@ -361,7 +404,7 @@ glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const
   const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
   if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
   // every CTA derives the layout once, so large batches walk their rows with a bounded grid
-  const int grid = rows > 0 ? (rows < 1184 ? rows : 1184) : 1;
+  const int grid = (rows > 0 ? (rows < 1184 ? rows : 1184) : 1) + (p.prefetch.w0 != nullptr ? p.prefetch.tiles : 0);
   launch_pdl(ep_plan_dispatch_kernel, dim3(grid), dim3(kPushThreads), smem, stream, a, p, hidden, payload,
              rows, top_k, hidden_dim);
   GLMRT_LAUNCH_CHECK("ep_plan_dispatch_kernel");

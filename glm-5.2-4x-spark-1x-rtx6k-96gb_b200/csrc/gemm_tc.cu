@@ -33,6 +33,8 @@
 #include "internal.h"
 #include "tc_ptx.cuh"
 
+GLMRT_CHAIN_TRACE_TU(gemm)
+
 namespace glmrt {
 namespace {
 
@@ -97,6 +99,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
                    const __grid_constant__ CUtensorMap map_b) {
   using C = Cfg<kFC1, kBN>;
   constexpr bool kDynamic = kOverlap && !kFC1;   // tiles drawn from a counter instead of a fixed stride
+  GLMRT_CHAIN_SCOPE(kFC1 ? kChainFc1 : kChainFc2);
   if (!(kOverlap && kFC1)) pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
@@ -122,6 +125,11 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   const int feat_tiles = out_rows / kTileRows;
   const int k_tiles64 = k_bytes / 32;                        // scale tiles (64 elements) along K
 
+  if (threadIdx.x == 32) {   // the maps are kernel parameters: fetched while the previous kernel still runs
+    prefetch_tensormap(&map_a0);
+    if (kFC1) prefetch_tensormap(&map_a1);
+    prefetch_tensormap(&map_b);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -150,20 +158,25 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   // FC1's completion (FC1 raised launch_dependents only after everything older than itself was
   // complete); it reads what it needs of FC1 tile by tile, below.
   if (!kDynamic) pdl_wait();
+  GLMRT_CHAIN_READY();
   if (kOverlap && kFC1) pdl_launch_dependents();
   // a step that has already reported an error runs no expert work (and tells no peer it did)
+  const uint32_t planned_chunks = __ldcg(a.counters + kCntChunks);   // both loads in flight together
   const bool step_failed = *reinterpret_cast<const volatile uint32_t*>(a.error_word) != 0u;
-  const int num_chunks = step_failed ? 0 : static_cast<int>(__ldcg(a.counters + kCntChunks));
+  const int num_chunks = step_failed ? 0 : static_cast<int>(planned_chunks);
   const int num_tiles = num_chunks * feat_tiles;
   if (!kDynamic) {
     // The work items of this CTA's tiles are fetched once, up front: a global load at the head of
     // every tile would stall each role for a memory round trip and drain the TMA pipeline.
+    // The loads do not depend on the chunk count (entries past it are never used), so both memory
+    // round trips of this prologue overlap.
     for (int i = threadIdx.x; i < C::kChunkCache; i += blockDim.x) {
-      const long long tile = static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x;
-      if (tile < num_tiles) chunk_cache[i] = a.chunks[tile / feat_tiles];
+      const long long ci = (static_cast<long long>(blockIdx.x) + static_cast<long long>(i) * gridDim.x) / feat_tiles;
+      if (ci < a.max_chunks) chunk_cache[i] = a.chunks[ci];
     }
     __syncthreads();
   }
+  GLMRT_CHAIN_MARK(0);
   // Tile sequence of a consumer role (every lane of the warp calls it; the warp stays converged).
   auto next_tile = [&](int it, TileSlot& ts) -> bool {
     if (!kDynamic) {
@@ -229,6 +242,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           const uint32_t s_sfa0 = s_b + C::kBBytes;
           const uint32_t s_sfb = s_sfa0 + C::kNumA * kSfStageBytes;
           mbar_expect_tx(&full_bar[stage], C::kTxBytes);
+          if (it == 0 && ks == 0) GLMRT_CHAIN_MARK_HERE(1);
           tma_load_2d(s_a0, &map_a0, &full_bar[stage], ks * kStageBytesK, w_row, pol_w);
           if (kFC1) tma_load_2d(s_a0 + C::kABytes, &map_a1, &full_bar[stage], ks * kStageBytesK, w_row, pol_w);
           tma_load_2d(s_b, &map_b, &full_bar[stage], ks * kStageBytesK, ch.slot_base, pol_x);
@@ -244,6 +258,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      GLMRT_CHAIN_MARK_HERE(2);
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
@@ -267,6 +282,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         for (int ks = 0; ks < k_stages; ++ks) {
           if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag)) { alive = false; break; }
           tc_fence_after();
+          if (it == 0 && ks == 0 && lane == 0) GLMRT_CHAIN_MARK_HERE(3);
           uint8_t* st = smem + static_cast<size_t>(stage) * C::kStageBytes;
           const uint32_t s_a0 = smem_u32(st);
           const uint32_t s_b = s_a0 + C::kNumA * C::kABytes;
@@ -302,6 +318,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
         __syncwarp();
         if (C::kAccBufs == 2) { abuf ^= 1; if (abuf == 0) aphase ^= 1u; } else { aphase ^= 1u; }
       }
+      if (lane == 0) GLMRT_CHAIN_MARK_HERE(4);
     }
   } else if (warp >= 6) {
     // ================= tile scheduler (overlapped FC2 only) =================
@@ -422,6 +439,7 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
     }
   }
 
+  if (warp == 2 && lane == 0) GLMRT_CHAIN_MARK_HERE(5);
   // ---- teardown ----
   __syncwarp();
   const uint32_t aborted = *abort_flag;
@@ -430,7 +448,6 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(aborted == 2u ? kErrPeerFailed : kErrWaitTimeout));
   }
-  if (!kFC1 && a.signal.ticket != nullptr) __threadfence_system();   // result rows stored to their home ranks
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);

@@ -116,6 +116,11 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
   const int out_rows = kFC1 ? a.inter : a.hidden;
   const int feat_tiles = out_rows / C::kFeatPerTile;
 
+  if (threadIdx.x == 32) {   // the maps are kernel parameters: fetched while the previous kernel still runs
+    prefetch_tensormap(&map_act);
+    prefetch_tensormap(&map_w0);
+    if (kFC1) prefetch_tensormap(&map_w1);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -344,7 +349,6 @@ expert_gemm_tokens_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_act
     for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land
     if (threadIdx.x == 0) atomicOr(a.error_word, static_cast<uint32_t>(aborted == 2u ? kErrPeerFailed : kErrWaitTimeout));
   }
-  if (!kFC1 && a.signal.ticket != nullptr) __threadfence_system();   // result rows stored to their home ranks
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);

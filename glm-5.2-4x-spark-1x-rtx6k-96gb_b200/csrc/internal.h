@@ -90,6 +90,19 @@ GLMRT_HD inline int slot_of_position(int pos, int chunk_tokens) {
 // A route entry with this expert id is "no route": it gets no slot and is not an error (the
 // expert worker's view of a request may name fewer than top_k experts for a row).
 constexpr uint32_t kNoRoute = 0xffffffffu;
+// Weights of the first FC1 work of a decode step, asked into the L2 while the rows are quantised and
+// dispatched: between the route plan and the first weight byte FC1 itself asks for, the memory
+// system is otherwise idle for several microseconds.  One SM turns out about one 128-byte request
+// per clock (256 GB/s), so the requests are spread over extra CTAs of the dispatch kernel, one
+// (work item, 128-row tile) pair of FC1's tile order each.
+struct WeightPrefetch {
+  const uint8_t* w0 = nullptr;    // gate codes [local experts * rows_per_expert, row_bytes]; nullptr: no prefetch
+  const uint8_t* w1 = nullptr;    // up codes, same shape
+  const uint8_t* sf0 = nullptr;   // their tiled scales
+  const uint8_t* sf1 = nullptr;
+  int rows_per_expert = 0, row_bytes = 0;
+  int tiles = 0;                  // extra CTAs = pairs asked for
+};
 struct PlanArgs {
   const uint32_t* topk_indices;  // [rows * top_k] global expert ids
   int rows, top_k, experts;      // experts = global count
@@ -104,6 +117,7 @@ struct PlanArgs {
   Chunk* chunks;                 // [max_chunks]
   uint32_t* counters;            // [kCntWords]
   uint32_t* fc_sync = nullptr;   // [kFcSyncHeader + max_chunks] cleared by the plan: see FfnArgs::fc_sync
+  WeightPrefetch prefetch;       // decode-sized steps: FC1's first weight tiles (expert-parallel push kernel)
 };
 // Optional tails of the router's selection kernel, run by the last CTA of its grid to finish.
 //   expert-parallel path (world > 0): count this rank's routes per expert, store the histogram into
@@ -137,6 +151,10 @@ struct DispatchArgs {
   uint16_t* combine_out = nullptr;       // [rows, hidden] bf16 layer output, or nullptr: per-route rows
   const float* topk_weights = nullptr;   // [rows * top_k]
   uint32_t* slot_weight = nullptr;       // [max_slots] the route weight as a bf16 pair
+  // fused quantise + dispatch of a decode-sized step: CTAs past `rows` prefetch FC1 weights
+  WeightPrefetch prefetch;
+  const Chunk* chunks = nullptr;
+  const uint32_t* counters = nullptr;
 };
 glmrt_status_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
 // quant.cu: quantises bf16 rows [rows, hidden] and dispatches them in one kernel (payload rows

@@ -18,6 +18,7 @@
 // layer of the same shape: the 75 sparse layers of a model run one after another on one stream
 // and need one workspace between them.  One handle is driven by one host thread at a time;
 // handles that share a workspace must be used on one stream, in order.
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <new>
@@ -186,6 +187,32 @@ glmrt_status_t build_maps(Layer* l) {
 // batch_rows: rows of the whole batch (over all ranks where known).  The FC1 -> FC2 overlap of the
 // decode kernels pays from about eight rows on (64 routes); below that FC2's tile scheduling costs
 // more than the overlap saves (measured at one row: +1.3 us on 67), so tiny batches run the plain pair.
+// How many (work item, 128-row tile) pairs of FC1's weights a decode-sized step asks into the L2
+// while its rows are quantised and dispatched: GLMRT_B200_PREFETCH_FC1, default 48 (38 MB of the
+// GLM-5.2 shape; measured at 1 / 64 rows: 32 pairs -2.7 / -2 us, 64 pairs -1.6 / -8 us, 128 pairs
+// +5 / -10 us of 62 / 751 us); 0 turns it off.
+int prefetch_tiles_fc1() {
+  static const int n = [] {
+    const char* v = std::getenv("GLMRT_B200_PREFETCH_FC1");
+    if (v == nullptr || *v == '\0') return 48;
+    const long x = std::strtol(v, nullptr, 10);
+    return static_cast<int>(x < 0 ? 0 : x > 1024 ? 1024 : x);
+  }();
+  return n;
+}
+WeightPrefetch fc1_prefetch(const Layer* l, int chunk_tokens) {
+  const auto& c = l->cfg;
+  WeightPrefetch w;
+  if (chunk_tokens == 32 && !(c.flags & GLMRT_B200_LAYER_ENGINE_SIMT) && c.intermediate_dim % 128 == 0 &&
+      c.hidden_dim % 256 == 0 && prefetch_tiles_fc1() > 0) {
+    w.w0 = l->gate_codes; w.w1 = l->up_codes; w.sf0 = l->gate_sf; w.sf1 = l->up_sf;
+    w.rows_per_expert = static_cast<int>(c.intermediate_dim);
+    w.row_bytes = static_cast<int>(c.hidden_dim / 2);
+    w.tiles = prefetch_tiles_fc1();
+  }
+  return w;
+}
+
 FfnArgs ffn_args(const Layer* l, int chunk_tokens, size_t batch_rows) {
   FfnArgs a{};
   a.gate_codes = l->gate_codes; a.up_codes = l->up_codes; a.down_codes = l->down_codes;
@@ -232,6 +259,7 @@ PlanArgs plan_args(const Layer* l, size_t rows, int chunk_tokens) {
   p.expert_base = l->expert_base; p.block_hist = l->block_hist;
   p.chunks = l->chunks; p.counters = l->counters;
   p.fc_sync = chunk_tokens == 32 ? l->fc_sync : nullptr;
+  if (c.ep_world > 1) p.prefetch = fc1_prefetch(l, chunk_tokens);
   return p;
 }
 
@@ -277,6 +305,7 @@ glmrt_status_t run_routed(Layer* l, const uint16_t* hidden, size_t rows, uint16_
   d.payload = l->payload; d.payload_out = l->payload; d.route_slot = l->route_slot;
   d.rows = static_cast<int>(rows); d.top_k = static_cast<int>(c.top_k); d.hidden = static_cast<int>(c.hidden_dim);
   d.act_codes = l->act1_codes; d.act_sf = l->act1_sf; d.route_rows = l->route_rows; d.slot_out = l->slot_out;
+  d.prefetch = fc1_prefetch(l, chunk_tokens); d.chunks = l->chunks; d.counters = l->counters;
   // The plan needs only the routes, so it runs first and the rows are quantised and dispatched by
   // one kernel (its time is reported as the dispatch stage, the quantise stage then reads 0).
   const bool fused = hidden != nullptr && quantize_dispatch_supported(hidden, d);
@@ -931,15 +960,7 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
     case 1: {
       // wait for every histogram, derive the layout, quantise the rows and push them to their owners
       mark(l, GLMRT_B200_STAGE_PLAN, s);
-      PlanArgs p{};
-      p.topk_indices = l->topk_idx;
-      p.rows = static_cast<int>(rows); p.top_k = static_cast<int>(c.top_k); p.experts = static_cast<int>(c.experts);
-      p.ep_world = static_cast<int>(c.ep_world); p.ep_rank = static_cast<int>(c.ep_rank);
-      p.chunk_tokens = chunk_tokens; p.max_slots = l->max_slots; p.max_chunks = l->max_chunks;
-      p.route_slot = l->route_slot; p.slot_route = l->slot_route; p.expert_counts = l->expert_counts;
-      p.expert_base = l->expert_base; p.block_hist = l->block_hist;
-      p.chunks = l->chunks; p.counters = l->counters;
-      p.fc_sync = chunk_tokens == 32 ? l->fc_sync : nullptr;
+      const PlanArgs p = plan_args(l, rows, chunk_tokens);
       mark(l, GLMRT_B200_STAGE_DISPATCH, s);
       return launch_ep_plan_dispatch(a, p, hidden, l->payload, static_cast<int>(rows), static_cast<int>(c.top_k),
                                      static_cast<int>(c.hidden_dim), s);

@@ -14,14 +14,18 @@
 #include "internal.h"
 #include "plan_body.cuh"
 
+GLMRT_CHAIN_TRACE_TU(plan)
+
 namespace glmrt {
 namespace {
 
 constexpr int kPlanThreads = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads) route_plan_kernel(PlanArgs a) {
+  GLMRT_CHAIN_SCOPE(kChainPlan);
   pdl_launch_dependents();
   pdl_wait();   // the routes come from the router's kernels
+  GLMRT_CHAIN_READY();
   route_plan_body(a, kPlanThreads);
 }
 

@@ -13,29 +13,62 @@ namespace glmrt {
 
 constexpr int kMaxLocalExperts = 1024;
 
+// chunk_tokens is 32, 128 or 256: the slot arithmetic of expert_slot_span / slot_of_position with
+// shifts (this runs on the critical path of every decode step).
+__device__ __forceinline__ int plan_slot_span(int count, int chunk_tokens, int shift) {
+  return chunk_tokens < 128 ? ((count + chunk_tokens - 1) >> shift) * 128 : (count + 127) & ~127;
+}
+__device__ __forceinline__ int plan_slot_of_position(int pos, int chunk_tokens, int shift) {
+  return chunk_tokens < 128 ? (pos >> shift) * 128 + (pos & (chunk_tokens - 1)) : pos;
+}
+
+constexpr int kPlanKeep = 4;   // routes a thread keeps in registers between the counting and the placing pass
+
 __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads) {
   __shared__ int cnt[kMaxLocalExperts];
   __shared__ int base[kMaxLocalExperts];
   __shared__ int s_error;
   __shared__ int s_total_chunks;
   const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
+  const int shift = 31 - __clz(a.chunk_tokens);
   for (int i = threadIdx.x; i < local_experts; i += nthreads) cnt[i] = 0;
   if (threadIdx.x == 0) s_error = 0;
   __syncthreads();
   const int n = a.rows * a.top_k;
-  for (int r = threadIdx.x; r < n; r += nthreads) {
-    const uint32_t e = a.topk_indices[r];
-    int pos = -1;
-    if (e == kNoRoute) {
-      // nothing to do for this entry
-    } else if (e >= static_cast<uint32_t>(a.experts)) {
-      atomicOr(&s_error, static_cast<int>(kErrBadExpert));
-    } else if (static_cast<int>(e % a.ep_world) == a.ep_rank) {
-      pos = atomicAdd(&cnt[e / a.ep_world], 1);
+  // Up to kPlanKeep * nthreads routes (64 rows of top-8 on 128 threads) stay in registers from the
+  // counting pass to the placing pass: their expert ids are loaded once, all loads of a thread in
+  // flight together, and route_slot is written once.
+  const bool keep = n <= kPlanKeep * nthreads;
+  int kept_le[kPlanKeep], kept_pos[kPlanKeep];
+  for (int r0 = 0; r0 < n; r0 += kPlanKeep * nthreads) {
+    uint32_t e[kPlanKeep];
+#pragma unroll
+    for (int j = 0; j < kPlanKeep; ++j) {
+      const int r = r0 + j * nthreads + threadIdx.x;
+      e[j] = r < n ? a.topk_indices[r] : kNoRoute;
     }
-    a.route_slot[r] = pos;
+#pragma unroll
+    for (int j = 0; j < kPlanKeep; ++j) {
+      const int r = r0 + j * nthreads + threadIdx.x;
+      int pos = -1, le = 0;
+      if (e[j] == kNoRoute) {
+        // nothing to do for this entry
+      } else if (e[j] >= static_cast<uint32_t>(a.experts)) {
+        atomicOr(&s_error, static_cast<int>(kErrBadExpert));
+      } else if (a.ep_world == 1) {
+        le = static_cast<int>(e[j]);
+        pos = atomicAdd(&cnt[le], 1);
+      } else if (static_cast<int>(e[j] % a.ep_world) == a.ep_rank) {
+        le = static_cast<int>(e[j] / a.ep_world);
+        pos = atomicAdd(&cnt[le], 1);
+      }
+      kept_le[j] = le;
+      kept_pos[j] = pos;
+      if (!keep && r < n) a.route_slot[r] = pos;
+    }
   }
   __syncthreads();
+  GLMRT_CHAIN_MARK(3);
   if (threadIdx.x < 32) {
     // warp 0: each lane owns a contiguous run of experts; exclusive scan of slots and chunks
     const int lane = threadIdx.x;
@@ -44,8 +77,8 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
     int slots = 0, chunks = 0, distinct = 0, routes = 0;
     for (int le = le0; le < le1; ++le) {
       const int c = cnt[le];
-      slots += expert_slot_span(c, a.chunk_tokens);
-      chunks += (c + a.chunk_tokens - 1) / a.chunk_tokens;
+      slots += plan_slot_span(c, a.chunk_tokens, shift);
+      chunks += (c + a.chunk_tokens - 1) >> shift;
       distinct += c != 0;
       routes += c;
     }
@@ -76,13 +109,13 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
         for (int off = 0; off < c; off += a.chunk_tokens) {
           Chunk ch;
           ch.expert = le;
-          ch.slot_base = slot_off + slot_of_position(off, a.chunk_tokens);
+          ch.slot_base = slot_off + plan_slot_of_position(off, a.chunk_tokens, shift);
           ch.tokens = min(a.chunk_tokens, c - off);
           ch.reserved = 0;
           a.chunks[chunk_off++] = ch;
         }
       }
-      slot_off += expert_slot_span(c, a.chunk_tokens);
+      slot_off += plan_slot_span(c, a.chunk_tokens, shift);
     }
     if (lane == 0) {
       s_total_chunks = err != 0 ? 0 : total_chunks;
@@ -96,16 +129,33 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
     }
   }
   __syncthreads();
+  GLMRT_CHAIN_MARK(4);
   if (a.fc_sync != nullptr) {
     // the decode GEMMs' hand-over words: FC2's tile counter and one "rows stored" count per work item
     for (int i = threadIdx.x; i < kFcSyncHeader + s_total_chunks; i += nthreads) a.fc_sync[i] = 0u;
   }
   const bool bad = s_error != 0;
+  GLMRT_CHAIN_MARK(5);
+  if (keep) {
+#pragma unroll
+    for (int j = 0; j < kPlanKeep; ++j) {
+      const int r = j * nthreads + threadIdx.x;
+      if (r >= n) continue;
+      int slot = -1;
+      if (kept_pos[j] >= 0 && !bad) {
+        slot = base[kept_le[j]] + plan_slot_of_position(kept_pos[j], a.chunk_tokens, shift);
+        if (slot >= a.max_slots) slot = -1;
+      }
+      a.route_slot[r] = slot;
+      if (slot >= 0) a.slot_route[slot] = r;
+    }
+    return;
+  }
   for (int r = threadIdx.x; r < n; r += nthreads) {
     const int pos = a.route_slot[r];
     if (pos < 0) continue;
     const uint32_t e = a.topk_indices[r];
-    const int slot = base[e / a.ep_world] + slot_of_position(pos, a.chunk_tokens);
+    const int slot = base[e / a.ep_world] + plan_slot_of_position(pos, a.chunk_tokens, shift);
     if (bad || slot >= a.max_slots) {
       a.route_slot[r] = -1;
     } else {

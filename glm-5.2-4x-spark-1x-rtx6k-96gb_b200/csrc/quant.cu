@@ -14,6 +14,8 @@
 #include "internal.h"
 #include "quant_block.cuh"
 
+GLMRT_CHAIN_TRACE_TU(quant)
+
 namespace glmrt {
 namespace {
 
@@ -203,41 +205,52 @@ unsigned grid_for(size_t n) { return static_cast<unsigned>((n + kThreads - 1) / 
 // vectors, scales as 4-byte words of the tiled layout.  Replaces a launch and the re-read of the
 // payload by one warp per route.
 constexpr int kFusedThreads = 256;   // measured faster than one thread per 16-element block (384 for hidden 6144)
+template <bool kLatency>
 __global__ void __launch_bounds__(kFusedThreads)
 quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
+  GLMRT_CHAIN_SCOPE(kChainQuantDispatch);
   pdl_launch_dependents();
   pdl_wait();
+  GLMRT_CHAIN_READY();
+  if (static_cast<int>(blockIdx.x) >= a.rows) {
+    // an extra CTA: asks the L2 for the gate and up weights of one (work item, 128-row tile) pair of
+    // FC1's tile order, while the other CTAs quantise and dispatch the rows
+    const WeightPrefetch& w = a.prefetch;
+    const int t = static_cast<int>(blockIdx.x) - a.rows;
+    const int feat_tiles = w.rows_per_expert / 128;
+    if (__ldcg(a.counters + kCntError) != 0u || t >= static_cast<int>(__ldcg(a.counters + kCntChunks)) * feat_tiles) return;
+    const int expert = __ldcg(&a.chunks[t / feat_tiles].expert);
+    const size_t first_row = static_cast<size_t>(expert) * w.rows_per_expert + static_cast<size_t>(t % feat_tiles) * 128;
+    l2_prefetch_weight_tile(w.w0, w.sf0, first_row, w.row_bytes, kFusedThreads);
+    l2_prefetch_weight_tile(w.w1, w.sf1, first_row, w.row_bytes, kFusedThreads);
+    return;
+  }
   extern __shared__ uint4 row_img[];
   uint8_t* img = reinterpret_cast<uint8_t*>(row_img);
   const int row = blockIdx.x;
   const int code_bytes = a.hidden / 2;
   const int kblocks = a.hidden / 16;
   const uint16_t* src_row = in + static_cast<size_t>(row) * a.hidden;
-  for (int blk = threadIdx.x; blk < kblocks; blk += kFusedThreads) {
-    const uint4 x0 = reinterpret_cast<const uint4*>(src_row + blk * 16)[0];
-    const uint4 x1 = reinterpret_cast<const uint4*>(src_row + blk * 16)[1];
-    const uint32_t w[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    float v[16];
+  // decode-sized batches: the slots of the row's first eight routes are asked for now and used
+  // after the quantisation
+  int slots[8];
+  if (kLatency) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-    uint32_t lo, hi, sbyte;
-    quantize_block16<true>(v, lo, hi, sbyte);
-    reinterpret_cast<uint2*>(img)[blk] = make_uint2(lo, hi);
-    img[code_bytes + blk] = static_cast<uint8_t>(sbyte);
+    for (int j = 0; j < 8; ++j) slots[j] = j < a.top_k ? a.route_slot[row * a.top_k + j] : -1;
   }
+  quantize_row_to_image<kLatency>(src_row, img, a.hidden, kFusedThreads);
   __syncthreads();
+  GLMRT_CHAIN_MARK(0);
   const int row_vecs = (code_bytes + kblocks) / 16;
   uint4* prow = reinterpret_cast<uint4*>(a.payload_out + static_cast<size_t>(row) * (code_bytes + kblocks));
   for (int i = threadIdx.x; i < row_vecs; i += kFusedThreads) prow[i] = row_img[i];
   const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(img + code_bytes);
   // the slots of up to eight routes are fetched together: one load latency instead of one per route
   for (int k0 = 0; k0 < a.top_k; k0 += 8) {
-    int slots[8];
+    if (k0 != 0 || !kLatency) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) slots[j] = k0 + j < a.top_k ? a.route_slot[row * a.top_k + k0 + j] : -1;
+      for (int j = 0; j < 8; ++j) slots[j] = k0 + j < a.top_k ? a.route_slot[row * a.top_k + k0 + j] : -1;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int slot = slots[j];
@@ -258,6 +271,7 @@ quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
       }
     }
   }
+  GLMRT_CHAIN_MARK(1);
 }
 
 }  // namespace
@@ -269,7 +283,11 @@ bool quantize_dispatch_supported(const uint16_t* in, const DispatchArgs& a) {
 
 glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& a, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(a.hidden) / 2 + a.hidden / 16;
-  launch_pdl(quantize_dispatch_kernel, dim3(a.rows), dim3(kFusedThreads), smem, stream, in, a);
+  if (a.rows <= 512)   // a few CTAs per SM at most: the time is the latency of one row
+    launch_pdl(quantize_dispatch_kernel<true>, dim3(a.rows + (a.prefetch.w0 != nullptr ? a.prefetch.tiles : 0)),
+               dim3(kFusedThreads), smem, stream, in, a);
+  else
+    launch_pdl(quantize_dispatch_kernel<false>, dim3(a.rows), dim3(kFusedThreads), smem, stream, in, a);
   GLMRT_LAUNCH_CHECK("quantize_dispatch_kernel");
   return GLMRT_STATUS_OK;
 }

@@ -14,6 +14,8 @@
 #include "internal.h"
 #include "plan_body.cuh"
 
+GLMRT_CHAIN_TRACE_TU(router)
+
 namespace glmrt {
 namespace {
 
@@ -105,8 +107,10 @@ template <typename WT>
 __global__ void __launch_bounds__(kSmallThreads)
 router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict__ w, float* __restrict__ logits,
                            int rows, int hidden, int experts, int chunk_rows) {
+  GLMRT_CHAIN_SCOPE(kChainLogits);
   pdl_launch_dependents();
   pdl_wait();
+  GLMRT_CHAIN_READY();
   __shared__ float partial[kSmallWarps][kSmallChunkRows][kSmallExperts];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int e0 = blockIdx.x * kSmallExperts;
@@ -125,6 +129,7 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
       wr[e][s] = j < steps ? load_w4<WT>(we + j * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
+  GLMRT_CHAIN_MARK(0);
   // CTAs walk the row groups in rotated order: all of them reading the same activation lines at the
   // same moment would queue on a few L2 slices (a row's result does not depend on the order)
   const int groups = (nrows + kSmallRows - 1) / kSmallRows;
@@ -174,6 +179,7 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
     }
   }
   __syncthreads();
+  GLMRT_CHAIN_MARK(1);
   for (int t = threadIdx.x; t < nrows * kSmallExperts; t += kSmallThreads) {
     const int r = t / kSmallExperts, e = t % kSmallExperts;
     float sum = 0.0f;
@@ -183,13 +189,17 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
   }
 }
 
-// One warp per row.  Shared memory: per warp `experts` selection scores.
+// One warp per row.  Shared memory: per warp 2 * `experts` floats (used above 256 experts; up to
+// 256 a lane keeps its eight experts in registers).
+constexpr int kSelectPerLane = 8;
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
                                      float* __restrict__ topk_weights, int rows, int experts, int top_k,
                                      float scaling, int splits, RouterCountTail tail) {
+  GLMRT_CHAIN_SCOPE(kChainSelect);
   pdl_launch_dependents();
   pdl_wait();
+  GLMRT_CHAIN_READY();
   extern __shared__ float smem[];
   const int warps = blockDim.x / 32;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -197,52 +207,102 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   if (row < rows) {
   float* sel = smem + static_cast<size_t>(warp) * 2 * experts;
   float* raw = sel + experts;
-  for (int e = lane; e < experts; e += 32) {
-    // a logit may arrive as `splits` partial sums (tensor-core router below one wave of tiles): added in order
-    const float* part = logits + static_cast<size_t>(row) * experts + e;
-    float logit = part[0];
-    if (splits > 1) {
-      const size_t stride = static_cast<size_t>(rows) * experts;
-      float v[7];
+  const bool in_regs = experts <= 32 * kSelectPerLane;   // GLM-5.2's 256 experts: eight per lane
+  float vsel[kSelectPerLane], vraw[kSelectPerLane];      // lane's experts j * 32 + lane (register path)
+  for (int base = 0; base < experts; base += 32 * kSelectPerLane) {
+    // All loads of a pass are issued before any is used: one memory round trip per 256 experts
+    // instead of one per expert.  A logit may arrive as `splits` partial sums (tensor-core router
+    // below one wave of tiles): added in order.
+    float lg[kSelectPerLane], bs[kSelectPerLane];
 #pragma unroll
-      for (int j = 0; j < 7; ++j) v[j] = j + 1 < splits ? part[(j + 1) * stride] : 0.0f;
-#pragma unroll
-      for (int j = 0; j < 7; ++j)
-        if (j + 1 < splits) logit = __fadd_rn(logit, v[j]);
+    for (int j = 0; j < kSelectPerLane; ++j) {
+      const int e = base + j * 32 + lane;
+      lg[j] = e < experts ? logits[static_cast<size_t>(row) * experts + e] : 0.0f;
+      bs[j] = e < experts ? bias[e] : 0.0f;
     }
-    const float s = sigmoid_f32(logit);
-    const bool fin = isfinite(s);
-    const float score = fin ? s : 0.0f;
-    const float corrected = score + bias[e];
-    raw[e] = score;
-    sel[e] = (fin && isfinite(corrected)) ? corrected : -CUDART_INF_F;
+    const size_t stride = static_cast<size_t>(rows) * experts;
+    for (int sp = 1; sp < splits; ++sp) {
+      float v[kSelectPerLane];
+#pragma unroll
+      for (int j = 0; j < kSelectPerLane; ++j) {
+        const int e = base + j * 32 + lane;
+        v[j] = e < experts ? logits[sp * stride + static_cast<size_t>(row) * experts + e] : 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < kSelectPerLane; ++j) lg[j] = __fadd_rn(lg[j], v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kSelectPerLane; ++j) {
+      const int e = base + j * 32 + lane;
+      const float sg = sigmoid_f32(lg[j]);
+      const bool fin = isfinite(sg);
+      const float score = fin ? sg : 0.0f;
+      const float corrected = score + bs[j];
+      const float pick = (fin && isfinite(corrected) && e < experts) ? corrected : -CUDART_INF_F;
+      if (in_regs) {
+        vraw[j] = score;
+        vsel[j] = pick;
+      } else if (e < experts) {
+        raw[e] = score;
+        sel[e] = pick;
+      }
+    }
   }
   __syncwarp();
+  GLMRT_CHAIN_MARK(0);
   float sum = 0.0f;
   float my_score = 0.0f;   // lane j keeps the score of rank j (top_k <= 64: two per lane)
   float my_score2 = 0.0f;
   uint32_t my_idx = 0, my_idx2 = 0;
   for (int rank = 0; rank < top_k; ++rank) {
-    float best = -CUDART_INF_F;
-    int best_e = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
-      const float v = sel[e];
-      if (v > best) { best = v; best_e = e; }   // ascending e: first maximum wins inside a lane
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
     float score = 0.0f;
     uint32_t idx = 0;
-    if (best_e != 0x7fffffff) {  // a finite candidate exists
-      score = raw[best_e];
-      idx = static_cast<uint32_t>(best_e);
-      if (lane == 0) sel[best_e] = -CUDART_INF_F;  // -inf entries are never picked (best starts at -inf)
+    if (in_regs) {
+      // the lane's best (first maximum in ascending expert order), then two warp reductions: the
+      // largest value, and the lowest expert among the lanes that hold it
+      float best = -CUDART_INF_F;
+      int best_j = 0;
+#pragma unroll
+      for (int j = 0; j < kSelectPerLane; ++j)
+        if (vsel[j] > best) { best = vsel[j]; best_j = j; }
+      const uint32_t bits = __float_as_uint(best + 0.0f);    // -0 becomes +0: equal as floats, equal as keys
+      const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);   // order-preserving
+      const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+      const uint32_t cand = (key == top && best > -CUDART_INF_F) ? static_cast<uint32_t>(best_j * 32 + lane) : 0x7fffffffu;
+      const uint32_t win = __reduce_min_sync(0xffffffffu, cand);
+      if (win != 0x7fffffffu) {   // a finite candidate exists
+        float r = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kSelectPerLane; ++j)
+          if (j == static_cast<int>(win >> 5)) r = vraw[j];
+        score = __shfl_sync(0xffffffffu, r, static_cast<int>(win & 31u));
+        idx = win;
+        if (lane == static_cast<int>(win & 31u)) {
+#pragma unroll
+          for (int j = 0; j < kSelectPerLane; ++j)
+            if (j == static_cast<int>(win >> 5)) vsel[j] = -CUDART_INF_F;   // never picked again
+        }
+      }
+    } else {
+      float best = -CUDART_INF_F;
+      int best_e = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = sel[e];
+        if (v > best) { best = v; best_e = e; }   // ascending e: first maximum wins inside a lane
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      if (best_e != 0x7fffffff) {  // a finite candidate exists
+        score = raw[best_e];
+        idx = static_cast<uint32_t>(best_e);
+        if (lane == 0) sel[best_e] = -CUDART_INF_F;  // -inf entries are never picked (best starts at -inf)
+      }
+      __syncwarp();
     }
-    __syncwarp();
     sum += score;  // sequential float32 sum in rank order (router.cu:52-56)
     if (rank == lane) { my_score = score; my_idx = idx; }
     if (rank == lane + 32) { my_score2 = score; my_idx2 = idx; }
@@ -260,17 +320,23 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     topk_weights[out + lane + 32] = my_score2 / sum * scaling;
   }
   }  // row < rows
+  GLMRT_CHAIN_MARK(1);
   if (tail.ticket == nullptr) return;
   // The last CTA to finish does what would otherwise be a launch of its own: on the
   // expert-parallel path it counts this rank's routes per expert and publishes the histogram to
   // every rank (the first step of the exchange); on one GPU it builds the route plan.
-  __shared__ int s_is_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_is_last = atomicAdd(tail.ticket, 1) == static_cast<int>(gridDim.x) - 1;
-  __syncthreads();
-  if (!s_is_last) return;
-  __threadfence();
+  if (gridDim.x > 1) {
+    __shared__ int s_is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_is_last = atomicAdd(tail.ticket, 1) == static_cast<int>(gridDim.x) - 1;
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+  } else {
+    __syncthreads();   // a grid of one CTA: its own rows are all there are
+  }
+  GLMRT_CHAIN_MARK(2);
   if (tail.do_plan) {
     if (threadIdx.x == 0) *tail.ticket = 0;
     route_plan_body(tail.plan, blockDim.x);
@@ -295,8 +361,7 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     *tail.error_word = 0u;   // a new step begins: clear the layer's error word
     *tail.ticket = 0;
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();   // the release below is cumulative over what the barrier ordered before it
   if (threadIdx.x < static_cast<unsigned>(tail.world)) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tail.peer_flags[threadIdx.x]), "r"(tail.epoch) : "memory");
   }

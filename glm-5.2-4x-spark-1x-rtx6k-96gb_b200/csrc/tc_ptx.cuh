@@ -108,6 +108,10 @@ __device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.
 // every group of this thread is complete (its global writes performed)
 __device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // makes generic-proxy shared-memory writes visible to the asynchronous proxy (TMA)
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first copy.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
