@@ -252,12 +252,15 @@ __device__ __forceinline__ void l2_prefetch_lines(const uint8_t* p, size_t bytes
   for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < bytes; off += static_cast<size_t>(threads) * 128)
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off) : "memory");
 }
-__device__ __forceinline__ void l2_prefetch_weight_tile(const uint8_t* codes, const uint8_t* sf, size_t first_row,
-                                                        int row_bytes, int threads) {
-  l2_prefetch_lines(codes + first_row * static_cast<size_t>(row_bytes), 128 * static_cast<size_t>(row_bytes), threads);
+// Quarter `part` (0..3) of a 128-row weight tile: 32 rows of codes and a quarter of its scale tiles.
+constexpr int kPrefetchParts = 4;
+__device__ __forceinline__ void l2_prefetch_weight_tile_part(const uint8_t* codes, const uint8_t* sf, size_t first_row,
+                                                             int row_bytes, int part, int threads) {
+  l2_prefetch_lines(codes + (first_row + 32 * static_cast<size_t>(part)) * row_bytes, 32 * static_cast<size_t>(row_bytes),
+                    threads);
   // scale tiles: 512 bytes per (128 rows, 64 elements of K)
-  l2_prefetch_lines(sf + (first_row / 128) * static_cast<size_t>(row_bytes / 32) * 512,
-                    static_cast<size_t>(row_bytes / 32) * 512, threads);
+  const size_t sf_bytes = static_cast<size_t>(row_bytes / 32) * 512;
+  l2_prefetch_lines(sf + (first_row / 128) * sf_bytes + part * (sf_bytes / kPrefetchParts), sf_bytes / kPrefetchParts, threads);
 }
 
 // Byte offset of the scale of (row r, 16-element block j) in the tiled scale layout the

@@ -50,7 +50,6 @@ __global__ void __launch_bounds__(kEpThreads) ep_count_kernel(EpArgs a, const ui
   for (int e = threadIdx.x; e < a.experts; e += kEpThreads) {
     const int c = hist[e];
     for (int p = 0; p < a.world; ++p) a.peer_ctrl[p]->counts_all[a.rank * kEpMaxExperts + e] = c;
-    a.ctrl->cursor[e] = 0;
   }
   if (threadIdx.x == 0) a.counters[kCntError] = static_cast<uint32_t>(s_err);  // also clears the word
   __syncthreads();   // the release below is cumulative over what the barrier ordered before it
@@ -81,7 +80,7 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   pdl_launch_dependents();
   if (threadIdx.x == 0) s_err = 0;
   __syncthreads();
-  pdl_wait();   // the routes (and the cleared cursors) come from the router's kernels
+  pdl_wait();   // the routes and their positions come from the router's kernels
   GLMRT_CHAIN_READY();
   if (threadIdx.x < a.world && !wait_flag(&a.ctrl->flag_counts[threadIdx.x], a.epoch))
     atomicOr(&s_err, static_cast<int>(kErrWaitTimeout));
@@ -189,19 +188,23 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   }
   __syncthreads();
   const bool plan_ok = s_err == 0;
-  if (!plan_ok && threadIdx.x == 0) {
+  const int push_ctas = static_cast<int>(gridDim.x) - p.prefetch.tiles * kPrefetchParts;
+  if (!plan_ok && threadIdx.x == 0 && static_cast<int>(blockIdx.x) < push_ctas) {
     atomicOr(&p.counters[kCntError], static_cast<uint32_t>(s_err));
     atomicOr(&a.ctrl->plan_failed, 1);   // read by the last CTA: one failing CTA poisons the whole push
   }
 
-  const int push_ctas = static_cast<int>(gridDim.x) - p.prefetch.tiles;
-  if (static_cast<int>(blockIdx.x) >= push_ctas && plan_ok) {
-    // an extra CTA: asks the L2 for the gate and up weights of one (work item, 128-row tile) pair of
-    // this rank's FC1, in FC1's tile order, while the rows travel
+  if (static_cast<int>(blockIdx.x) >= push_ctas) {
+    // an extra CTA: asks the L2 for a quarter of the gate and up weights of one (work item, 128-row
+    // tile) pair of this rank's FC1, in FC1's tile order, while the rows travel.  It takes no part in
+    // the hand-over to the owners below.
+    if (!plan_ok) return;
     __shared__ int s_pf_expert;
+    const int id = static_cast<int>(blockIdx.x) - push_ctas;
+    const int t = id / kPrefetchParts, part = id % kPrefetchParts;
+    const int feat_tiles = p.prefetch.rows_per_expert / 128;
     if (threadIdx.x == 0) {
-      const int feat_tiles = p.prefetch.rows_per_expert / 128;
-      const int want = (static_cast<int>(blockIdx.x) - push_ctas) / feat_tiles;   // work item number
+      const int want = t / feat_tiles;   // work item number
       const int n_local = (a.experts - a.rank + a.world - 1) / a.world;
       int seen = 0, found = -1;
       for (int i = 0; i < n_local && found < 0; ++i) {
@@ -213,24 +216,25 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
     }
     __syncthreads();
     if (s_pf_expert >= 0) {
-      const int feat_tiles = p.prefetch.rows_per_expert / 128;
       const size_t first_row = static_cast<size_t>(s_pf_expert) * p.prefetch.rows_per_expert +
-                               static_cast<size_t>((static_cast<int>(blockIdx.x) - push_ctas) % feat_tiles) * 128;
-      l2_prefetch_weight_tile(p.prefetch.w0, p.prefetch.sf0, first_row, p.prefetch.row_bytes, kPushThreads);
-      l2_prefetch_weight_tile(p.prefetch.w1, p.prefetch.sf1, first_row, p.prefetch.row_bytes, kPushThreads);
+                               static_cast<size_t>(t % feat_tiles) * 128;
+      l2_prefetch_weight_tile_part(p.prefetch.w0, p.prefetch.sf0, first_row, p.prefetch.row_bytes, part, kPushThreads);
+      l2_prefetch_weight_tile_part(p.prefetch.w1, p.prefetch.sf1, first_row, p.prefetch.row_bytes, part, kPushThreads);
     }
+    return;
   }
-  for (int row = blockIdx.x; row < rows && static_cast<int>(blockIdx.x) < push_ctas; row += push_ctas) {
+  for (int row = blockIdx.x; row < rows; row += push_ctas) {
     const int code_bytes = hidden_dim / 2, kblocks = hidden_dim / 16;
     __syncthreads();   // the previous row's image and positions have been read
     const size_t row_bytes = static_cast<size_t>(code_bytes + kblocks);
     if (plan_ok) {
       // positions of the row's routes among this rank's routes of each expert: asked for first, the
-      // round trips of the id load and of the counter run under the quantisation of the row
+      // round trip of the loads runs under the quantisation of the row
       if (threadIdx.x < top_k) {
         const uint32_t e = p.topk_indices[row * top_k + threadIdx.x];
         s_expert[threadIdx.x] = static_cast<int>(e);
-        s_pos[threadIdx.x] = e < static_cast<uint32_t>(a.experts) ? atomicAdd(&a.ctrl->cursor[e], 1) : -1;
+        // its position among this rank's routes of that expert was counted by the router's tail
+        s_pos[threadIdx.x] = e < static_cast<uint32_t>(a.experts) ? p.route_slot[row * top_k + threadIdx.x] : -1;
       }
       if (hidden != nullptr) {
         if (a.chunk_tokens < 128)   // decode-sized step
@@ -243,12 +247,14 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
           reinterpret_cast<uint4*>(img)[i] = src[i];
       }
       __syncthreads();
+      GLMRT_CHAIN_MARK(3);
       if (hidden != nullptr) {
         uint4* prow = reinterpret_cast<uint4*>(payload + row * row_bytes);
         for (int i = threadIdx.x; i < static_cast<int>(row_bytes / 16); i += kPushThreads)
           prow[i] = reinterpret_cast<const uint4*>(img)[i];
       }
       const uint32_t* sf_words = reinterpret_cast<const uint32_t*>(img + code_bytes);
+      GLMRT_CHAIN_MARK(4);
       for (int k = 0; k < top_k; ++k) {
         const int route = row * top_k + k;
         const int pos = s_pos[k];
@@ -290,7 +296,7 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     __threadfence_system();
-    s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == static_cast<int>(gridDim.x) - 1;
+    s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == push_ctas - 1;
     if (s_last) __threadfence_system();
   }
   __syncthreads();
@@ -391,7 +397,6 @@ RouterCountTail ep_count_tail(const EpArgs& a) {
     t.peer_counts[p] = a.peer_ctrl[p]->counts_all + a.rank * kEpMaxExperts;   // address arithmetic only
     t.peer_flags[p] = a.peer_ctrl[p]->flag_counts + a.rank;
   }
-  t.cursor = a.ctrl->cursor;
   t.error_word = a.counters + kCntError;
   t.ticket = &a.ctrl->ticket_select;
   return t;
@@ -404,7 +409,7 @@ glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const
   const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
   if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
   // every CTA derives the layout once, so large batches walk their rows with a bounded grid
-  const int grid = (rows > 0 ? (rows < 1184 ? rows : 1184) : 1) + (p.prefetch.w0 != nullptr ? p.prefetch.tiles : 0);
+  const int grid = (rows > 0 ? (rows < 1184 ? rows : 1184) : 1) + (p.prefetch.w0 != nullptr ? p.prefetch.tiles * kPrefetchParts : 0);
   launch_pdl(ep_plan_dispatch_kernel, dim3(grid), dim3(kPushThreads), smem, stream, a, p, hidden, payload,
              rows, top_k, hidden_dim);
   GLMRT_LAUNCH_CHECK("ep_plan_dispatch_kernel");

@@ -93,15 +93,16 @@ constexpr uint32_t kNoRoute = 0xffffffffu;
 // Weights of the first FC1 work of a decode step, asked into the L2 while the rows are quantised and
 // dispatched: between the route plan and the first weight byte FC1 itself asks for, the memory
 // system is otherwise idle for several microseconds.  One SM turns out about one 128-byte request
-// per clock (256 GB/s), so the requests are spread over extra CTAs of the dispatch kernel, one
-// (work item, 128-row tile) pair of FC1's tile order each.
+// per clock (256 GB/s), so the requests are spread over extra CTAs of the dispatch kernel: four per
+// (work item, 128-row tile) pair of FC1's tile order, about a microsecond of requests each, so that
+// they are done well before the CTAs that quantise rows.
 struct WeightPrefetch {
   const uint8_t* w0 = nullptr;    // gate codes [local experts * rows_per_expert, row_bytes]; nullptr: no prefetch
   const uint8_t* w1 = nullptr;    // up codes, same shape
   const uint8_t* sf0 = nullptr;   // their tiled scales
   const uint8_t* sf1 = nullptr;
   int rows_per_expert = 0, row_bytes = 0;
-  int tiles = 0;                  // extra CTAs = pairs asked for
+  int tiles = 0;                  // pairs asked for (kPrefetchParts extra CTAs each)
 };
 struct PlanArgs {
   const uint32_t* topk_indices;  // [rows * top_k] global expert ids
@@ -121,7 +122,7 @@ struct PlanArgs {
 };
 // Optional tails of the router's selection kernel, run by the last CTA of its grid to finish.
 //   expert-parallel path (world > 0): count this rank's routes per expert, store the histogram into
-//     every rank's count table, clear this rank's per-expert cursors and the layer's error word, and
+//     every rank's count table, number each route among this rank's routes of its expert, clear the layer's error word, and
 //     raise the per-peer "counts" epoch flag;
 //   one GPU, decode-sized batches (do_plan): build the route plan right there (one launch less).
 struct RouterCountTail {
@@ -129,7 +130,7 @@ struct RouterCountTail {
   uint32_t epoch = 0;
   int32_t* peer_counts[kEpMaxWorld];     // this rank's row of each rank's count table
   uint32_t* peer_flags[kEpMaxWorld];     // this rank's "counts" flag at each rank
-  int32_t* cursor;                       // [experts], local
+  int32_t* route_pos = nullptr;          // [routes], local: a route's number among this rank's routes of its expert (-1: no valid expert)
   uint32_t* error_word;                  // local
   int32_t* ticket = nullptr;             // local, zero between launches
   int do_plan = 0;
@@ -172,7 +173,6 @@ struct EpControl {
   uint32_t poison_dispatch[kEpMaxWorld];             // epoch in which that rank had no valid plan and pushed nothing
   uint32_t flag_combine[kEpMaxWorld];                // epoch of the last completed result push from each owner
   // local only
-  int32_t cursor[kEpMaxExperts];      // next free position among this rank's routes
   int32_t ticket_select;              // last-CTA tickets of the kernels that end with a publish step
   int32_t ticket_dispatch;
   int32_t ticket_fc2;

@@ -949,7 +949,8 @@ glmrt_status_t ep_phase(Layer* l, uint32_t phase, const uint16_t* hidden, size_t
       // router; the tail of its selection kernel publishes this rank's routes-per-expert histogram
       mark(l, GLMRT_B200_STAGE_ROUTER, s);
       if (rows > 0) {
-        const RouterCountTail tail = ep_count_tail(a);
+        RouterCountTail tail = ep_count_tail(a);
+        tail.route_pos = l->route_slot;   // positions now, slots once the push kernel has placed the routes
         GLMRT_RETURN_IF_ERROR(run_router(l, hidden, rows, s, &tail));
       } else {
         GLMRT_RETURN_IF_ERROR(launch_ep_count(a, l->topk_idx, 0, s));

@@ -213,16 +213,17 @@ quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
   pdl_wait();
   GLMRT_CHAIN_READY();
   if (static_cast<int>(blockIdx.x) >= a.rows) {
-    // an extra CTA: asks the L2 for the gate and up weights of one (work item, 128-row tile) pair of
-    // FC1's tile order, while the other CTAs quantise and dispatch the rows
+    // an extra CTA: asks the L2 for a quarter of the gate and up weights of one (work item, 128-row
+    // tile) pair of FC1's tile order, while the other CTAs quantise and dispatch the rows
     const WeightPrefetch& w = a.prefetch;
-    const int t = static_cast<int>(blockIdx.x) - a.rows;
+    const int id = static_cast<int>(blockIdx.x) - a.rows;
+    const int t = id / kPrefetchParts, part = id % kPrefetchParts;
     const int feat_tiles = w.rows_per_expert / 128;
     if (__ldcg(a.counters + kCntError) != 0u || t >= static_cast<int>(__ldcg(a.counters + kCntChunks)) * feat_tiles) return;
     const int expert = __ldcg(&a.chunks[t / feat_tiles].expert);
     const size_t first_row = static_cast<size_t>(expert) * w.rows_per_expert + static_cast<size_t>(t % feat_tiles) * 128;
-    l2_prefetch_weight_tile(w.w0, w.sf0, first_row, w.row_bytes, kFusedThreads);
-    l2_prefetch_weight_tile(w.w1, w.sf1, first_row, w.row_bytes, kFusedThreads);
+    l2_prefetch_weight_tile_part(w.w0, w.sf0, first_row, w.row_bytes, part, kFusedThreads);
+    l2_prefetch_weight_tile_part(w.w1, w.sf1, first_row, w.row_bytes, part, kFusedThreads);
     return;
   }
   extern __shared__ uint4 row_img[];
@@ -284,7 +285,7 @@ bool quantize_dispatch_supported(const uint16_t* in, const DispatchArgs& a) {
 glmrt_status_t launch_quantize_dispatch(const uint16_t* in, const DispatchArgs& a, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(a.hidden) / 2 + a.hidden / 16;
   if (a.rows <= 512)   // a few CTAs per SM at most: the time is the latency of one row
-    launch_pdl(quantize_dispatch_kernel<true>, dim3(a.rows + (a.prefetch.w0 != nullptr ? a.prefetch.tiles : 0)),
+    launch_pdl(quantize_dispatch_kernel<true>, dim3(a.rows + (a.prefetch.w0 != nullptr ? a.prefetch.tiles * kPrefetchParts : 0)),
                dim3(kFusedThreads), smem, stream, in, a);
   else
     launch_pdl(quantize_dispatch_kernel<false>, dim3(a.rows), dim3(kFusedThreads), smem, stream, in, a);

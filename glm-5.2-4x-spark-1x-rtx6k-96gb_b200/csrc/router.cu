@@ -349,13 +349,15 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   const volatile uint32_t* all_idx = topk_indices;   // written by other CTAs of this grid
   for (int r = threadIdx.x; r < routes; r += blockDim.x) {
     const uint32_t e = all_idx[r];
-    if (e < static_cast<uint32_t>(experts)) atomicAdd(&hist[e], 1);
+    // the count so far is the route's position among this rank's routes of that expert: the push
+    // kernel needs no counter of its own
+    const int pos = e < static_cast<uint32_t>(experts) ? atomicAdd(&hist[e], 1) : -1;
+    if (tail.route_pos != nullptr) tail.route_pos[r] = pos;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int c = hist[e];
     for (int p = 0; p < tail.world; ++p) tail.peer_counts[p][e] = c;
-    tail.cursor[e] = 0;
   }
   if (threadIdx.x == 0) {
     *tail.error_word = 0u;   // a new step begins: clear the layer's error word
