@@ -93,7 +93,7 @@ constexpr int kSmallRows = 4;        // rows per pass
 constexpr int kSmallMaxRows = 128;
 constexpr int kSmallMaxSteps = 4;     // 128-element steps per warp: hidden <= 8192
 constexpr int kSmallExperts = 4;      // experts per CTA
-constexpr int kSmallChunkRows = 64;   // rows per CTA (the batch is cut in two above 32 rows)
+constexpr int kSmallChunkRows = 64;   // rows per CTA (the batch is cut in two from eight rows on)
 
 // One CTA computes kSmallExperts experts for one chunk of the rows.  The 128-element steps of the
 // reduction are dealt round-robin to the 16 warps; each warp keeps its slice of the weight rows in
@@ -394,8 +394,9 @@ glmrt_status_t launch_router(const void* hidden, bool hidden_bf16, const void* w
   const bool small = hidden_bf16 && rows <= kSmallMaxRows && hidden_dim <= 128 * kSmallWarps * kSmallMaxSteps && hidden_dim % 128 == 0 &&
                      reinterpret_cast<uintptr_t>(hidden) % 8 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
   if (small) {
-    // rows are cut into two chunks above 32 rows (chunk sizes are multiples of the 4-row pass)
-    const int chunk_rows = r <= 32 ? r : std::min(kSmallChunkRows, ((r + 1) / 2 + kSmallRows - 1) / kSmallRows * kSmallRows);
+    // from eight rows on the rows are cut into two chunks (chunk sizes are multiples of the 4-row
+    // pass): 128 CTAs instead of 64, each with half the passes; a row's logits do not depend on the cut
+    const int chunk_rows = r < 8 ? r : std::min(kSmallChunkRows, ((r + 1) / 2 + kSmallRows - 1) / kSmallRows * kSmallRows);
     const dim3 ctas(static_cast<unsigned>((experts + kSmallExperts - 1) / kSmallExperts),
                     static_cast<unsigned>((r + chunk_rows - 1) / chunk_rows));
     if (weight_bf16)

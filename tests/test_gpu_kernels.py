@@ -118,6 +118,35 @@ def test_router_reference_named_entry_points_and_golden(lib, golden_dir):
                            C.c_size_t(512), C.c_size_t(32), C.c_size_t(4), stream()) == 1
 
 
+@pytest.mark.parametrize("E", [40, 256, 320])
+def test_router_negative_selection_scores_on_both_selection_paths(lib, E):
+    """Up to 256 experts the selection runs on registers with an order-preserving integer key, above
+    that on shared memory: both must rank negative selection scores (a strongly negative bias) like
+    the oracle, whose arg-max is on the corrected score while the weights come from the raw one."""
+    T, H, K = 12, 512, 8
+    rng = np.random.default_rng(E)
+    rw = (rng.standard_normal((E, H), np.float32) * np.float32(0.05)).astype(np.float32)
+    bias = (-2.0 - rng.random(E)).astype(np.float32)
+    hid = O.make_hidden(E, T, H)
+    x = bf16_tensor(hid)
+    w, b = torch.from_numpy(rw).cuda(), torch.from_numpy(bias).cuda()
+    logits = torch.empty(T * E, dtype=torch.float32, device="cuda")
+    idx = torch.empty((T, K), dtype=torch.int32, device="cuda")
+    sc = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    wt = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    lib.call("glmrt_b200_router_topk_bf16_f32w_async", ptr(x), ptr(w), ptr(b), ptr(logits), ptr(idx), ptr(sc),
+             ptr(wt), C.c_size_t(T), C.c_size_t(H), C.c_size_t(E), C.c_size_t(K), stream())
+    torch.cuda.synchronize()
+    oi, ow, _, _ = O.router_topk(O.bf16_to_f32(hid), rw, bias, K)
+    sel64 = (1.0 / (1.0 + np.exp(-(O.bf16_to_f32(hid).astype(np.float64) @ rw.astype(np.float64).T)))) + bias
+    assert (sel64 < 0).all()
+    gi = idx.cpu().numpy()
+    assert O.router_indices_equivalent(gi, oi, sel64, tol=1e-6)
+    same = np.all(gi == oi.astype(np.int32), axis=1)
+    assert same.mean() > 0.9
+    np.testing.assert_allclose(wt.cpu().numpy()[same], ow[same], atol=2e-6, rtol=1e-5)
+
+
 def test_router_ties_go_to_lower_expert_and_nonfinite_scores_are_skipped(lib):
     H, E, K = 256, 8, 3
     x = np.zeros((2, H), np.float32)
