@@ -253,7 +253,13 @@ __device__ __forceinline__ void l2_prefetch_lines(const uint8_t* p, size_t bytes
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off) : "memory");
 }
 // Quarter `part` (0..3) of a 128-row weight tile: 32 rows of codes and a quarter of its scale tiles.
+// The CTAs that only prefetch share their SMs with the CTAs that quantise rows, whose few loads
+// would queue behind the thousands of prefetch requests (measured: a row's quantisation 2.6 -> 4-6 us);
+// the prefetch CTAs therefore let the rows go first.
 constexpr int kPrefetchParts = 4;
+__device__ __forceinline__ void prefetch_cta_yield() {
+  for (int i = 0; i < 3; ++i) __nanosleep(1000);
+}
 __device__ __forceinline__ void l2_prefetch_weight_tile_part(const uint8_t* codes, const uint8_t* sf, size_t first_row,
                                                              int row_bytes, int part, int threads) {
   l2_prefetch_lines(codes + (first_row + 32 * static_cast<size_t>(part)) * row_bytes, 32 * static_cast<size_t>(row_bytes),

@@ -188,42 +188,12 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   }
   __syncthreads();
   const bool plan_ok = s_err == 0;
-  const int push_ctas = static_cast<int>(gridDim.x) - p.prefetch.tiles * kPrefetchParts;
-  if (!plan_ok && threadIdx.x == 0 && static_cast<int>(blockIdx.x) < push_ctas) {
+  if (!plan_ok && threadIdx.x == 0) {
     atomicOr(&p.counters[kCntError], static_cast<uint32_t>(s_err));
     atomicOr(&a.ctrl->plan_failed, 1);   // read by the last CTA: one failing CTA poisons the whole push
   }
 
-  if (static_cast<int>(blockIdx.x) >= push_ctas) {
-    // an extra CTA: asks the L2 for a quarter of the gate and up weights of one (work item, 128-row
-    // tile) pair of this rank's FC1, in FC1's tile order, while the rows travel.  It takes no part in
-    // the hand-over to the owners below.
-    if (!plan_ok) return;
-    __shared__ int s_pf_expert;
-    const int id = static_cast<int>(blockIdx.x) - push_ctas;
-    const int t = id / kPrefetchParts, part = id % kPrefetchParts;
-    const int feat_tiles = p.prefetch.rows_per_expert / 128;
-    if (threadIdx.x == 0) {
-      const int want = t / feat_tiles;   // work item number
-      const int n_local = (a.experts - a.rank + a.world - 1) / a.world;
-      int seen = 0, found = -1;
-      for (int i = 0; i < n_local && found < 0; ++i) {
-        const int items = (s_tot[a.rank + i * a.world] + p.chunk_tokens - 1) / p.chunk_tokens;
-        if (want < seen + items) found = i;
-        seen += items;
-      }
-      s_pf_expert = found;
-    }
-    __syncthreads();
-    if (s_pf_expert >= 0) {
-      const size_t first_row = static_cast<size_t>(s_pf_expert) * p.prefetch.rows_per_expert +
-                               static_cast<size_t>(t % feat_tiles) * 128;
-      l2_prefetch_weight_tile_part(p.prefetch.w0, p.prefetch.sf0, first_row, p.prefetch.row_bytes, part, kPushThreads);
-      l2_prefetch_weight_tile_part(p.prefetch.w1, p.prefetch.sf1, first_row, p.prefetch.row_bytes, part, kPushThreads);
-    }
-    return;
-  }
-  for (int row = blockIdx.x; row < rows; row += push_ctas) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const int code_bytes = hidden_dim / 2, kblocks = hidden_dim / 16;
     __syncthreads();   // the previous row's image and positions have been read
     const size_t row_bytes = static_cast<size_t>(code_bytes + kblocks);
@@ -296,7 +266,7 @@ ep_plan_dispatch_kernel(EpArgs a, PlanArgs p, const uint16_t* __restrict__ hidde
   __shared__ int s_last;
   if (threadIdx.x == 0) {
     __threadfence_system();
-    s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == push_ctas - 1;
+    s_last = atomicAdd(&a.ctrl->ticket_dispatch, 1) == static_cast<int>(gridDim.x) - 1;
     if (s_last) __threadfence_system();
   }
   __syncthreads();
@@ -409,7 +379,7 @@ glmrt_status_t launch_ep_plan_dispatch(const EpArgs& a, const PlanArgs& p, const
   const size_t smem = ((static_cast<size_t>(a.experts) * 12 + 15) & ~size_t(15)) + hidden_dim / 2 + hidden_dim / 16;
   if (smem > 40 * 1024) return fail(GLMRT_STATUS_INVALID_ARGUMENT, "expert-parallel dispatch: hidden too large");
   // every CTA derives the layout once, so large batches walk their rows with a bounded grid
-  const int grid = (rows > 0 ? (rows < 1184 ? rows : 1184) : 1) + (p.prefetch.w0 != nullptr ? p.prefetch.tiles * kPrefetchParts : 0);
+  const int grid = rows > 0 ? (rows < 1184 ? rows : 1184) : 1;
   launch_pdl(ep_plan_dispatch_kernel, dim3(grid), dim3(kPushThreads), smem, stream, a, p, hidden, payload,
              rows, top_k, hidden_dim);
   GLMRT_LAUNCH_CHECK("ep_plan_dispatch_kernel");

@@ -118,7 +118,6 @@ struct PlanArgs {
   Chunk* chunks;                 // [max_chunks]
   uint32_t* counters;            // [kCntWords]
   uint32_t* fc_sync = nullptr;   // [kFcSyncHeader + max_chunks] cleared by the plan: see FfnArgs::fc_sync
-  WeightPrefetch prefetch;       // decode-sized steps: FC1's first weight tiles (expert-parallel push kernel)
 };
 // Optional tails of the router's selection kernel, run by the last CTA of its grid to finish.
 //   expert-parallel path (world > 0): count this rank's routes per expert, store the histogram into

@@ -259,7 +259,6 @@ PlanArgs plan_args(const Layer* l, size_t rows, int chunk_tokens) {
   p.expert_base = l->expert_base; p.block_hist = l->block_hist;
   p.chunks = l->chunks; p.counters = l->counters;
   p.fc_sync = chunk_tokens == 32 ? l->fc_sync : nullptr;
-  if (c.ep_world > 1) p.prefetch = fc1_prefetch(l, chunk_tokens);
   return p;
 }
 

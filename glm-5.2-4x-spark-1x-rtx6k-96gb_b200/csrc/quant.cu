@@ -222,6 +222,7 @@ quantize_dispatch_kernel(const uint16_t* __restrict__ in, DispatchArgs a) {
     if (__ldcg(a.counters + kCntError) != 0u || t >= static_cast<int>(__ldcg(a.counters + kCntChunks)) * feat_tiles) return;
     const int expert = __ldcg(&a.chunks[t / feat_tiles].expert);
     const size_t first_row = static_cast<size_t>(expert) * w.rows_per_expert + static_cast<size_t>(t % feat_tiles) * 128;
+    prefetch_cta_yield();
     l2_prefetch_weight_tile_part(w.w0, w.sf0, first_row, w.row_bytes, part, kFusedThreads);
     l2_prefetch_weight_tile_part(w.w1, w.sf1, first_row, w.row_bytes, part, kFusedThreads);
     return;
