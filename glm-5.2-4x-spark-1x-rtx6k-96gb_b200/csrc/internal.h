@@ -94,8 +94,8 @@ constexpr uint32_t kNoRoute = 0xffffffffu;
 // dispatched: between the route plan and the first weight byte FC1 itself asks for, the memory
 // system is otherwise idle for several microseconds.  One SM turns out about one 128-byte request
 // per clock (256 GB/s), so the requests are spread over extra CTAs of the dispatch kernel: four per
-// (work item, 128-row tile) pair of FC1's tile order, about a microsecond of requests each, so that
-// they are done well before the CTAs that quantise rows.
+// (work item, 128-row tile) pair of FC1's tile order.  (One GPU only: on the expert-parallel push
+// kernel the same CTAs changed nothing.)
 struct WeightPrefetch {
   const uint8_t* w0 = nullptr;    // gate codes [local experts * rows_per_expert, row_bytes]; nullptr: no prefetch
   const uint8_t* w1 = nullptr;    // up codes, same shape
