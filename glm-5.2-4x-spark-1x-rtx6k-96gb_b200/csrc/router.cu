@@ -109,8 +109,6 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
                            int rows, int hidden, int experts, int chunk_rows) {
   GLMRT_CHAIN_SCOPE(kChainLogits);
   pdl_launch_dependents();
-  pdl_wait();
-  GLMRT_CHAIN_READY();
   __shared__ float partial[kSmallWarps][kSmallChunkRows][kSmallExperts];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int e0 = blockIdx.x * kSmallExperts;
@@ -118,7 +116,9 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
   const int nrows = min(chunk_rows, rows - row0);
   if (nrows <= 0) return;
   const int steps = hidden / 128;
-  // this warp's slice of the weight rows stays in registers for the whole sweep over the rows
+  // this warp's slice of the weight rows stays in registers for the whole sweep over the rows.  The
+  // router weight is a constant of the layer, not a result of the kernel in front: it is loaded
+  // before griddepcontrol.wait, under that kernel's tail
   float4 wr[kSmallExperts][kSmallMaxSteps];
 #pragma unroll
   for (int e = 0; e < kSmallExperts; ++e) {
@@ -129,6 +129,8 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
       wr[e][s] = j < steps ? load_w4<WT>(we + j * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
+  pdl_wait();   // the activation rows may be the previous kernel's output
+  GLMRT_CHAIN_READY();
   GLMRT_CHAIN_MARK(0);
   // CTAs walk the row groups in rotated order: all of them reading the same activation lines at the
   // same moment would queue on a few L2 slices (a row's result does not depend on the order)
