@@ -157,6 +157,9 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   // here on this kernel reads what earlier kernels wrote.  The overlapped FC2 does not wait for
   // FC1's completion (FC1 raised launch_dependents only after everything older than itself was
   // complete); it reads what it needs of FC1 tile by tile, below.
+  // cache policies of the loads (register-only; created before the wait, off the critical path)
+  const uint64_t pol_w = policy_evict_first();   // weights are read once
+  const uint64_t pol_x = policy_evict_last();    // activations are re-read by every feature tile
   if (!kDynamic) pdl_wait();
   GLMRT_CHAIN_READY();
   if (kOverlap && kFC1) pdl_launch_dependents();
@@ -197,8 +200,6 @@ expert_gemm_kernel(FfnArgs a, const __grid_constant__ CUtensorMap map_a0, const 
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first();   // weights are read once
-      const uint64_t pol_x = policy_evict_last();    // activations are re-read by every feature tile
       const uint8_t* sfa0 = kFC1 ? a.gate_sf : a.down_sf;
       const uint8_t* sfa1 = a.up_sf;
       const uint8_t* sfb = kFC1 ? a.act1_sf : a.act2_sf;
