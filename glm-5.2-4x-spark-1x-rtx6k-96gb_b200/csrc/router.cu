@@ -194,6 +194,13 @@ router_logits_small_kernel(const uint16_t* __restrict__ x, const WT* __restrict_
 // One warp per row.  Shared memory: per warp 2 * `experts` floats (used above 256 experts; up to
 // 256 a lane keeps its eight experts in registers).
 constexpr int kSelectPerLane = 8;
+// Order-preserving integer key of a selection score (-0 and +0 get the same key, as they compare
+// equal); -inf, the mark of an entry that must never be picked, gets the lowest key of all.
+constexpr uint32_t kSelectNoKey = 0x007fffffu;   // key of -inf
+__device__ __forceinline__ uint32_t select_key(float v) {
+  const uint32_t bits = __float_as_uint(v + 0.0f);
+  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      uint32_t* __restrict__ topk_indices, float* __restrict__ topk_scores,
                                      float* __restrict__ topk_weights, int rows, int experts, int top_k,
@@ -210,7 +217,10 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   float* sel = smem + static_cast<size_t>(warp) * 2 * experts;
   float* raw = sel + experts;
   const bool in_regs = experts <= 32 * kSelectPerLane;   // GLM-5.2's 256 experts: eight per lane
-  float vsel[kSelectPerLane], vraw[kSelectPerLane];      // lane's experts j * 32 + lane (register path)
+  // register path: the lane's experts j * 32 + lane as (order-preserving key of the selection score,
+  // expert id, raw score)
+  uint32_t vkey[kSelectPerLane], vid[kSelectPerLane];
+  float vraw[kSelectPerLane];
   for (int base = 0; base < experts; base += 32 * kSelectPerLane) {
     // All loads of a pass are issued before any is used: one memory round trip per 256 experts
     // instead of one per expert.  A logit may arrive as `splits` partial sums (tensor-core router
@@ -243,7 +253,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
       const float pick = (fin && isfinite(corrected) && e < experts) ? corrected : -CUDART_INF_F;
       if (in_regs) {
         vraw[j] = score;
-        vsel[j] = pick;
+        vid[j] = static_cast<uint32_t>(e);
+        vkey[j] = select_key(pick);
       } else if (e < experts) {
         raw[e] = score;
         sel[e] = pick;
@@ -252,6 +263,25 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   }
   __syncwarp();
   GLMRT_CHAIN_MARK(0);
+  if (in_regs) {
+    // The lane's eight candidates are sorted once (best first; equal scores: lower expert first), so
+    // that every rank below looks at the lane's head only.  19 compare-exchanges, four at a time.
+    auto order = [&](int i, int j) {
+      const bool swap = vkey[j] > vkey[i] || (vkey[j] == vkey[i] && vid[j] < vid[i]);
+      const uint32_t ki = vkey[i], ii = vid[i];
+      const float ri = vraw[i];
+      vkey[i] = swap ? vkey[j] : ki; vid[i] = swap ? vid[j] : ii; vraw[i] = swap ? vraw[j] : ri;
+      vkey[j] = swap ? ki : vkey[j]; vid[j] = swap ? ii : vid[j]; vraw[j] = swap ? ri : vraw[j];
+    };
+    static_assert(kSelectPerLane == 8, "the sorting network below is the 8-input one");
+    order(0, 1); order(2, 3); order(4, 5); order(6, 7);
+    order(0, 2); order(1, 3); order(4, 6); order(5, 7);
+    order(1, 2); order(5, 6); order(0, 4); order(3, 7);
+    order(1, 5); order(2, 6);
+    order(1, 4); order(3, 6);
+    order(2, 4); order(3, 5);
+    order(3, 4);
+  }
   float sum = 0.0f;
   float my_score = 0.0f;   // lane j keeps the score of rank j (top_k <= 64: two per lane)
   float my_score2 = 0.0f;
@@ -260,29 +290,18 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     float score = 0.0f;
     uint32_t idx = 0;
     if (in_regs) {
-      // the lane's best (first maximum in ascending expert order), then two warp reductions: the
-      // largest value, and the lowest expert among the lanes that hold it
-      float best = -CUDART_INF_F;
-      int best_j = 0;
-#pragma unroll
-      for (int j = 0; j < kSelectPerLane; ++j)
-        if (vsel[j] > best) { best = vsel[j]; best_j = j; }
-      const uint32_t bits = __float_as_uint(best + 0.0f);    // -0 becomes +0: equal as floats, equal as keys
-      const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);   // order-preserving
-      const uint32_t top = __reduce_max_sync(0xffffffffu, key);
-      const uint32_t cand = (key == top && best > -CUDART_INF_F) ? static_cast<uint32_t>(best_j * 32 + lane) : 0x7fffffffu;
+      // two warp reductions over the lanes' heads: the largest key, and the lowest expert among the
+      // lanes that hold it; the winning lane moves on to its next candidate
+      const uint32_t top = __reduce_max_sync(0xffffffffu, vkey[0]);
+      const uint32_t cand = (vkey[0] == top && top != kSelectNoKey) ? vid[0] : 0x7fffffffu;
       const uint32_t win = __reduce_min_sync(0xffffffffu, cand);
       if (win != 0x7fffffffu) {   // a finite candidate exists
-        float r = 0.0f;
-#pragma unroll
-        for (int j = 0; j < kSelectPerLane; ++j)
-          if (j == static_cast<int>(win >> 5)) r = vraw[j];
-        score = __shfl_sync(0xffffffffu, r, static_cast<int>(win & 31u));
+        score = __shfl_sync(0xffffffffu, vraw[0], static_cast<int>(win & 31u));
         idx = win;
         if (lane == static_cast<int>(win & 31u)) {
 #pragma unroll
-          for (int j = 0; j < kSelectPerLane; ++j)
-            if (j == static_cast<int>(win >> 5)) vsel[j] = -CUDART_INF_F;   // never picked again
+          for (int j = 0; j + 1 < kSelectPerLane; ++j) { vkey[j] = vkey[j + 1]; vid[j] = vid[j + 1]; vraw[j] = vraw[j + 1]; }
+          vkey[kSelectPerLane - 1] = kSelectNoKey;
         }
       }
     } else {
