@@ -417,7 +417,10 @@ def run_gpu(args):
                     "traffic": NCU_FC1_TRAFFIC_PER_EXPERT * distinct,
                     "traffic_source": "ncu dram read+write of one FC1 launch on a 64-expert T=16 case "
                                       "(profiles/expert_gemm_fc1_fc2_E64_T16_ncu_full.md), per expert touched, "
-                                      "times the experts touched here"}
+                                      "times the experts touched here",
+                    "note": "the weights of this kernel's first 48 (work item, 128-row tile) pairs, 38 MB of its "
+                            "3.1 GB, are asked into the L2 by extra CTAs of the dispatch kernel before it starts "
+                            "(GLMRT_B200_PREFETCH_FC1=0 turns that off); the ncu capture predates that prefetch"}
     else:
         # prefill: the contraction is what one pays for; FP4 runs at four times the bf16 rate and the
         # measured peaks hold a bf16 figure only, so the peak is 4 x the measured bf16 burst figure
