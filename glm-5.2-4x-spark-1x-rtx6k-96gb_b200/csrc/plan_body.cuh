@@ -22,6 +22,67 @@ __device__ __forceinline__ int plan_slot_of_position(int pos, int chunk_tokens, 
   return chunk_tokens < 128 ? (pos >> shift) * 128 + (pos & (chunk_tokens - 1)) : pos;
 }
 
+// The plan of at most 32 routes (up to four rows of top-8: the single-row decode step) by one warp,
+// without the shared-memory histogram and its barriers: a lane per route, `match.any` finds the
+// routes of the same expert (position = lower lanes among them, count = all of them), an expert's
+// rank among the touched experts (in expert order, as the counting sort places them) is counted over
+// the 32 lanes, and every touched expert gets one work item in a 128-slot group of its own.  Same
+// outputs as the general body below for the same routes, except that a route's position inside its
+// expert follows the route order (there: the order of the atomic counter).  Decode layout only
+// (32-token work items), all experts local.
+__device__ __forceinline__ void route_plan_tiny(const PlanArgs& a, int nthreads) {
+  const int n = a.rows * a.top_k;
+  for (int i = threadIdx.x; i < a.experts; i += nthreads) a.expert_counts[i] = 0;
+  __syncthreads();   // the counts of the touched experts are stored after the zeros
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  const uint32_t e = lane < n ? a.topk_indices[lane] : kNoRoute;
+  const bool valid = e != kNoRoute && e < static_cast<uint32_t>(a.experts);
+  const unsigned bad = __ballot_sync(0xffffffffu, lane < n && e != kNoRoute && e >= static_cast<uint32_t>(a.experts));
+  const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : (0x80000000u | static_cast<uint32_t>(lane)));
+  const int pos = __popc(peers & ((1u << lane) - 1u));
+  const int count = __popc(peers);
+  const bool leader = valid && pos == 0;
+  int rank = 0;
+#pragma unroll 8
+  for (int k = 0; k < 32; ++k) {
+    const uint32_t ek = __shfl_sync(0xffffffffu, e, k);
+    const int lk = __shfl_sync(0xffffffffu, leader ? 1 : 0, k);
+    rank += (lk != 0 && ek < e) ? 1 : 0;
+  }
+  const int distinct = __popc(__ballot_sync(0xffffffffu, leader));
+  const int routes = __popc(__ballot_sync(0xffffffffu, valid));
+  const int total_slots = 128 * distinct;
+  int err = bad != 0u ? static_cast<int>(kErrBadExpert) : 0;
+  if (total_slots > a.max_slots) err |= static_cast<int>(kErrSlotOverflow);
+  if (distinct > a.max_chunks) err |= static_cast<int>(kErrChunkOverflow);
+  if (leader) {
+    a.expert_counts[e] = count;
+    if (err == 0) {
+      Chunk ch;
+      ch.expert = static_cast<int32_t>(e);
+      ch.slot_base = rank * 128;
+      ch.tokens = count;
+      ch.reserved = 0;
+      a.chunks[rank] = ch;
+    }
+  }
+  if (lane < n) {
+    const int slot = (valid && err == 0) ? rank * 128 + pos : -1;
+    a.route_slot[lane] = slot;
+    if (slot >= 0) a.slot_route[slot] = lane;
+  }
+  if (a.fc_sync != nullptr && err == 0)
+    for (int i = lane; i < kFcSyncHeader + distinct; i += 32) a.fc_sync[i] = 0u;
+  if (lane == 0) {
+    a.counters[kCntChunks] = err != 0 ? 0u : static_cast<uint32_t>(distinct);   // never launch expert work on an inconsistent plan
+    a.counters[kCntSlots] = static_cast<uint32_t>(total_slots);
+    a.counters[kCntError] = static_cast<uint32_t>(err);   // also clears the word for the kernels that follow
+    a.counters[kCntDistinct] = static_cast<uint32_t>(distinct);
+    a.counters[kCntLocalRoutes] = static_cast<uint32_t>(routes);
+  }
+}
+
 constexpr int kPlanKeep = 4;   // routes a thread keeps in registers between the counting and the placing pass
 
 __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads) {
@@ -29,6 +90,10 @@ __device__ __forceinline__ void route_plan_body(const PlanArgs& a, int nthreads)
   __shared__ int base[kMaxLocalExperts];
   __shared__ int s_error;
   __shared__ int s_total_chunks;
+  if (a.rows * a.top_k <= 32 && a.ep_world == 1 && a.chunk_tokens == 32) {
+    route_plan_tiny(a, nthreads);
+    return;
+  }
   const int local_experts = (a.experts - a.ep_rank + a.ep_world - 1) / a.ep_world;
   const int shift = 31 - __clz(a.chunk_tokens);
   for (int i = threadIdx.x; i < local_experts; i += nthreads) cnt[i] = 0;
