@@ -288,6 +288,44 @@ def test_stream_data_frames_parse_with_their_own_rules(P, Err):
         make_request(P, 1, P.ExpertV2SourceKind.Decode, hidden_dim=32, flags=flags).encode()
 
 
+def test_streamed_request_frames_parse_and_carry_the_plan(P):
+    """Sender side of streamed ingress (protocol_v2/stream.rs:9-27, 86-150; request.rs:183-230): a
+    stream-plan frame with the request's rows and routes and the GLMSTRM2 plan as payload, then
+    stream-data frames with runs of rows in the plan's order; the last one is flagged final."""
+    rows, hidden = 5, 64
+    req = make_request(P, rows, P.ExpertV2SourceKind.MtpVerify, hidden_dim=hidden)
+    stride = 2 * hidden
+    req.hidden_payload = bytes((r * 16 + (i % 16)) & 0xff for r in range(rows) for i in range(stride))
+    order = [3, 0, 4, 1, 2]
+    groups = [P.ExpertProtocolV2StreamRouteGroup(2, [6, 7, 0, 1], [3, 0]),
+              P.ExpertProtocolV2StreamRouteGroup(5, [8, 9, 2, 3, 4, 5], [4, 1, 2])]
+    plan = P.ExpertProtocolV2StreamPlan(rows, len(req.routes), order, groups)
+    blob = plan.encode()
+    assert blob[:8] == b"GLMSTRM2" and struct.unpack_from("<HHI", blob, 8) == (1, 40, len(blob))
+    assert struct.unpack_from("<IIIIII", blob, 16) == (rows, len(req.routes), rows, 2, 10, 5)
+    assert len(blob) == 40 + 2 * 20 + 4 * (5 + 10 + 5)
+    assert struct.unpack_from("<IIIII", blob, 60) == (5, 4, 6, 2, 3)          # second group: offsets follow the first
+    assert list(struct.unpack_from("<5I", blob, 80)) == order
+
+    frames = P.streamed_request_frames(req, plan, 2)
+    assert len(frames) == 1 + 3
+    head = P.ExpertProtocolV2RequestView.parse(frames[0])
+    assert head.header.flags & P.EXPERT_PROTOCOL_V2_FLAG_STREAM_PLAN
+    assert head.header.row_count == rows and head.header.route_count == len(req.routes)
+    assert head.hidden_payload() == blob
+    seen = []
+    for k, frame in enumerate(frames[1:]):
+        v = P.ExpertProtocolV2RequestView.parse(frame)
+        final = bool(v.header.flags & P.EXPERT_PROTOCOL_V2_FLAG_STREAM_FINAL)
+        assert v.header.flags & P.EXPERT_PROTOCOL_V2_FLAG_STREAM_DATA and final == (k == 2)
+        assert v.header.route_count == 2 * k and v.row_descriptor_count == 0      # position of the run's first row
+        run = order[2 * k:2 * k + 2]
+        assert v.header.row_count == len(run)
+        assert v.hidden_payload() == b"".join(req.hidden_payload[r * stride:(r + 1) * stride] for r in run)
+        seen += run
+    assert seen == order
+
+
 # ---------------------------------------------------------------------------------------------
 # The reference's own frame validator (native/src/glmrt_native.cc, compiled by oracle/build_ref.py
 # into oracle/_ref/) on the frames this repository encodes: pins magic, version, kind, the header
@@ -340,6 +378,10 @@ def all_test_frames(P):
     checked = P.ExpertProtocolV2Response(5, 1, 0, 3, 64, D.Bf16, ok, b"\x22" * 384)
     checked.with_debug_checksum().with_row_indices([2, 1, 0], False)
     out.append((checked.encode(), 2))
+    streamed = make_request(P, 4, K.MtpVerify, hidden_dim=64)
+    plan = P.ExpertProtocolV2StreamPlan(4, len(streamed.routes), [2, 0, 3, 1],
+                                        [P.ExpertProtocolV2StreamRouteGroup(4, list(range(len(streamed.routes))), [0, 1, 2, 3])])
+    out += [(f, 1) for f in P.streamed_request_frames(streamed, plan, 3)]
     return out
 
 
